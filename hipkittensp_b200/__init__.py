@@ -1,0 +1,10 @@
+"""B200-native MX-FP6 GEMM: C[M,N] (bf16) = A[M,K] @ B[N,K]^T with packed 6-bit operands and E8M0
+block scales, behind the `tk_kernel.dispatch_micro` calling convention of benenzhu/HipKittensP.
+
+The compute path is the CUDA library libmxfp6.so (C ABI: include/mxfp6.h); importing this package
+fails if it has not been built (`python -m hipkittensp_b200.build`)."""
+from ._lib import E2M3, E3M2, LIB_PATH, Mxfp6Error, lib  # noqa: F401
+from .gemm import dequantize, device_status, dispatch_micro, gemm, quantize, tma_dump  # noqa: F401
+
+__all__ = ["E2M3", "E3M2", "dispatch_micro", "gemm", "quantize", "dequantize", "device_status", "tma_dump",
+           "Mxfp6Error", "lib", "LIB_PATH"]

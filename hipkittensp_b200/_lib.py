@@ -1,0 +1,63 @@
+"""ctypes binding of libmxfp6.so (the C ABI in include/mxfp6.h).  There is no fallback: if the library
+is missing or does not load, importing this module raises."""
+from __future__ import annotations
+
+import ctypes
+import os
+
+_PKG = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_PKG, "libmxfp6.so")
+
+E2M3 = 0
+E3M2 = 1
+
+OK, ERR_BAD_ARG, ERR_CUDA, ERR_DEVICE_WAIT, ERR_UNSUPPORTED = 0, 1, 2, 3, 4
+
+# every symbol include/mxfp6.h declares
+SYMBOLS = ("mxfp6_version", "mxfp6_last_error", "mxfp6_gemm", "mxfp6_gemm_workspace_bytes", "mxfp6_gemm_ws",
+           "mxfp6_quantize", "mxfp6_dequantize", "mxfp6_device_status", "mxfp6_debug_tma_dump")
+
+
+class Mxfp6Error(RuntimeError):
+    def __init__(self, code: int, msg: str):
+        super().__init__(f"mxfp6 error {code}: {msg}")
+        self.code = code
+
+
+def _load() -> ctypes.CDLL:
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(f"{LIB_PATH} is missing: build it with `python -m hipkittensp_b200.build` "
+                          "(there is no CPU or PyTorch fallback for this path)")
+    try:
+        import torch  # noqa: F401  -- loads the CUDA runtime torch ships, so both share one runtime instance
+    except Exception:
+        pass
+    lib = ctypes.CDLL(LIB_PATH)
+    vp, i64, ci, sz = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int, ctypes.c_size_t
+    lib.mxfp6_version.restype = ci
+    lib.mxfp6_version.argtypes = []
+    lib.mxfp6_last_error.restype = ctypes.c_char_p
+    lib.mxfp6_last_error.argtypes = []
+    lib.mxfp6_gemm.restype = ci
+    lib.mxfp6_gemm.argtypes = [vp, vp, vp, vp, vp, i64, i64, i64, ci, ci, vp]
+    lib.mxfp6_gemm_workspace_bytes.restype = sz
+    lib.mxfp6_gemm_workspace_bytes.argtypes = [i64, i64, i64]
+    lib.mxfp6_gemm_ws.restype = ci
+    lib.mxfp6_gemm_ws.argtypes = [vp, vp, vp, vp, vp, i64, i64, i64, ci, ci, vp, sz, vp]
+    lib.mxfp6_quantize.restype = ci
+    lib.mxfp6_quantize.argtypes = [vp, ci, i64, i64, ci, vp, vp, vp]
+    lib.mxfp6_dequantize.restype = ci
+    lib.mxfp6_dequantize.argtypes = [vp, vp, i64, i64, ci, vp, vp]
+    lib.mxfp6_device_status.restype = ci
+    lib.mxfp6_device_status.argtypes = [ctypes.POINTER(ci)]
+    lib.mxfp6_debug_tma_dump.restype = ci
+    lib.mxfp6_debug_tma_dump.argtypes = [vp, i64, i64, i64, i64, vp, vp]
+    return lib
+
+
+lib = _load()
+
+
+def check(rc: int) -> None:
+    if rc != OK:
+        raise Mxfp6Error(rc, lib.mxfp6_last_error().decode())

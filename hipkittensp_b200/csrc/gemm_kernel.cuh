@@ -1,0 +1,489 @@
+// MX-FP6 block-scaled GEMM for sm_100a:  D[p,q] = sum_k P[p,k] * Q[q,k]   (both operands K-contiguous)
+//
+//   P : "row" operand of the tensor-core instruction, 128 rows per tile  (MMA operand A)
+//   Q : "column" operand, BN rows per tile                               (MMA operand B)
+//
+// The host maps (A,B) of C = A*B^T onto (P,Q): normally P=A, Q=B and D is stored as C[p,q]; for
+// skinny M the operands are swapped (P=B, Q=A, SWAP=true) and D is stored transposed, C[q,p], so the
+// long dimension rides the 128-row side of the instruction.
+//
+// One persistent CTA per SM, 8 warps with fixed roles:
+//   warp 0   TMA producer: packed 6-bit operand tiles (tensor-map type 16U6_ALIGN16B, 128-byte swizzle)
+//            and raw E8M0 scale slabs into shared-memory rings
+//   warp 1   MMA issuer: copies the scale atoms into TMEM (tcgen05.cp) and issues
+//            tcgen05.mma.kind::mxf8f6f4.block_scale, accumulating in TMEM
+//   warp 2   scale re-tiler: row-major [rows, K/32] scale bytes -> the 32x16-byte atoms the MMA wants
+//   warp 3   idle
+//   warps 4-7 epilogue: TMEM -> registers -> bf16 -> global (or fp32 partials for split tiles)
+//
+// Every wait on an mbarrier is bounded; on expiry the CTA records a status code and leaves cleanly.
+#pragma once
+#include "ptx.cuh"
+
+namespace mxfp6 {
+
+// device status codes (0 = ok); the low byte is the code, the rest identifies the CTA
+enum : int {
+    kStatusOk = 0,
+    kStatusTimeoutProducer = 1,
+    kStatusTimeoutMma = 2,
+    kStatusTimeoutScale = 3,
+    kStatusTimeoutEpilogue = 4,
+};
+
+struct GemmParams {
+    int p_rows, q_rows;        // valid rows of P and Q
+    int kblocks;               // K / 128
+    int tiles_p, tiles_q;      // ceil(p_rows/128), ceil(q_rows/BN)
+    int ldc;                   // row stride of C in elements (= N)
+    int c_rows, c_cols;        // M, N
+    uint32_t idesc;            // instruction descriptor without scale ids
+    int sf_tma;                // 1: scale slabs come by TMA; 0: the scale warp reads them with plain loads
+    int sf_ld;                 // K / 32, row stride of the scale arrays in bytes
+    int stage_tx_bytes;        // bytes one operand stage reports to its mbarrier
+    const uint8_t* sfp;        // scales of P / Q (row-major [rows, K/32])
+    const uint8_t* sfq;
+    __nv_bfloat16* c;
+    float* ws_partial;         // split-tile partial sums: [tile][slot][BN][128] fp32
+    unsigned int* ws_counter;  // per-tile arrival counters (zero between launches)
+    int ws_slots;              // partial slots per tile
+    int* status;               // device status word
+    unsigned long long wait_cycles;  // budget of one wait in clock cycles
+};
+
+template <int BN_, bool SWAP_, bool STREAMK_>
+struct GemmCfg {
+    static constexpr int BN = BN_;
+    static constexpr bool SWAP = SWAP_;
+    static constexpr bool STREAMK = STREAMK_;
+    static constexpr int BM = 128;
+    static constexpr int BK = 128;                       // elements of K per pipeline stage (= bytes in smem)
+    static constexpr int P_BYTES = BM * BK;
+    static constexpr int Q_BYTES = BN * BK;
+    static constexpr int STAGE_BYTES = P_BYTES + Q_BYTES;
+    static constexpr int STAGES = BN >= 256 ? 4 : BN >= 128 ? 6 : BN >= 64 ? 8 : 10;
+    static constexpr int QATOMS = (BN + 127) / 128;      // 128-row scale atoms on the Q side
+    static constexpr int RAW_SLOTS = BN >= 256 ? 2 : 4;  // each raw slab covers 4 K-blocks (16 scale bytes per row)
+    static constexpr int RAW_Q_ROWS = BN < 32 ? 32 : BN;
+    static constexpr int RAW_BYTES = (BM + RAW_Q_ROWS) * 16;
+    static constexpr int RAW_TX_BYTES = (BM + BN) * 16;
+    static constexpr int ATOM_SLOTS = 8;
+    static constexpr int ATOM_BYTES = 512 * (1 + QATOMS);
+    static constexpr bool OVERLAP = BN == 256;           // two 256-column accumulators share 32 columns
+    static constexpr int ACC_COL1 = OVERLAP ? 224 : BN;
+    static constexpr int SF_COL = OVERLAP ? 480 : 2 * BN;
+    static constexpr int TMEM_COLS = 512;
+    static constexpr int NUM_BARS = 2 * STAGES + 2 * RAW_SLOTS + 2 * ATOM_SLOTS + 5;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + RAW_SLOTS * RAW_BYTES + ATOM_SLOTS * ATOM_BYTES +
+                                      NUM_BARS * 8 + 64;
+    static constexpr int SMEM_ALLOC = SMEM_BYTES + 1024;  // slack for the 1024-byte alignment of the operand ring
+    static constexpr int THREADS = 256;
+    static constexpr int GROUP_P = 8;                     // tile rasterisation: groups of 8 P-tiles share Q-tiles
+    static_assert(SMEM_ALLOC <= 232448, "exceeds the 227 KiB of shared memory a CTA can have");
+};
+
+// One unit of work of a CTA: a K range of one output tile.
+struct Segment {
+    int tile, p0, q0, k0, k1;
+    int nseg, segidx;           // how many CTAs contribute to this tile, and which of them this is
+};
+
+template <class Cfg>
+struct SegIter {
+    const GemmParams& P;
+    int num_tiles;
+    long long u, u_end;          // STREAMK: current / last K-block unit of this CTA
+    int tile;                    // !STREAMK: current tile
+    __device__ SegIter(const GemmParams& p) : P(p) {
+        num_tiles = P.tiles_p * P.tiles_q;
+        if (Cfg::STREAMK) {
+            long long U = (long long)num_tiles * P.kblocks;
+            u = (U * blockIdx.x) / gridDim.x;
+            u_end = (U * (blockIdx.x + 1)) / gridDim.x;
+        } else {
+            tile = blockIdx.x;
+            u = u_end = 0;
+        }
+    }
+    __device__ static int owner(long long unit, long long U, int G) { return (int)(((unit + 1) * G - 1) / U); }
+    __device__ void coords(int t, int& p0, int& q0) const {
+        int per_group = Cfg::GROUP_P * P.tiles_q;
+        int group = t / per_group, in = t % per_group;
+        int first_p = group * Cfg::GROUP_P;
+        int gsz = min(P.tiles_p - first_p, Cfg::GROUP_P);
+        p0 = (first_p + in % gsz) * Cfg::BM;
+        q0 = (in / gsz) * Cfg::BN;
+    }
+    __device__ bool next(Segment& s) {
+        if (Cfg::STREAMK) {
+            if (u >= u_end) return false;
+            long long U = (long long)num_tiles * P.kblocks;
+            s.tile = (int)(u / P.kblocks);
+            s.k0 = (int)(u % P.kblocks);
+            long long left = u_end - u;
+            s.k1 = (int)min((long long)P.kblocks, s.k0 + left);
+            long long t0 = (long long)s.tile * P.kblocks;
+            int first = owner(t0, U, gridDim.x), last = owner(t0 + P.kblocks - 1, U, gridDim.x);
+            s.nseg = last - first + 1;
+            s.segidx = (int)blockIdx.x - first;
+            coords(s.tile, s.p0, s.q0);
+            u += s.k1 - s.k0;
+            return true;
+        } else {
+            if (tile >= num_tiles) return false;
+            s.tile = tile; s.k0 = 0; s.k1 = P.kblocks; s.nseg = 1; s.segidx = 0;
+            coords(tile, s.p0, s.q0);
+            tile += gridDim.x;
+            return true;
+        }
+    }
+};
+
+// Bounded wait.  Returns false when the CTA is aborting (this wait ran out, or another one did).
+__device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                         const GemmParams& P, int code) {
+    if (mbar_try_wait(bar, parity)) return true;
+    long long t0 = clock64();
+    uint32_t n = 0;
+    while (!mbar_try_wait(bar, parity)) {
+        if ((++n & 255u) == 0) {
+            if (*abort_flag) return false;
+            if ((unsigned long long)(clock64() - t0) > P.wait_cycles) {
+                *abort_flag = 1;
+                atomicCAS(P.status, 0, code | ((int)blockIdx.x << 8));
+                return false;
+            }
+        }
+    }
+    return true;
+}
+
+// Same, for a whole converged warp: every lane waits, and all lanes agree on the outcome.
+__device__ __forceinline__ bool wait_bar_warp(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                              const GemmParams& P, int code) {
+    return __all_sync(0xffffffffu, wait_bar(bar, parity, abort_flag, P, code));
+}
+
+template <class Cfg>
+__global__ void __launch_bounds__(Cfg::THREADS, 1)
+mxfp6_gemm_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__ CUtensorMap tm_q,
+                  const __grid_constant__ CUtensorMap tm_sfp, const __grid_constant__ CUtensorMap tm_sfq,
+                  const GemmParams P) {
+    constexpr int BN = Cfg::BN;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+
+    // ---- shared-memory carve-up
+    const uint32_t stage_base = smem_base;
+    const uint32_t raw_base = stage_base + Cfg::STAGES * Cfg::STAGE_BYTES;
+    const uint32_t atom_base = raw_base + Cfg::RAW_SLOTS * Cfg::RAW_BYTES;
+    const uint32_t bar_base = atom_base + Cfg::ATOM_SLOTS * Cfg::ATOM_BYTES;
+    auto bar_full = [&](int s) { return bar_base + 8u * s; };
+    auto bar_empty = [&](int s) { return bar_base + 8u * (Cfg::STAGES + s); };
+    auto bar_raw_full = [&](int s) { return bar_base + 8u * (2 * Cfg::STAGES + s); };
+    auto bar_raw_empty = [&](int s) { return bar_base + 8u * (2 * Cfg::STAGES + Cfg::RAW_SLOTS + s); };
+    auto bar_atom_full = [&](int s) { return bar_base + 8u * (2 * Cfg::STAGES + 2 * Cfg::RAW_SLOTS + s); };
+    auto bar_atom_empty = [&](int s) { return bar_base + 8u * (2 * Cfg::STAGES + 2 * Cfg::RAW_SLOTS + Cfg::ATOM_SLOTS + s); };
+    const uint32_t bar_misc = bar_base + 8u * (2 * Cfg::STAGES + 2 * Cfg::RAW_SLOTS + 2 * Cfg::ATOM_SLOTS);
+    auto bar_acc_full = [&](int b) { return bar_misc + 8u * b; };
+    auto bar_acc_empty = [&](int b) { return bar_misc + 8u * (2 + b); };
+    const uint32_t bar_ovl = bar_misc + 8u * 4;
+    const uint32_t misc_off = (bar_base - smem_base) + Cfg::NUM_BARS * 8;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_gen + misc_off);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + misc_off + 4);
+    volatile int* ticket_slot = reinterpret_cast<volatile int*>(smem_gen + misc_off + 8);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < Cfg::STAGES; ++s) { mbar_init(bar_full(s), 1); mbar_init(bar_empty(s), 1); }
+        for (int s = 0; s < Cfg::RAW_SLOTS; ++s) { mbar_init(bar_raw_full(s), 1); mbar_init(bar_raw_empty(s), 32); }
+        for (int s = 0; s < Cfg::ATOM_SLOTS; ++s) { mbar_init(bar_atom_full(s), 32); mbar_init(bar_atom_empty(s), 1); }
+        for (int b = 0; b < 2; ++b) { mbar_init(bar_acc_full(b), 1); mbar_init(bar_acc_empty(b), 128); }
+        mbar_init(bar_ovl, 128);
+        *abort_flag = 0;
+        *ticket_slot = 0;
+        fence_barrier_init();
+    }
+    if (warp == 0 && lane == 0) {
+        tma_prefetch_desc(&tm_p); tma_prefetch_desc(&tm_q);
+        if (P.sf_tma) { tma_prefetch_desc(&tm_sfp); tma_prefetch_desc(&tm_sfq); }
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(tmem_slot), Cfg::TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    // =========================================================== warp 0: TMA producer
+    if (warp == 0) {
+        // the whole warp walks the schedule (so it stays converged for the final barrier); lane 0 issues
+        SegIter<Cfg> it(P);
+        Segment sg;
+        uint32_t n_stage = 0, n_raw = 0;
+        bool ok = true;
+        while (ok && it.next(sg)) {
+            for (int kb = sg.k0; kb < sg.k1 && ok; ++kb) {
+                if (P.sf_tma && (kb == sg.k0 || (kb & 3) == 0)) {
+                    const int r = n_raw % Cfg::RAW_SLOTS;
+                    const uint32_t ph = (n_raw / Cfg::RAW_SLOTS) & 1;
+                    ok = wait_bar_warp(bar_raw_empty(r), ph ^ 1, abort_flag, P, kStatusTimeoutProducer);
+                    if (!ok) break;
+                    if (lane == 0) {
+                        const uint32_t dst = raw_base + r * Cfg::RAW_BYTES;
+                        mbar_arrive_expect_tx(bar_raw_full(r), Cfg::RAW_TX_BYTES);
+                        tma_load_2d(dst, &tm_sfp, bar_raw_full(r), (kb >> 2) * 16, sg.p0);
+                        tma_load_2d(dst + Cfg::BM * 16, &tm_sfq, bar_raw_full(r), (kb >> 2) * 16, sg.q0);
+                    }
+                    ++n_raw;
+                }
+                const int s = n_stage % Cfg::STAGES;
+                const uint32_t ph = (n_stage / Cfg::STAGES) & 1;
+                ok = wait_bar_warp(bar_empty(s), ph ^ 1, abort_flag, P, kStatusTimeoutProducer);
+                if (!ok) break;
+                if (lane == 0) {
+                    const uint32_t dst = stage_base + s * Cfg::STAGE_BYTES;
+                    mbar_arrive_expect_tx(bar_full(s), (uint32_t)P.stage_tx_bytes);
+                    tma_load_2d(dst, &tm_p, bar_full(s), kb * Cfg::BK, sg.p0);
+                    tma_load_2d(dst + Cfg::P_BYTES, &tm_q, bar_full(s), kb * Cfg::BK, sg.q0);
+                }
+                __syncwarp();
+                ++n_stage;
+            }
+        }
+    }
+    // =========================================================== warp 1: MMA issuer
+    else if (warp == 1) {
+        SegIter<Cfg> it(P);
+        Segment sg;
+        uint32_t n_kb = 0, n_seg = 0;
+        bool ok = true;
+        while (ok && it.next(sg)) {
+            const int b = n_seg & 1;
+            const uint32_t acc = tmem_base + (b ? Cfg::ACC_COL1 : 0);
+            if (Cfg::OVERLAP) {
+                if (n_seg > 0) ok = wait_bar_warp(bar_ovl, (n_seg - 1) & 1, abort_flag, P, kStatusTimeoutMma);
+            } else {
+                ok = wait_bar_warp(bar_acc_empty(b), ((n_seg >> 1) & 1) ^ 1, abort_flag, P, kStatusTimeoutMma);
+            }
+            if (!ok) break;
+            tc_fence_after();
+            for (int kb = sg.k0; kb < sg.k1; ++kb) {
+                const int s = n_kb % Cfg::STAGES;
+                const int a = n_kb % Cfg::ATOM_SLOTS;
+                ok = wait_bar_warp(bar_full(s), (n_kb / Cfg::STAGES) & 1, abort_flag, P, kStatusTimeoutMma) &&
+                     wait_bar_warp(bar_atom_full(a), (n_kb / Cfg::ATOM_SLOTS) & 1, abort_flag, P, kStatusTimeoutMma);
+                if (!ok) break;
+                tc_fence_after();
+                if (lane == 0) {
+                    const uint32_t sfa = tmem_base + Cfg::SF_COL + (n_kb & 1) * 16;
+                    const uint32_t sfb = sfa + 4;
+                    const uint32_t atom = atom_base + a * Cfg::ATOM_BYTES;
+                    tc_cp_32x128b_warpx4(sfa, smem_desc_sf(atom));
+#pragma unroll
+                    for (int q = 0; q < Cfg::QATOMS; ++q) tc_cp_32x128b_warpx4(sfb + 4 * q, smem_desc_sf(atom + 512 * (1 + q)));
+                    const uint32_t sp = stage_base + s * Cfg::STAGE_BYTES;
+                    const uint64_t adesc = smem_desc_sw128(sp);
+                    const uint64_t bdesc = smem_desc_sw128(sp + Cfg::P_BYTES);
+#pragma unroll
+                    for (uint32_t k = 0; k < 4; ++k) {
+                        mma_mxf8f6f4(acc, adesc + 2 * k, bdesc + 2 * k, idesc_with_sf(P.idesc, k),
+                                     sfa | (k << 30), sfb | (k << 30), (kb > sg.k0 || k > 0) ? 1u : 0u);
+                    }
+                    tc_commit(bar_empty(s));
+                    tc_commit(bar_atom_empty(a));
+                }
+                __syncwarp();
+                ++n_kb;
+            }
+            if (!ok) break;
+            if (lane == 0) tc_commit(bar_acc_full(b));
+            __syncwarp();
+            ++n_seg;
+        }
+    }
+    // =========================================================== warp 2: scale re-tiler
+    else if (warp == 2) {
+        SegIter<Cfg> it(P);
+        Segment sg;
+        uint32_t n_kb = 0, n_raw = 0;
+        bool ok = true;
+        constexpr int QG = (BN + 31) / 32;        // 32-row groups on the Q side
+        uint32_t rp[4][4];                          // [row group][k-block in slab] scale words of P rows
+        uint32_t rq[QG][4];
+        while (ok && it.next(sg)) {
+            for (int kb = sg.k0; kb < sg.k1; ++kb) {
+                const int j = kb & 3;
+                uint32_t wp[4], wq[Cfg::QATOMS * 4];     // this K-block's scale words per 32-row group
+                if (P.sf_tma) {
+                    if (kb == sg.k0 || j == 0) {
+                        const int r = n_raw % Cfg::RAW_SLOTS;
+                        ok = wait_bar_warp(bar_raw_full(r), (n_raw / Cfg::RAW_SLOTS) & 1, abort_flag, P, kStatusTimeoutScale);
+                        if (!ok) break;
+                        const uint8_t* raw = smem_gen + (raw_base - smem_base) + r * Cfg::RAW_BYTES;
+#pragma unroll
+                        for (int c = 0; c < 4; ++c) {
+                            uint4 v = *reinterpret_cast<const uint4*>(raw + (lane + 32 * c) * 16);
+                            rp[c][0] = v.x; rp[c][1] = v.y; rp[c][2] = v.z; rp[c][3] = v.w;
+                        }
+#pragma unroll
+                        for (int c = 0; c < QG; ++c) {
+                            uint4 v = *reinterpret_cast<const uint4*>(raw + Cfg::BM * 16 + (lane + 32 * c) * 16);
+                            rq[c][0] = v.x; rq[c][1] = v.y; rq[c][2] = v.z; rq[c][3] = v.w;
+                        }
+                        mbar_arrive(bar_raw_empty(r));
+                        ++n_raw;
+                    }
+                    // register arrays are indexed with compile-time constants only (no local memory)
+#pragma unroll
+                    for (int c = 0; c < 4; ++c)
+                        wp[c] = j == 0 ? rp[c][0] : j == 1 ? rp[c][1] : j == 2 ? rp[c][2] : rp[c][3];
+#pragma unroll
+                    for (int c = 0; c < Cfg::QATOMS * 4; ++c) {
+                        if (c < QG) wq[c] = j == 0 ? rq[c < QG ? c : 0][0] : j == 1 ? rq[c < QG ? c : 0][1]
+                                          : j == 2 ? rq[c < QG ? c : 0][2] : rq[c < QG ? c : 0][3];
+                        else wq[c] = 0u;
+                    }
+                } else {
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        const int row = sg.p0 + lane + 32 * c;
+                        wp[c] = row < P.p_rows
+                            ? *reinterpret_cast<const uint32_t*>(P.sfp + (size_t)row * P.sf_ld + kb * 4) : 0u;
+                    }
+#pragma unroll
+                    for (int c = 0; c < Cfg::QATOMS * 4; ++c) {
+                        const int row = sg.q0 + lane + 32 * c;
+                        wq[c] = (c < QG && row < P.q_rows)
+                            ? *reinterpret_cast<const uint32_t*>(P.sfq + (size_t)row * P.sf_ld + kb * 4) : 0u;
+                    }
+                }
+                const int a = n_kb % Cfg::ATOM_SLOTS;
+                ok = wait_bar_warp(bar_atom_empty(a), ((n_kb / Cfg::ATOM_SLOTS) & 1) ^ 1, abort_flag, P, kStatusTimeoutScale);
+                if (!ok) break;
+                uint8_t* atom = smem_gen + (atom_base - smem_base) + a * Cfg::ATOM_BYTES;
+                // atom layout: 32 rows of 16 bytes; row (r%32) holds, for the four 32-row groups c = r/32,
+                // the 4 scale bytes of this K-block: byte offset (r%32)*16 + c*4 + (k/32)%4.
+                *reinterpret_cast<uint4*>(atom + lane * 16) = make_uint4(wp[0], wp[1], wp[2], wp[3]);
+#pragma unroll
+                for (int qa = 0; qa < Cfg::QATOMS; ++qa)
+                    *reinterpret_cast<uint4*>(atom + 512 * (1 + qa) + lane * 16) =
+                        make_uint4(wq[4 * qa], wq[4 * qa + 1], wq[4 * qa + 2], wq[4 * qa + 3]);
+                fence_proxy_async_smem();
+                mbar_arrive(bar_atom_full(a));
+                ++n_kb;
+            }
+        }
+    }
+    // =========================================================== warps 4-7: epilogue
+    else if (warp >= 4) {
+        const int quad = warp & 3;
+        const int prow = quad * 32 + lane;                 // row of the tile this thread owns (TMEM lane)
+        const int etid = threadIdx.x - 128;
+        SegIter<Cfg> it(P);
+        Segment sg;
+        uint32_t n_seg = 0;
+        bool ok = true;
+        constexpr int CW = BN >= 32 ? 32 : 16;             // columns per TMEM load
+        constexpr int NCH = BN / CW;
+        while (ok && it.next(sg)) {
+            const int b = n_seg & 1;
+            ok = wait_bar_warp(bar_acc_full(b), (n_seg >> 1) & 1, abort_flag, P, kStatusTimeoutEpilogue);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t tacc = tmem_base + ((uint32_t)(quad * 32) << 16) + (b ? Cfg::ACC_COL1 : 0);
+            const bool partial = Cfg::STREAMK && sg.nseg > 1;
+            float* slot = nullptr;
+            if (partial) slot = P.ws_partial + ((size_t)sg.tile * P.ws_slots + sg.segidx) * (size_t)(BN * 128);
+            const int p = sg.p0 + prow;
+#pragma unroll 1
+            for (int ci = 0; ci < NCH; ++ci) {
+                // with overlapping accumulators the 32 shared columns are drained first
+                const int ch = Cfg::OVERLAP ? (b == 0 ? (ci + NCH - 1) % NCH : ci) : ci;
+                uint32_t v[CW];
+                if constexpr (CW == 32) tmem_ld_x32(tacc + ch * CW, reinterpret_cast<uint32_t(&)[32]>(v));
+                else tmem_ld_x16(tacc + ch * CW, reinterpret_cast<uint32_t(&)[16]>(v));
+                tmem_ld_wait();
+                if (Cfg::OVERLAP && ci == 0) { tc_fence_before(); mbar_arrive(bar_ovl); }
+                if (!Cfg::OVERLAP && ci == NCH - 1) { tc_fence_before(); mbar_arrive(bar_acc_empty(b)); }
+                const int qc = sg.q0 + ch * CW;              // first D column of this chunk
+                if (partial) {
+#pragma unroll
+                    for (int i = 0; i < CW; ++i) slot[(size_t)(ch * CW + i) * 128 + prow] = __uint_as_float(v[i]);
+                } else if (Cfg::SWAP) {
+                    // D[p,q] -> C[q,p]: consecutive lanes write consecutive bf16 of one C row
+                    if (p < P.c_cols) {
+#pragma unroll
+                        for (int i = 0; i < CW; ++i)
+                            if (qc + i < P.c_rows)
+                                P.c[(size_t)(qc + i) * P.ldc + p] = __float2bfloat16_rn(__uint_as_float(v[i]));
+                    }
+                } else {
+                    if (p < P.c_rows) {
+                        __nv_bfloat16* dst = P.c + (size_t)p * P.ldc + qc;
+                        const bool vec = ((P.ldc & 7) == 0) && ((reinterpret_cast<uintptr_t>(P.c) & 15) == 0);
+#pragma unroll
+                        for (int i = 0; i < CW; i += 8) {
+                            if (vec && qc + i + 8 <= P.c_cols) {
+                                uint4 o;
+                                o.x = pack_bf16x2(__uint_as_float(v[i + 0]), __uint_as_float(v[i + 1]));
+                                o.y = pack_bf16x2(__uint_as_float(v[i + 2]), __uint_as_float(v[i + 3]));
+                                o.z = pack_bf16x2(__uint_as_float(v[i + 4]), __uint_as_float(v[i + 5]));
+                                o.w = pack_bf16x2(__uint_as_float(v[i + 6]), __uint_as_float(v[i + 7]));
+                                *reinterpret_cast<uint4*>(dst + i) = o;
+                            } else {
+#pragma unroll
+                                for (int e = 0; e < 8; ++e)
+                                    if (qc + i + e < P.c_cols) dst[i + e] = __float2bfloat16_rn(__uint_as_float(v[i + e]));
+                            }
+                        }
+                    }
+                }
+            }
+            if (partial) {
+                // publish this CTA's partial; the contributor that arrives last adds all partials of the
+                // tile in slot order (a fixed order, so the result does not depend on timing)
+                __threadfence();
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (etid == 0) *ticket_slot = (int)atomicAdd(P.ws_counter + sg.tile, 1u);
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                const bool last = (*ticket_slot == sg.nseg - 1);
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (last) {
+                    __threadfence();
+                    const float* base = P.ws_partial + (size_t)sg.tile * P.ws_slots * (size_t)(BN * 128);
+                    for (int col = 0; col < BN; ++col) {
+                        float acc = 0.f;
+                        for (int sgi = 0; sgi < sg.nseg; ++sgi)
+                            acc += __ldcg(base + (size_t)sgi * (BN * 128) + (size_t)col * 128 + prow);
+                        const int q = sg.q0 + col;
+                        if (Cfg::SWAP) {
+                            if (p < P.c_cols && q < P.c_rows) P.c[(size_t)q * P.ldc + p] = __float2bfloat16_rn(acc);
+                        } else {
+                            if (p < P.c_rows && q < P.c_cols) P.c[(size_t)p * P.ldc + q] = __float2bfloat16_rn(acc);
+                        }
+                    }
+                    if (etid == 0) P.ws_counter[sg.tile] = 0u;
+                }
+            }
+            ++n_seg;
+        }
+    }
+
+    // ---- teardown: every role loop above terminates (bounded waits), so all warps arrive here
+    if (*abort_flag) {
+        // give copies and MMAs that are still in flight time to land before shared memory and TMEM go away
+        const long long t0 = clock64();
+        while (clock64() - t0 < 400000) { __nanosleep(1000); }
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    if (warp == 1) tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+}
+
+}  // namespace mxfp6

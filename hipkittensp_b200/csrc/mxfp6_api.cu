@@ -1,0 +1,494 @@
+// C ABI of the MX-FP6 GEMM path (see include/mxfp6.h): argument checks, tensor maps, kernel choice,
+// launches.  Plain pointers and sizes only; no torch types.
+#include "../../include/mxfp6.h"
+
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp6.h>
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <map>
+#include <mutex>
+#include <string>
+#include <tuple>
+
+#include "gemm_kernel.cuh"
+
+namespace mxfp6 {
+
+// ---------------------------------------------------------------------------------- errors
+static thread_local std::string g_err;
+static int fail(int code, const char* fmt, ...) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof buf, fmt, ap);
+    va_end(ap);
+    g_err = buf;
+    return code;
+}
+#define CUDA_TRY(expr)                                                                              \
+    do {                                                                                            \
+        cudaError_t e_ = (expr);                                                                    \
+        if (e_ != cudaSuccess) return fail(MXFP6_ERR_CUDA, "%s: %s", #expr, cudaGetErrorString(e_)); \
+    } while (0)
+
+// ---------------------------------------------------------------------------------- device state
+// Device-side status word written by kernels whose bounded waits run out.
+static __device__ int g_status_word[4];
+
+struct DeviceState {
+    bool init = false;
+    int sm_count = 0;
+    int cc_major = 0;
+    unsigned long long wait_cycles = 0;
+    int* status = nullptr;       // device address of g_status_word on this device
+    void* ws = nullptr;          // library-owned scratch for split tiles
+    size_t ws_bytes = 0;
+    std::map<const void*, bool> smem_attr_set;
+};
+static std::mutex g_mu;
+static DeviceState g_dev[64];
+
+static int env_int(const char* name, int dflt) {
+    const char* v = getenv(name);
+    return v ? atoi(v) : dflt;
+}
+
+static int get_device_state(DeviceState** out) {
+    int dev = 0;
+    CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return fail(MXFP6_ERR_BAD_ARG, "device index %d out of range", dev);
+    DeviceState& d = g_dev[dev];
+    if (!d.init) {
+        int khz = 0;
+        CUDA_TRY(cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, dev));
+        CUDA_TRY(cudaDeviceGetAttribute(&d.cc_major, cudaDevAttrComputeCapabilityMajor, dev));
+        CUDA_TRY(cudaDeviceGetAttribute(&khz, cudaDevAttrClockRate, dev));
+        if (d.cc_major != 10) return fail(MXFP6_ERR_UNSUPPORTED, "device %d is sm_%d0; this library is sm_100a only", dev, d.cc_major);
+        const int wait_ms = env_int("MXFP6_WAIT_MS", 2000);
+        d.wait_cycles = (unsigned long long)khz * (unsigned long long)wait_ms;
+        CUDA_TRY(cudaGetSymbolAddress((void**)&d.status, g_status_word));
+        CUDA_TRY(cudaMemset(d.status, 0, sizeof(int) * 4));
+        d.init = true;
+    }
+    *out = &d;
+    return MXFP6_OK;
+}
+
+// ---------------------------------------------------------------------------------- tensor maps
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn g_encode = nullptr;
+
+static int get_encode_fn() {
+    if (g_encode) return MXFP6_OK;
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    CUDA_TRY(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres));
+    if (!fn || qres != cudaDriverEntryPointSuccess) return fail(MXFP6_ERR_CUDA, "cuTensorMapEncodeTiled not available from the driver");
+    g_encode = (EncodeTiledFn)fn;
+    return MXFP6_OK;
+}
+
+struct MapKey {
+    const void* ptr; int64_t rows, inner; int box_rows, kind;
+    bool operator<(const MapKey& o) const {
+        return std::tie(ptr, rows, inner, box_rows, kind) < std::tie(o.ptr, o.rows, o.inner, o.box_rows, o.kind);
+    }
+};
+static std::map<MapKey, CUtensorMap> g_maps;
+
+// kind 0: packed 6-bit operand [rows, K] (inner = K elements), box 128 x box_rows, 128-byte swizzle
+// kind 1: scale bytes [rows, K/32] (inner = K/32 bytes), box 16 x box_rows, no swizzle
+static int make_map(const void* ptr, int64_t rows, int64_t inner, int box_rows, int kind, CUtensorMap* out) {
+    MapKey key{ptr, rows, inner, box_rows, kind};
+    {
+        std::lock_guard<std::mutex> lk(g_mu);
+        auto it = g_maps.find(key);
+        if (it != g_maps.end()) { *out = it->second; return MXFP6_OK; }
+    }
+    int rc = get_encode_fn();
+    if (rc) return rc;
+    cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)(kind == 0 ? inner * 3 / 4 : inner)};
+    cuuint32_t box[2] = {(cuuint32_t)(kind == 0 ? 128 : 16), (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = g_encode(out, kind == 0 ? CU_TENSOR_MAP_DATA_TYPE_16U6_ALIGN16B : CU_TENSOR_MAP_DATA_TYPE_UINT8, 2,
+                          const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          kind == 0 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                          CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        return fail(MXFP6_ERR_CUDA, "cuTensorMapEncodeTiled(kind=%d rows=%lld inner=%lld box_rows=%d) failed with %d",
+                    kind, (long long)rows, (long long)inner, box_rows, (int)r);
+    std::lock_guard<std::mutex> lk(g_mu);
+    if (g_maps.size() > 256) g_maps.clear();
+    g_maps[key] = *out;
+    return MXFP6_OK;
+}
+
+// ---------------------------------------------------------------------------------- GEMM dispatch
+struct Plan {
+    int bn; bool swap; bool streamk;
+    int grid;
+    int tiles_p, tiles_q;
+    int ws_slots;
+    size_t ws_counter_bytes, ws_bytes;
+};
+
+static int ceil_div(int64_t a, int64_t b) { return (int)((a + b - 1) / b); }
+
+static Plan make_plan(int64_t M, int64_t N, int64_t K, int sm_count) {
+    Plan p{};
+    const int kb = (int)(K / 128);
+    const char* force = getenv("MXFP6_FORCE_CFG");   // "bn,swap,streamk", for tests
+    int fbn = 0, fswap = -1, fsk = -1;
+    if (force) sscanf(force, "%d,%d,%d", &fbn, &fswap, &fsk);
+    if (M <= 128 && N > M) {
+        p.swap = true; p.streamk = true;
+        p.bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : 128;
+    } else {
+        p.swap = false; p.streamk = false;
+        const int64_t t256 = (int64_t)ceil_div(M, 128) * ceil_div(N, 256);
+        p.bn = (N >= 256 && t256 >= sm_count) ? 256 : 128;
+    }
+    if (fbn) p.bn = fbn;
+    if (fswap >= 0) p.swap = fswap != 0;
+    if (fsk >= 0) p.streamk = fsk != 0;
+    const int64_t prow = p.swap ? N : M, qrow = p.swap ? M : N;
+    p.tiles_p = ceil_div(prow, 128);
+    p.tiles_q = ceil_div(qrow, p.bn);
+    const int64_t tiles = (int64_t)p.tiles_p * p.tiles_q;
+    if (p.streamk) {
+        const int64_t U = tiles * kb;
+        int64_t g = U / 4; if (g < 1) g = 1;
+        p.grid = (int)(g < sm_count ? g : sm_count);
+        const int64_t chunk = U / p.grid;           // smallest number of K-blocks a CTA gets (>= 1)
+        int64_t maxseg = (kb + chunk - 1) / chunk + 1;
+        if (maxseg > p.grid) maxseg = p.grid;
+        p.ws_slots = (int)maxseg;
+        p.ws_counter_bytes = (size_t)((tiles * 4 + 255) / 256 * 256);
+        p.ws_bytes = p.ws_counter_bytes + (size_t)tiles * maxseg * (size_t)p.bn * 128 * 4;
+    } else {
+        p.grid = (int)(tiles < sm_count ? tiles : sm_count);
+        p.ws_slots = 0; p.ws_counter_bytes = 0; p.ws_bytes = 0;
+    }
+    return p;
+}
+
+template <class Cfg>
+static int launch_cfg(DeviceState& d, const Plan& pl, const CUtensorMap& tp, const CUtensorMap& tq,
+                      const CUtensorMap& tsp, const CUtensorMap& tsq, const GemmParams& P, cudaStream_t st) {
+    auto kern = mxfp6_gemm_kernel<Cfg>;
+    {
+        std::lock_guard<std::mutex> lk(g_mu);
+        if (!d.smem_attr_set[(const void*)kern]) {
+            CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_ALLOC));
+            d.smem_attr_set[(const void*)kern] = true;
+        }
+    }
+    kern<<<pl.grid, Cfg::THREADS, Cfg::SMEM_ALLOC, st>>>(tp, tq, tsp, tsq, P);
+    CUDA_TRY(cudaGetLastError());
+    return MXFP6_OK;
+}
+
+static int gemm_impl(const void* a, const void* sfa, const void* b, const void* sfb, void* c, int64_t M, int64_t N,
+                     int64_t K, int fmt_a, int fmt_b, void* ws, size_t ws_bytes, bool own_ws, void* stream) {
+    if (M < 0 || N < 0 || K < 0) return fail(MXFP6_ERR_BAD_ARG, "negative dimension (M=%lld N=%lld K=%lld)", (long long)M, (long long)N, (long long)K);
+    if (K % 128 != 0) return fail(MXFP6_ERR_BAD_ARG, "K=%lld must be a multiple of 128", (long long)K);
+    if ((fmt_a != MXFP6_E2M3 && fmt_a != MXFP6_E3M2) || (fmt_b != MXFP6_E2M3 && fmt_b != MXFP6_E3M2))
+        return fail(MXFP6_ERR_BAD_ARG, "format must be MXFP6_E2M3 (0) or MXFP6_E3M2 (1)");
+    if (M > 0x7fffff00LL || N > 0x7fffff00LL || K > 0x7fffff00LL) return fail(MXFP6_ERR_BAD_ARG, "dimension too large");
+    if (M == 0 || N == 0) return MXFP6_OK;
+    if (!c) return fail(MXFP6_ERR_BAD_ARG, "null C");
+    cudaStream_t st = (cudaStream_t)stream;
+    if (K == 0) { CUDA_TRY(cudaMemsetAsync(c, 0, (size_t)M * N * 2, st)); return MXFP6_OK; }
+    if (!a || !b || !sfa || !sfb) return fail(MXFP6_ERR_BAD_ARG, "null operand pointer");
+    if (((uintptr_t)a & 31) || ((uintptr_t)b & 31)) return fail(MXFP6_ERR_BAD_ARG, "packed operands must be 32-byte aligned");
+    if (((uintptr_t)sfa & 3) || ((uintptr_t)sfb & 3)) return fail(MXFP6_ERR_BAD_ARG, "scale arrays must be 4-byte aligned");
+    if ((uintptr_t)c & 1) return fail(MXFP6_ERR_BAD_ARG, "C must be 2-byte aligned");
+
+    DeviceState* dp = nullptr;
+    int rc = get_device_state(&dp);
+    if (rc) return rc;
+    DeviceState& d = *dp;
+    Plan pl = make_plan(M, N, K, d.sm_count);
+
+    if (pl.ws_bytes) {
+        if (own_ws) {
+            std::lock_guard<std::mutex> lk(g_mu);
+            if (d.ws_bytes < pl.ws_bytes) {
+                if (d.ws) { CUDA_TRY(cudaDeviceSynchronize()); CUDA_TRY(cudaFree(d.ws)); d.ws = nullptr; d.ws_bytes = 0; }
+                size_t want = pl.ws_bytes < (size_t)(8u << 20) ? (size_t)(8u << 20) : pl.ws_bytes;
+                CUDA_TRY(cudaMalloc(&d.ws, want));
+                CUDA_TRY(cudaMemset(d.ws, 0, want));
+                d.ws_bytes = want;
+            }
+            ws = d.ws;
+        } else {
+            if (!ws || ws_bytes < pl.ws_bytes) return fail(MXFP6_ERR_BAD_ARG, "workspace too small: need %zu bytes, got %zu", pl.ws_bytes, ws_bytes);
+            if ((uintptr_t)ws & 255) return fail(MXFP6_ERR_BAD_ARG, "workspace must be 256-byte aligned");
+        }
+    }
+
+    const void* pp = pl.swap ? b : a; const void* qp = pl.swap ? a : b;
+    const void* sp = pl.swap ? sfb : sfa; const void* sq = pl.swap ? sfa : sfb;
+    const int64_t prow = pl.swap ? N : M, qrow = pl.swap ? M : N;
+    const int fp = pl.swap ? fmt_b : fmt_a, fq = pl.swap ? fmt_a : fmt_b;
+
+    CUtensorMap tp, tq, tsp, tsq;
+    if ((rc = make_map(pp, prow, K, 128, 0, &tp))) return rc;
+    if ((rc = make_map(qp, qrow, K, pl.bn, 0, &tq))) return rc;
+    const bool sf_tma = ((K / 32) % 16 == 0) && !((uintptr_t)sp & 15) && !((uintptr_t)sq & 15) && !env_int("MXFP6_NO_SF_TMA", 0);
+    if (sf_tma) {
+        if ((rc = make_map(sp, prow, K / 32, 128, 1, &tsp))) return rc;
+        if ((rc = make_map(sq, qrow, K / 32, pl.bn, 1, &tsq))) return rc;
+    } else {
+        tsp = tp; tsq = tq;   // unused by the kernel in this mode
+    }
+
+    GemmParams P{};
+    P.p_rows = (int)prow; P.q_rows = (int)qrow;
+    P.kblocks = (int)(K / 128);
+    P.tiles_p = pl.tiles_p; P.tiles_q = pl.tiles_q;
+    P.ldc = (int)N; P.c_rows = (int)M; P.c_cols = (int)N;
+    P.idesc = make_idesc(fp == MXFP6_E2M3 ? kFmtE2M3 : kFmtE3M2, fq == MXFP6_E2M3 ? kFmtE2M3 : kFmtE3M2, (uint32_t)pl.bn);
+    P.sf_tma = sf_tma ? 1 : 0;
+    P.sf_ld = (int)(K / 32);
+    P.stage_tx_bytes = (128 + pl.bn) * env_int("MXFP6_TX_BYTES_PER_ROW", 128);
+    P.sfp = (const uint8_t*)sp; P.sfq = (const uint8_t*)sq;
+    P.c = (__nv_bfloat16*)c;
+    P.ws_counter = (unsigned int*)ws;
+    P.ws_partial = ws ? (float*)((uint8_t*)ws + pl.ws_counter_bytes) : nullptr;
+    P.ws_slots = pl.ws_slots;
+    P.status = d.status;
+    P.wait_cycles = d.wait_cycles;
+
+#define MXFP6_CASE(BN_, SWAP_, SK_)                                                              \
+    if (pl.bn == BN_ && pl.swap == SWAP_ && pl.streamk == SK_)                                   \
+        return launch_cfg<GemmCfg<BN_, SWAP_, SK_>>(d, pl, tp, tq, tsp, tsq, P, st);
+    MXFP6_CASE(256, false, false)
+    MXFP6_CASE(128, false, false)
+    MXFP6_CASE(256, false, true)
+    MXFP6_CASE(128, false, true)
+    MXFP6_CASE(16, true, true)
+    MXFP6_CASE(32, true, true)
+    MXFP6_CASE(64, true, true)
+    MXFP6_CASE(128, true, true)
+#undef MXFP6_CASE
+    return fail(MXFP6_ERR_BAD_ARG, "no kernel for bn=%d swap=%d streamk=%d", pl.bn, (int)pl.swap, (int)pl.streamk);
+}
+
+// ---------------------------------------------------------------------------------- quantise / dequantise
+template <typename T> __device__ __forceinline__ void load4(const T* p, float (&x)[4]);
+template <> __device__ __forceinline__ void load4<float>(const float* p, float (&x)[4]) {
+    float4 v = *reinterpret_cast<const float4*>(p);
+    x[0] = v.x; x[1] = v.y; x[2] = v.z; x[3] = v.w;
+}
+template <> __device__ __forceinline__ void load4<__nv_bfloat16>(const __nv_bfloat16* p, float (&x)[4]) {
+    uint2 v = *reinterpret_cast<const uint2*>(p);
+    x[0] = __uint_as_float(v.x << 16); x[1] = __uint_as_float(v.x & 0xffff0000u);
+    x[2] = __uint_as_float(v.y << 16); x[3] = __uint_as_float(v.y & 0xffff0000u);
+}
+
+// One thread per 4 consecutive elements; 8 adjacent lanes share a 32-element block.
+template <typename T, int FMT>
+__global__ void __launch_bounds__(256) quantize_kernel(const T* __restrict__ src, int64_t n_quads, uint32_t* __restrict__ packed_words,
+                                                       uint8_t* __restrict__ scales) {
+    constexpr int EMAX = FMT == MXFP6_E2M3 ? 2 : 4;
+    const int lane = threadIdx.x & 31;
+    // n_quads is a multiple of 8, so whole warps share the loop trip count up to the tail handled by `live`
+    for (int64_t q0 = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) & ~31LL; q0 < n_quads; q0 += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t q = q0 + lane;
+        const bool live = q < n_quads;
+        float x[4] = {0.f, 0.f, 0.f, 0.f};
+        if (live) load4<T>(src + q * 4, x);
+        float amax = fmaxf(fmaxf(fabsf(x[0]), fabsf(x[1])), fmaxf(fabsf(x[2]), fabsf(x[3])));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
+        // floor(log2(amax)) from the exponent field (fp32 subnormals: from the leading mantissa bit)
+        const uint32_t u = __float_as_uint(amax);
+        int fl = (int)((u >> 23) & 0xff) - 127;
+        if (((u >> 23) & 0xff) == 0) fl = 31 - __clz(u & 0x7fffff) - 149;
+        int sb = fl - EMAX + 127;
+        sb = sb < 0 ? 0 : sb > 254 ? 254 : sb;
+        if (!(amax > 0.f)) sb = 0;
+        if (isinf(amax)) sb = 254;
+        const int e = sb - 127;
+        const int h = (-e) / 2;
+        const float f1 = __uint_as_float((uint32_t)(h + 127) << 23), f2 = __uint_as_float((uint32_t)(-e - h + 127) << 23);
+        uint32_t w = 0;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const uint32_t code = __nv_cvt_float_to_fp6(x[i] * f1 * f2, FMT == MXFP6_E2M3 ? __NV_E2M3 : __NV_E3M2, cudaRoundNearest) & 63u;
+            w |= code << (6 * i);
+        }
+        // 4 lanes hold 4 x 24 bits = three 32-bit words of the packed stream
+        const uint32_t wn = __shfl_down_sync(0xffffffffu, w, 1);
+        const int i4 = lane & 3;
+        if (live && i4 < 3) packed_words[(q >> 2) * 3 + i4] = (w >> (8 * i4)) | (wn << (24 - 8 * i4));
+        if (live && (lane & 7) == 0) scales[q >> 3] = (uint8_t)sb;
+    }
+}
+
+template <int FMT>
+__global__ void __launch_bounds__(256) dequantize_kernel(const uint8_t* __restrict__ packed, const uint8_t* __restrict__ scales,
+                                                         int64_t n_quads, float* __restrict__ out) {
+    constexpr int MB = FMT == MXFP6_E2M3 ? 3 : 2;
+    constexpr int BIAS = FMT == MXFP6_E2M3 ? 1 : 3;
+    for (int64_t q = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; q < n_quads; q += (int64_t)gridDim.x * blockDim.x) {
+        const uint8_t* p = packed + q * 3;
+        const uint32_t w = (uint32_t)p[0] | ((uint32_t)p[1] << 8) | ((uint32_t)p[2] << 16);
+        const uint32_t sbyte = scales[q >> 3];
+        // 2^(sbyte-127) as fp32 (sbyte 0 -> 2^-127, an fp32 subnormal)
+        const float s = sbyte == 255 ? __uint_as_float(0x7fc00000u) : sbyte == 0 ? __uint_as_float(0x00400000u) : __uint_as_float(sbyte << 23);
+        float4 o;
+        float* of = reinterpret_cast<float*>(&o);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const uint32_t c = (w >> (6 * i)) & 63u;
+            const uint32_t e = (c >> MB) & ((1u << (5 - MB)) - 1), m = c & ((1u << MB) - 1);
+            float mag = e ? __uint_as_float(((e - BIAS + 127) << 23) | (m << (23 - MB)))
+                          : (float)m * __uint_as_float((uint32_t)(1 - BIAS - MB + 127) << 23);
+            of[i] = ((c >> 5) ? -mag : mag) * s;
+        }
+        *reinterpret_cast<float4*>(out + q * 4) = o;
+    }
+}
+
+// ---------------------------------------------------------------------------------- diagnostics
+__global__ void tma_dump_kernel(const __grid_constant__ CUtensorMap tm, int x, int y, uint32_t tx_bytes,
+                                unsigned long long wait_cycles, uint8_t* out, int* status) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* gen = smem_raw + (base - smem_u32(smem_raw));
+    const uint32_t bar = base + 16384;
+    for (int i = threadIdx.x; i < 16384 / 4; i += blockDim.x) reinterpret_cast<uint32_t*>(gen)[i] = 0xEEEEEEEEu;
+    if (threadIdx.x == 0) { mbar_init(bar, 1); fence_barrier_init(); }
+    fence_proxy_async_smem();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        mbar_arrive_expect_tx(bar, tx_bytes);
+        tma_load_2d(base, &tm, bar, x, y);
+        const long long t0 = clock64();
+        bool done = false;
+        while (!(done = mbar_try_wait(bar, 0))) {
+            if ((unsigned long long)(clock64() - t0) > wait_cycles) break;
+        }
+        if (!done) atomicCAS(status, 0, 0x7f);
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < 16384; i += blockDim.x) out[i] = gen[i];
+}
+
+}  // namespace mxfp6
+
+// ====================================================================================== C ABI
+using namespace mxfp6;
+
+extern "C" int mxfp6_version(void) { return 100; }
+
+extern "C" const char* mxfp6_last_error(void) { return g_err.c_str(); }
+
+extern "C" int mxfp6_gemm(const void* a, const void* sfa, const void* b, const void* sfb, void* c, int64_t M, int64_t N,
+                          int64_t K, int fmt_a, int fmt_b, void* stream) {
+    return gemm_impl(a, sfa, b, sfb, c, M, N, K, fmt_a, fmt_b, nullptr, 0, true, stream);
+}
+
+extern "C" size_t mxfp6_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K) {
+    if (M <= 0 || N <= 0 || K <= 0 || K % 128) return 0;
+    DeviceState* d = nullptr;
+    if (get_device_state(&d)) return 0;
+    return make_plan(M, N, K, d->sm_count).ws_bytes;
+}
+
+extern "C" int mxfp6_gemm_ws(const void* a, const void* sfa, const void* b, const void* sfb, void* c, int64_t M, int64_t N,
+                             int64_t K, int fmt_a, int fmt_b, void* workspace, size_t workspace_bytes, void* stream) {
+    return gemm_impl(a, sfa, b, sfb, c, M, N, K, fmt_a, fmt_b, workspace, workspace_bytes, false, stream);
+}
+
+extern "C" int mxfp6_quantize(const void* src, int src_dtype, int64_t rows, int64_t K, int fmt, void* packed, void* scales,
+                              void* stream) {
+    if (rows < 0 || K < 0 || K % 32) return fail(MXFP6_ERR_BAD_ARG, "quantize: rows=%lld K=%lld (K must be a multiple of 32)", (long long)rows, (long long)K);
+    if (fmt != MXFP6_E2M3 && fmt != MXFP6_E3M2) return fail(MXFP6_ERR_BAD_ARG, "quantize: bad format %d", fmt);
+    if (src_dtype != 0 && src_dtype != 1) return fail(MXFP6_ERR_BAD_ARG, "quantize: src_dtype must be 0 (fp32) or 1 (bf16)");
+    if (rows == 0 || K == 0) return MXFP6_OK;
+    if (!src || !packed || !scales) return fail(MXFP6_ERR_BAD_ARG, "quantize: null pointer");
+    if (((uintptr_t)src & (src_dtype == 0 ? 15 : 7)) || ((uintptr_t)packed & 3)) return fail(MXFP6_ERR_BAD_ARG, "quantize: misaligned pointer");
+    DeviceState* d = nullptr;
+    int rc = get_device_state(&d);
+    if (rc) return rc;
+    const int64_t nq = rows * K / 4;
+    int64_t blocks = (nq + 255) / 256;
+    const int64_t cap = (int64_t)d->sm_count * 16;
+    if (blocks > cap) blocks = cap;
+    cudaStream_t st = (cudaStream_t)stream;
+#define QK(T, F) quantize_kernel<T, F><<<(unsigned)blocks, 256, 0, st>>>((const T*)src, nq, (uint32_t*)packed, (uint8_t*)scales)
+    if (src_dtype == 0) { if (fmt == MXFP6_E2M3) QK(float, MXFP6_E2M3); else QK(float, MXFP6_E3M2); }
+    else { if (fmt == MXFP6_E2M3) QK(__nv_bfloat16, MXFP6_E2M3); else QK(__nv_bfloat16, MXFP6_E3M2); }
+#undef QK
+    CUDA_TRY(cudaGetLastError());
+    return MXFP6_OK;
+}
+
+extern "C" int mxfp6_dequantize(const void* packed, const void* scales, int64_t rows, int64_t K, int fmt, void* out_f32,
+                                void* stream) {
+    if (rows < 0 || K < 0 || K % 32) return fail(MXFP6_ERR_BAD_ARG, "dequantize: rows=%lld K=%lld (K must be a multiple of 32)", (long long)rows, (long long)K);
+    if (fmt != MXFP6_E2M3 && fmt != MXFP6_E3M2) return fail(MXFP6_ERR_BAD_ARG, "dequantize: bad format %d", fmt);
+    if (rows == 0 || K == 0) return MXFP6_OK;
+    if (!packed || !scales || !out_f32) return fail(MXFP6_ERR_BAD_ARG, "dequantize: null pointer");
+    if ((uintptr_t)out_f32 & 15) return fail(MXFP6_ERR_BAD_ARG, "dequantize: output must be 16-byte aligned");
+    DeviceState* d = nullptr;
+    int rc = get_device_state(&d);
+    if (rc) return rc;
+    const int64_t nq = rows * K / 4;
+    int64_t blocks = (nq + 255) / 256;
+    const int64_t cap = (int64_t)d->sm_count * 16;
+    if (blocks > cap) blocks = cap;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (fmt == MXFP6_E2M3) dequantize_kernel<MXFP6_E2M3><<<(unsigned)blocks, 256, 0, st>>>((const uint8_t*)packed, (const uint8_t*)scales, nq, (float*)out_f32);
+    else dequantize_kernel<MXFP6_E3M2><<<(unsigned)blocks, 256, 0, st>>>((const uint8_t*)packed, (const uint8_t*)scales, nq, (float*)out_f32);
+    CUDA_TRY(cudaGetLastError());
+    return MXFP6_OK;
+}
+
+extern "C" int mxfp6_device_status(int* status_out) {
+    DeviceState* d = nullptr;
+    int rc = get_device_state(&d);
+    if (rc) return rc;
+    CUDA_TRY(cudaDeviceSynchronize());
+    int h[4] = {0, 0, 0, 0};
+    CUDA_TRY(cudaMemcpy(h, d->status, sizeof h, cudaMemcpyDeviceToHost));
+    if (status_out) *status_out = h[0];
+    if (h[0] != 0) {
+        CUDA_TRY(cudaMemset(d->status, 0, sizeof h));
+        // arrival counters of split tiles may be left non-zero by an aborted launch
+        std::lock_guard<std::mutex> lk(g_mu);
+        if (d->ws) CUDA_TRY(cudaMemset(d->ws, 0, d->ws_bytes));
+        return fail(MXFP6_ERR_DEVICE_WAIT, "a bounded wait ran out on the device: role %d, CTA %d", h[0] & 0xff, h[0] >> 8);
+    }
+    return MXFP6_OK;
+}
+
+extern "C" int mxfp6_debug_tma_dump(const void* packed, int64_t rows, int64_t K, int64_t row0, int64_t k0, void* out16k,
+                                    void* stream) {
+    if (!packed || !out16k || K <= 0 || K % 128 || k0 % 128 || rows <= 0) return fail(MXFP6_ERR_BAD_ARG, "tma_dump: bad argument");
+    if ((uintptr_t)packed & 31) return fail(MXFP6_ERR_BAD_ARG, "tma_dump: operand must be 32-byte aligned");
+    DeviceState* d = nullptr;
+    int rc = get_device_state(&d);
+    if (rc) return rc;
+    CUtensorMap tm;
+    if ((rc = make_map(packed, rows, K, 128, 0, &tm))) return rc;
+    static bool attr = false;
+    if (!attr) { CUDA_TRY(cudaFuncSetAttribute(tma_dump_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 16384 + 2048)); attr = true; }
+    const uint32_t tx = 128u * (uint32_t)env_int("MXFP6_TX_BYTES_PER_ROW", 128);
+    tma_dump_kernel<<<1, 128, 16384 + 2048, (cudaStream_t)stream>>>(tm, (int)k0, (int)row0, tx, d->wait_cycles / 20, (uint8_t*)out16k, d->status);
+    CUDA_TRY(cudaGetLastError());
+    return MXFP6_OK;
+}

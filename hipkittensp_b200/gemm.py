@@ -1,0 +1,118 @@
+"""Host-side mirror of the reference's operator for the MX-FP6 GEMM path.
+
+`dispatch_micro(A, B, C, scale_A, scale_B, fmt)` keeps the reference's calling convention
+(kernels/gemm/bf16fp32/bench.py:34: positional tensors, output written in place, returns None;
+scale tensors after C as in kernels/torch_scaled/scaled_matmul.cu:17-18) and its tensor-acceptance
+errors (include/pyutils/pyutils.cuh:18-44), and forwards to the C ABI on torch's current stream.
+torch is used for device memory and streams only.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _lib
+from ._lib import E2M3, E3M2, check, lib
+
+
+def _accept(t, name: str, dtype) -> None:
+    if not isinstance(t, torch.Tensor):
+        raise RuntimeError("Expected a torch.Tensor")
+    if not t.is_contiguous():
+        raise RuntimeError("Tensor must be contiguous")
+    if t.device.type == "cpu":
+        raise RuntimeError("Tensor must be on CUDA device")
+    if t.dim() > 4:
+        raise RuntimeError("Expected Tensor.ndim <= 4")
+    if t.dtype != dtype:
+        raise RuntimeError(f"{name} must be {dtype}, got {t.dtype}")
+    if t.dim() != 2:
+        raise RuntimeError(f"{name} must be 2-D")
+
+
+def _stream_ptr() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def dispatch_micro(A, B, C, scale_A, scale_B, fmt: int = E2M3, fmt_b: int | None = None) -> None:
+    """C[M,N] (bf16, in place) = A[M,K] @ B[N,K]^T.
+
+    A [M,3K/4] u8 and B [N,3K/4] u8 are packed fp6 (format `fmt`; `fmt_b` if B differs),
+    scale_A [M,K/32] u8 and scale_B [N,K/32] u8 are E8M0 bytes.  M is taken from A, N from C,
+    K from A, as the reference does (256_256_64_32_with16x32.cpp:52-54)."""
+    _accept(A, "A", torch.uint8)
+    _accept(B, "B", torch.uint8)
+    _accept(C, "C", torch.bfloat16)
+    _accept(scale_A, "scale_A", torch.uint8)
+    _accept(scale_B, "scale_B", torch.uint8)
+    M, N = A.shape[0], C.shape[1]
+    if A.shape[1] % 3:
+        raise RuntimeError("A.shape[1] must be 3K/4 bytes")
+    K = A.shape[1] // 3 * 4
+    if K % 128:
+        raise RuntimeError("K must be a multiple of 128")
+    if C.shape[0] != M:
+        raise RuntimeError("C.shape[0] must equal A.shape[0]")
+    if tuple(B.shape) != (N, A.shape[1]):
+        raise RuntimeError("B must be [N, 3K/4]")
+    if tuple(scale_A.shape) != (M, K // 32) or tuple(scale_B.shape) != (N, K // 32):
+        raise RuntimeError("scales must be [rows, K/32]")
+    if len({t.device for t in (A, B, C, scale_A, scale_B)}) != 1:
+        raise RuntimeError("all tensors must be on the same device")
+    with torch.cuda.device(A.device):
+        check(lib.mxfp6_gemm(A.data_ptr(), scale_A.data_ptr(), B.data_ptr(), scale_B.data_ptr(), C.data_ptr(),
+                             M, N, K, fmt, fmt if fmt_b is None else fmt_b, _stream_ptr()))
+
+
+def gemm(A, scale_A, B, scale_B, fmt: int = E2M3, fmt_b: int | None = None, out=None):
+    """Allocating convenience wrapper around dispatch_micro; returns C."""
+    M, N = A.shape[0], B.shape[0]
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.bfloat16, device=A.device)
+    dispatch_micro(A, B, out, scale_A, scale_B, fmt, fmt_b)
+    return out
+
+
+def quantize(x: torch.Tensor, fmt: int = E2M3):
+    """fp32 or bf16 [rows,K] on the GPU -> (packed u8 [rows,3K/4], scales u8 [rows,K/32])."""
+    if x.device.type == "cpu":
+        raise RuntimeError("Tensor must be on CUDA device")
+    if x.dtype not in (torch.float32, torch.bfloat16) or x.dim() != 2 or not x.is_contiguous():
+        raise RuntimeError("quantize expects a contiguous 2-D fp32 or bf16 tensor")
+    rows, K = x.shape
+    if K % 32:
+        raise RuntimeError("K must be a multiple of 32")
+    packed = torch.empty((rows, K * 3 // 4), dtype=torch.uint8, device=x.device)
+    scales = torch.empty((rows, K // 32), dtype=torch.uint8, device=x.device)
+    with torch.cuda.device(x.device):
+        check(lib.mxfp6_quantize(x.data_ptr(), 0 if x.dtype == torch.float32 else 1, rows, K, fmt,
+                                 packed.data_ptr(), scales.data_ptr(), _stream_ptr()))
+    return packed, scales
+
+
+def dequantize(packed: torch.Tensor, scales: torch.Tensor, fmt: int = E2M3) -> torch.Tensor:
+    """(packed, scales) on the GPU -> fp32 [rows,K]."""
+    _accept(packed, "packed", torch.uint8)
+    _accept(scales, "scales", torch.uint8)
+    rows, K = packed.shape[0], packed.shape[1] // 3 * 4
+    out = torch.empty((rows, K), dtype=torch.float32, device=packed.device)
+    with torch.cuda.device(packed.device):
+        check(lib.mxfp6_dequantize(packed.data_ptr(), scales.data_ptr(), rows, K, fmt, out.data_ptr(), _stream_ptr()))
+    return out
+
+
+def device_status() -> int:
+    """Synchronise and return the device status word (0 = ok); raises if a kernel wait ran out."""
+    import ctypes
+
+    st = ctypes.c_int(0)
+    check(lib.mxfp6_device_status(ctypes.byref(st)))
+    return st.value
+
+
+def tma_dump(packed: torch.Tensor, row0: int = 0, k0: int = 0) -> torch.Tensor:
+    """Diagnostic: the 16 KiB shared-memory image of one 128x128 operand box as the GEMM loads it."""
+    rows, K = packed.shape[0], packed.shape[1] // 3 * 4
+    out = torch.empty(16384, dtype=torch.uint8, device=packed.device)
+    with torch.cuda.device(packed.device):
+        check(lib.mxfp6_debug_tma_dump(packed.data_ptr(), rows, K, row0, k0, out.data_ptr(), _stream_ptr()))
+    return out

@@ -1,0 +1,106 @@
+/*
+ * mxfp6.h -- C ABI of the B200 (sm_100a) MX-FP6 GEMM path.
+ *
+ *   C[M,N] (bf16) = A[M,K] * B[N,K]^T
+ *
+ * A and B are packed MX-FP6: 6-bit codes (E2M3 or E3M2), four values per three bytes, dense
+ * little-endian along K (element i of a row occupies bits [6i, 6i+6) of the row's byte string,
+ * row stride 3K/4 bytes), with one E8M0 scale byte (value 2^(x-127)) per 32 elements along K,
+ * row-major [rows, K/32].  Accumulation is fp32, the output is rounded once to bf16 (RNE).
+ *
+ * Conventions shared by every entry point
+ *   - all pointers are DEVICE pointers unless a comment says otherwise; the caller owns every
+ *     buffer, the library keeps no pointer after a call returns;
+ *   - `stream` is a cudaStream_t passed as void* (NULL = the legacy default stream); calls are
+ *     asynchronous on that stream and do not synchronise;
+ *   - the return value is 0 on success, a MXFP6_ERR_* code otherwise; mxfp6_last_error() gives
+ *     the message of the calling thread's last failure;
+ *   - preconditions: K % 128 == 0; packed operand pointers 32-byte aligned; C 2-byte aligned
+ *     (16-byte aligned C with N % 8 == 0 takes the vector store path); M, N >= 0.
+ *
+ * Each declaration names the interface of the reference (benenzhu/HipKittensP) it stands in for.
+ */
+#ifndef MXFP6_H_
+#define MXFP6_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MXFP6_E2M3 0
+#define MXFP6_E3M2 1
+
+#define MXFP6_OK 0
+#define MXFP6_ERR_BAD_ARG 1      /* shape / alignment / format / null pointer */
+#define MXFP6_ERR_CUDA 2         /* a CUDA runtime or driver call failed */
+#define MXFP6_ERR_DEVICE_WAIT 3  /* a bounded wait inside a kernel ran out (see mxfp6_device_status) */
+#define MXFP6_ERR_UNSUPPORTED 4  /* not an sm_100 device */
+
+/* Library version, major*10000 + minor*100 + patch.  (No counterpart in the reference.) */
+int mxfp6_version(void);
+
+/* Message of the calling thread's last failing call ("" if none).  Stands in for the reference's
+ * CHECK_CUDA_ERROR printing (include/pyutils/util.cuh:7-19), as a queryable string. */
+const char* mxfp6_last_error(void);
+
+/*
+ * The GEMM.  Replaces the launch made by dispatch_micro(micro_globals)
+ * (kernels/gemm/bf16fp32/256_256_64_32_with16x32.cpp:383-387) with the operand set of
+ * micro_globals (:47-58) extended by the two scale tensors in the argument order of the
+ * reference's scale-taking kernel (kernels/torch_scaled/scaled_matmul.cu:17-18).
+ *   a   [M, 3K/4] u8   sfa [M, K/32] u8    fmt_a MXFP6_E2M3 | MXFP6_E3M2
+ *   b   [N, 3K/4] u8   sfb [N, K/32] u8    fmt_b likewise
+ *   c   [M, N] bf16, written in place
+ * Shapes that split output tiles along K use a per-device scratch buffer that the library
+ * allocates on first need (cudaMalloc) and keeps; concurrent calls on different streams of one
+ * device must use mxfp6_gemm_ws with their own scratch instead.
+ */
+int mxfp6_gemm(const void* a, const void* sfa, const void* b, const void* sfb, void* c,
+               int64_t M, int64_t N, int64_t K, int fmt_a, int fmt_b, void* stream);
+
+/* Scratch bytes mxfp6_gemm_ws needs for this shape on the current device (0 if none). */
+size_t mxfp6_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K);
+
+/* Same as mxfp6_gemm with caller-provided scratch (256-byte aligned, zero-filled once before its
+ * first use; the kernel leaves it zeroed where it must be).  (No counterpart in the reference,
+ * which never splits tiles.) */
+int mxfp6_gemm_ws(const void* a, const void* sfa, const void* b, const void* sfb, void* c,
+                  int64_t M, int64_t N, int64_t K, int fmt_a, int fmt_b,
+                  void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * Block quantiser: src [rows, K] (src_dtype 0 = fp32, 1 = bf16), K % 32 == 0  ->
+ * packed [rows, 3K/4] + scales [rows, K/32].  Scale exponent = floor(log2(amax)) - 2 (E2M3) or - 4
+ * (E3M2), elements rounded to nearest even and saturated.  The step in front of the GEMM; the
+ * reference's fp8 harness does it on the host (kernels/gemm/fp8fp32/FP8_8wave/8_wave.cu:258-268).
+ */
+int mxfp6_quantize(const void* src, int src_dtype, int64_t rows, int64_t K, int fmt,
+                   void* packed, void* scales, void* stream);
+
+/* Inverse, to fp32 [rows, K]: decode(code) * 2^(scale-127).  Test aid. */
+int mxfp6_dequantize(const void* packed, const void* scales, int64_t rows, int64_t K, int fmt,
+                     void* out_f32, void* stream);
+
+/*
+ * Synchronises the current device and reports the device-side status word of the kernels launched
+ * so far (0 = ok; otherwise low byte = role whose wait ran out, upper bits = CTA index), then clears
+ * it.  Returns MXFP6_ERR_DEVICE_WAIT if it was non-zero.  The reference ignores launch status
+ * (256_256_64_32_with16x32.cpp:385 leaves `ret` unused); this is the checked alternative.
+ */
+int mxfp6_device_status(int* status_out);
+
+/*
+ * Diagnostic: TMA-loads one 128-row x 128-element box of a packed operand (rows row0.., elements
+ * k0..k0+127, k0 % 128 == 0) exactly as the GEMM does and copies the 16 KiB of shared memory it
+ * produced to out16k (device).  Used by the tests to pin the shared-memory image of the 6-bit type.
+ */
+int mxfp6_debug_tma_dump(const void* packed, int64_t rows, int64_t K, int64_t row0, int64_t k0,
+                         void* out16k, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MXFP6_H_ */

@@ -1,0 +1,77 @@
+"""CPU-only checks of the boundary: the shared library loads, exports every symbol the header declares,
+and rejects bad arguments before touching the GPU."""
+import ctypes
+import os
+import re
+
+import pytest
+
+import hipkittensp_b200 as hk
+from hipkittensp_b200 import _lib
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _header_symbols():
+    src = open(os.path.join(ROOT, "include", "mxfp6.h")).read()
+    src = re.sub(r"/\*.*?\*/", "", src, flags=re.S)
+    return sorted(set(re.findall(r"\b(mxfp6_[a-z0-9_]+)\s*\(", src)))
+
+
+def test_library_exports_every_declared_symbol():
+    declared = _header_symbols()
+    assert declared, "no declarations found in include/mxfp6.h"
+    raw = ctypes.CDLL(_lib.LIB_PATH)
+    for name in declared:
+        assert hasattr(raw, name), f"{name} is declared in mxfp6.h but not exported by libmxfp6.so"
+    assert set(declared) == set(_lib.SYMBOLS)
+
+
+def test_version_and_error_string():
+    assert hk.lib.mxfp6_version() >= 100
+    assert isinstance(hk.lib.mxfp6_last_error(), bytes)
+
+
+def test_bad_arguments_rejected_without_gpu():
+    L = hk.lib
+    assert L.mxfp6_gemm(None, None, None, None, None, 16, 16, 100, 0, 0, None) == _lib.ERR_BAD_ARG
+    assert b"multiple of 128" in L.mxfp6_last_error()
+    assert L.mxfp6_gemm(None, None, None, None, None, -1, 16, 128, 0, 0, None) == _lib.ERR_BAD_ARG
+    assert L.mxfp6_gemm(None, None, None, None, None, 16, 16, 128, 7, 0, None) == _lib.ERR_BAD_ARG
+    assert L.mxfp6_gemm(None, None, None, None, None, 0, 16, 128, 0, 0, None) == _lib.OK      # empty problem
+    assert L.mxfp6_gemm(None, None, None, None, None, 16, 16, 128, 0, 0, None) == _lib.ERR_BAD_ARG  # null C
+    assert L.mxfp6_quantize(None, 0, 4, 33, 0, None, None, None) == _lib.ERR_BAD_ARG
+    assert L.mxfp6_quantize(None, 5, 4, 32, 0, None, None, None) == _lib.ERR_BAD_ARG
+    assert L.mxfp6_quantize(None, 0, 0, 32, 0, None, None, None) == _lib.OK
+    assert L.mxfp6_dequantize(None, None, 4, 32, 3, None, None) == _lib.ERR_BAD_ARG
+    assert L.mxfp6_gemm_workspace_bytes(16, 16, 100) == 0
+
+
+def test_python_wrapper_rejects_cpu_and_bad_tensors():
+    import torch
+    A = torch.zeros(16, 96, dtype=torch.uint8)
+    C = torch.zeros(16, 16, dtype=torch.bfloat16)
+    S = torch.zeros(16, 4, dtype=torch.uint8)
+    with pytest.raises(RuntimeError, match="Tensor must be on CUDA device"):
+        hk.dispatch_micro(A, A, C, S, S)
+    with pytest.raises(RuntimeError, match="Tensor must be contiguous"):
+        hk.dispatch_micro(A.t(), A, C, S, S)
+    with pytest.raises(RuntimeError, match="Expected a torch.Tensor"):
+        hk.dispatch_micro(1, A, C, S, S)
+
+
+def test_tk_kernel_module_matches_reference_names():
+    import sys
+    sys.path.insert(0, os.path.join(ROOT, "hipkittensp_b200"))
+    import tk_kernel
+    import torch
+    assert callable(tk_kernel.dispatch_micro)
+    A = torch.zeros(16, 96, dtype=torch.uint8)
+    C = torch.zeros(16, 16, dtype=torch.bfloat16)
+    S = torch.zeros(16, 4, dtype=torch.uint8)
+    with pytest.raises(RuntimeError, match="Tensor must be on CUDA device"):
+        tk_kernel.dispatch_micro(A, A, C, S, S)
+    with pytest.raises(RuntimeError, match="Tensor must be contiguous"):
+        tk_kernel.dispatch_micro(A.t(), A, C, S, S)
+    with pytest.raises(RuntimeError, match="Expected a torch.Tensor"):
+        tk_kernel.dispatch_micro(3, A, C, S, S)

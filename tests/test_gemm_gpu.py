@@ -1,0 +1,165 @@
+"""GPU parity tests of the MX-FP6 GEMM against the CPU oracle, through the C ABI.
+
+Tolerances (the path's stated bar): per row, max_n |C-C_ref| / ||C_ref[r,:]||_2 <= 1e-2, and no element
+further than 2 bf16 ulp from the oracle, where the oracle is the fp64-accumulated product of the exactly
+dequantised operands and elements whose error lies inside the fp32 accumulation noise floor
+(2^-20 * sum_k |a_k b_k|) are excused and counted."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import hipkittensp_b200 as hk
+from oracle import mxfp6_ref as R
+from tests.gpu_util import check, oracle_f64, quantized_inputs, run_gpu
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(autouse=True)
+def _clean_env():
+    yield
+    os.environ.pop("MXFP6_FORCE_CFG", None)
+    os.environ.pop("MXFP6_NO_SF_TMA", None)
+
+
+def _case(config, M, N, K, fmt=R.E2M3, seed=0, force=None, fmt_b=None):
+    if force:
+        os.environ["MXFP6_FORCE_CFG"] = force
+    pa, sa, pb, sb = quantized_inputs(config, M, N, K, fmt, seed, fmt_b)
+    c = run_gpu(pa, sa, pb, sb, fmt, fmt_b)
+    ref, absdot = oracle_f64(pa, sa, pb, sb, fmt, fmt_b)
+    return check(c, ref, absdot)
+
+
+def test_tma_image_of_packed_fp6():
+    """The 6-bit tensor-map type expands each 12-byte group of 16 codes to a 16-byte slot; the packed
+    stream is little-endian, 6 bits per element.  Pins the global packing against the hardware."""
+    rows, K = 128, 256
+    codes = (np.arange(K)[None, :] + np.arange(rows)[:, None]) % 64
+    packed = torch.from_numpy(R.pack_codes(codes.astype(np.uint8))).cuda()
+    for k0 in (0, 128):
+        img = hk.tma_dump(packed, 0, k0).cpu().numpy()
+        assert hk.device_status() == 0
+        for r in range(rows):
+            rowb = img[r * 128:(r + 1) * 128].reshape(8, 16)
+            un = np.stack([rowb[c ^ (r % 8)] for c in range(8)])       # undo the 128-byte swizzle
+            got = R.unpack_codes(un[:, :12].reshape(1, -1))[0]
+            np.testing.assert_array_equal(got, codes[r, k0:k0 + 128])
+
+
+def test_single_tile_unit_scales():
+    os.environ["MXFP6_FORCE_CFG"] = "128,0,0"
+    pa, sa, pb, sb = quantized_inputs("normal", 128, 128, 128)
+    sa[:] = 127
+    sb[:] = 127
+    c = run_gpu(pa, sa, pb, sb, R.E2M3)
+    ref, absdot = oracle_f64(pa, sa, pb, sb, R.E2M3)
+    check(c, ref, absdot)
+
+
+def test_identity_operand_exposes_layout():
+    """B = identity-like one-hot rows: C[m,n] must reproduce A[m,n] exactly (any operand- or scale-layout
+    mistake permutes or rescales it)."""
+    os.environ["MXFP6_FORCE_CFG"] = "128,0,0"
+    M = N = K = 256
+    A, _ = R.make_inputs("lognormal", M, N, K, seed=5)
+    pa, sa = R.quantize(A, R.E2M3)
+    pb, sb = R.quantize(np.eye(N, K, dtype=np.float32), R.E2M3)
+    c = run_gpu(pa, sa, pb, sb, R.E2M3)
+    want = torch.from_numpy(R.dequantize(pa, sa, R.E2M3)).to(torch.bfloat16).float().numpy()
+    np.testing.assert_array_equal(c, want)
+
+
+def test_distinct_power_of_two_scales_per_block():
+    os.environ["MXFP6_FORCE_CFG"] = "128,0,0"
+    M, N, K = 128, 128, 1024
+    pa, sa, pb, sb = quantized_inputs("normal", M, N, K, seed=2)
+    rng = np.random.default_rng(0)
+    sa[:] = rng.integers(110, 140, size=sa.shape, dtype=np.uint8)
+    sb[:] = rng.integers(110, 140, size=sb.shape, dtype=np.uint8)
+    c = run_gpu(pa, sa, pb, sb, R.E2M3)
+    ref, absdot = oracle_f64(pa, sa, pb, sb, R.E2M3)
+    check(c, ref, absdot)
+
+
+@pytest.mark.parametrize("K", [128, 256, 384, 512, 1024])
+def test_k_sweep(K):
+    _case("lognormal", 128, 128, K, force="128,0,0")
+
+
+@pytest.mark.parametrize("force", ["128,0,0", "256,0,0", "128,0,1", "256,0,1"])
+def test_tile_configs(force):
+    _case("lognormal", 384, 768, 1024, force=force, seed=1)
+
+
+@pytest.mark.parametrize("M", [1, 16, 17, 127, 129])
+def test_ragged_m(M):
+    _case("normal", M, 384, 512, seed=M)
+
+
+@pytest.mark.parametrize("N", [16, 64, 128, 200, 520])
+def test_ragged_n(N):
+    _case("normal", 160, N, 512, seed=N)
+
+
+def test_scale_plain_load_path():
+    os.environ["MXFP6_NO_SF_TMA"] = "1"
+    _case("lognormal", 256, 256, 1024, seed=4)
+
+
+def test_zero_and_max_blocks():
+    M, N, K = 128, 128, 256
+    A, B = R.make_inputs("normal", M, N, K, seed=9)
+    A[:, :32] = 0.0
+    B[5, :] = 0.0
+    A[7, 32:64] = 7.5 * 2.0 ** 20
+    pa, sa = R.quantize(A, R.E2M3)
+    pb, sb = R.quantize(B, R.E2M3)
+    c = run_gpu(pa, sa, pb, sb, R.E2M3)
+    ref, absdot = oracle_f64(pa, sa, pb, sb, R.E2M3)
+    check(c, ref, absdot)
+    assert (c[:, 5] == 0).all()
+
+
+def test_config_cpu_runnable_1024_cubed():
+    rep = _case("normal", 1024, 1024, 1024)
+    assert rep["n_1pct"] < 0.02 * 1024 * 1024
+
+
+def test_config_e3m2_ffn_shape_reduced():
+    _case("ffn", 512, 1792, 2048, fmt=R.E3M2)
+
+
+def test_mixed_formats():
+    _case("ffn", 256, 256, 512, fmt=R.E3M2, fmt_b=R.E2M3)
+
+
+@pytest.mark.parametrize("M", [1, 16, 64])
+def test_config_decode_reduced(M):
+    _case("decode", M, 3584, 2048, seed=M)
+
+
+def test_skinny_full_k_many_tiles():
+    _case("decode", 16, 28672, 1024)
+
+
+def test_tk_kernel_module():
+    import sys
+    sys.path.insert(0, os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "hipkittensp_b200"))
+    import tk_kernel
+    pa, sa, pb, sb = quantized_inputs("normal", 256, 256, 512)
+    t = [torch.from_numpy(x).cuda() for x in (pa, pb, sa, sb)]
+    C = torch.empty(256, 256, dtype=torch.bfloat16, device="cuda")
+    tk_kernel.dispatch_micro(t[0], t[1], C, t[2], t[3], 0)
+    assert hk.device_status() == 0
+    ref, absdot = oracle_f64(pa, sa, pb, sb, R.E2M3)
+    check(C.float().cpu().numpy(), ref, absdot)
+
+
+def test_repeat_calls_are_deterministic():
+    pa, sa, pb, sb = quantized_inputs("decode", 16, 4096, 4096)
+    c1 = run_gpu(pa, sa, pb, sb, R.E2M3)
+    c2 = run_gpu(pa, sa, pb, sb, R.E2M3)
+    np.testing.assert_array_equal(c1, c2)
