@@ -143,6 +143,9 @@ struct Plan {
 
 static int ceil_div(int64_t a, int64_t b) { return (int)((a + b - 1) / b); }
 
+// Most output tiles a problem may have and still split tiles along K (bounds the counter region).
+constexpr int64_t kMaxSplitTiles = 65536;
+
 static Plan make_plan(int64_t M, int64_t N, int64_t K, int sm_count) {
     Plan p{};
     const int kb = (int)(K / 128);
@@ -150,7 +153,8 @@ static Plan make_plan(int64_t M, int64_t N, int64_t K, int sm_count) {
     int fbn = 0, fswap = -1, fsk = -1;
     if (force) sscanf(force, "%d,%d,%d", &fbn, &fswap, &fsk);
     if (M <= 128 && N > M) {
-        p.swap = true; p.streamk = true;
+        p.swap = true;
+        p.streamk = (int64_t)ceil_div(N, 128) <= kMaxSplitTiles;
         p.bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : 128;
     } else {
         p.swap = false; p.streamk = false;
@@ -160,6 +164,10 @@ static Plan make_plan(int64_t M, int64_t N, int64_t K, int sm_count) {
     if (fbn) p.bn = fbn;
     if (fswap >= 0) p.swap = fswap != 0;
     if (fsk >= 0) p.streamk = fsk != 0;
+    {
+        const int64_t t = (int64_t)ceil_div(p.swap ? N : M, 128) * ceil_div(p.swap ? M : N, p.bn);
+        if (t > kMaxSplitTiles) p.streamk = false;
+    }
     const int64_t prow = p.swap ? N : M, qrow = p.swap ? M : N;
     p.tiles_p = ceil_div(prow, 128);
     p.tiles_q = ceil_div(qrow, p.bn);
@@ -172,7 +180,9 @@ static Plan make_plan(int64_t M, int64_t N, int64_t K, int sm_count) {
         int64_t maxseg = (kb + chunk - 1) / chunk + 1;
         if (maxseg > p.grid) maxseg = p.grid;
         p.ws_slots = (int)maxseg;
-        p.ws_counter_bytes = (size_t)((tiles * 4 + 255) / 256 * 256);
+        // The arrival counters always occupy the same fixed region at the start of the scratch buffer, so a
+        // buffer that is reused for another shape never sees partial sums where it expects zeroed counters.
+        p.ws_counter_bytes = (size_t)kMaxSplitTiles * 4;
         p.ws_bytes = p.ws_counter_bytes + (size_t)tiles * maxseg * (size_t)p.bn * 128 * 4;
     } else {
         p.grid = (int)(tiles < sm_count ? tiles : sm_count);
@@ -260,7 +270,7 @@ static int gemm_impl(const void* a, const void* sfa, const void* b, const void* 
     P.idesc = make_idesc(fp == MXFP6_E2M3 ? kFmtE2M3 : kFmtE3M2, fq == MXFP6_E2M3 ? kFmtE2M3 : kFmtE3M2, (uint32_t)pl.bn);
     P.sf_tma = sf_tma ? 1 : 0;
     P.sf_ld = (int)(K / 32);
-    P.stage_tx_bytes = (128 + pl.bn) * env_int("MXFP6_TX_BYTES_PER_ROW", 128);
+    P.stage_tx_bytes = (128 + pl.bn) * env_int("MXFP6_TX_BYTES_PER_ROW", 96);
     P.sfp = (const uint8_t*)sp; P.sfq = (const uint8_t*)sq;
     P.c = (__nv_bfloat16*)c;
     P.ws_counter = (unsigned int*)ws;
@@ -280,6 +290,10 @@ static int gemm_impl(const void* a, const void* sfa, const void* b, const void* 
     MXFP6_CASE(32, true, true)
     MXFP6_CASE(64, true, true)
     MXFP6_CASE(128, true, true)
+    MXFP6_CASE(16, true, false)
+    MXFP6_CASE(32, true, false)
+    MXFP6_CASE(64, true, false)
+    MXFP6_CASE(128, true, false)
 #undef MXFP6_CASE
     return fail(MXFP6_ERR_BAD_ARG, "no kernel for bn=%d swap=%d streamk=%d", pl.bn, (int)pl.swap, (int)pl.streamk);
 }
@@ -487,7 +501,7 @@ extern "C" int mxfp6_debug_tma_dump(const void* packed, int64_t rows, int64_t K,
     if ((rc = make_map(packed, rows, K, 128, 0, &tm))) return rc;
     static bool attr = false;
     if (!attr) { CUDA_TRY(cudaFuncSetAttribute(tma_dump_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 16384 + 2048)); attr = true; }
-    const uint32_t tx = 128u * (uint32_t)env_int("MXFP6_TX_BYTES_PER_ROW", 128);
+    const uint32_t tx = 128u * (uint32_t)env_int("MXFP6_TX_BYTES_PER_ROW", 96);
     tma_dump_kernel<<<1, 128, 16384 + 2048, (cudaStream_t)stream>>>(tm, (int)k0, (int)row0, tx, d->wait_cycles / 20, (uint8_t*)out16k, d->status);
     CUDA_TRY(cudaGetLastError());
     return MXFP6_OK;

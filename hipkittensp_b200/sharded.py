@@ -1,0 +1,71 @@
+"""Column-parallel MX-FP6 GEMM over the GPUs of one box.
+
+B[N,K] (and its scales) is split along N into `world` contiguous row blocks, A is replicated, rank r
+computes C[:, r*N/g:(r+1)*N/g] with the single-GPU kernel and the shards are all-gathered so that every
+rank ends with the full row-major C[M,N].  The reference's only multi-GPU GEMM shards A by rows and has
+no exchange step (distributed-kernels/bf16_gemm/example.py:70,112); the column-parallel split with a
+gather is this path's own multi-GPU form.
+
+The exchange is one NCCL all-gather of the contiguous [M, N/g] shards into a [g, M, N/g] buffer followed
+by a strided device copy into row-major C (`gather="nccl"`).
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+from ._lib import E2M3
+from .gemm import dispatch_micro
+
+
+def shard_bounds(N: int, world: int, rank: int) -> tuple[int, int]:
+    """Rows [lo, hi) of B (columns of C) owned by `rank`.  N must divide evenly into 128-row blocks per rank
+    only loosely: any N % world == 0 is accepted."""
+    if N % world:
+        raise ValueError(f"N={N} is not divisible by the number of ranks {world}")
+    per = N // world
+    return rank * per, (rank + 1) * per
+
+
+def shard_rows(t: torch.Tensor, world: int, rank: int) -> torch.Tensor:
+    """The contiguous row block of a [N, *] operand that `rank` owns."""
+    lo, hi = shard_bounds(t.shape[0], world, rank)
+    return t[lo:hi].contiguous()
+
+
+def assemble_columns(gathered: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """[g, M, N/g] (shard-major, as an all-gather of [M, N/g] shards produces) -> row-major [M, N]."""
+    g, M, per = gathered.shape
+    out.view(M, g, per).copy_(gathered.permute(1, 0, 2))
+    return out
+
+
+class ColumnParallelGemm:
+    """Holds the communicator and the reusable buffers of one sharded GEMM shape."""
+
+    def __init__(self, M: int, N: int, K: int, group=None, device=None, fmt: int = E2M3):
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.M, self.N, self.K, self.fmt = M, N, K, fmt
+        self.lo, self.hi = shard_bounds(N, self.world, self.rank)
+        self.device = device
+        self.c_shard = torch.empty((M, self.hi - self.lo), dtype=torch.bfloat16, device=device)
+        self.gathered = torch.empty((self.world, M, self.hi - self.lo), dtype=torch.bfloat16, device=device) \
+            if self.world > 1 else None
+        self.c_full = torch.empty((M, N), dtype=torch.bfloat16, device=device) if self.world > 1 else self.c_shard
+
+    def local_gemm(self, A, scale_A, B_shard, scale_B_shard) -> torch.Tensor:
+        """This rank's [M, N/g] block of C."""
+        dispatch_micro(A, B_shard, self.c_shard, scale_A, scale_B_shard, self.fmt)
+        return self.c_shard
+
+    def gather(self) -> torch.Tensor:
+        if self.world == 1:
+            return self.c_shard
+        dist.all_gather_into_tensor(self.gathered.view(-1), self.c_shard.view(-1), group=self.group)
+        return assemble_columns(self.gathered, self.c_full)
+
+    def __call__(self, A, scale_A, B_shard, scale_B_shard) -> torch.Tensor:
+        self.local_gemm(A, scale_A, B_shard, scale_B_shard)
+        return self.gather()

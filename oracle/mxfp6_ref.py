@@ -300,3 +300,29 @@ def c_gemm_ref(a_packed, sfa, b_packed, sfb, fmt_a=E2M3, fmt_b=None, acc_mode=0,
 
 def bf16_bits_to_f32(bits: np.ndarray) -> np.ndarray:
     return (np.asarray(bits, np.uint16).astype(np.uint32) << 16).view(np.float32)
+
+
+# --------------------------------------------------------------------------- the timed CPU path
+def dequantize_torch(packed, scales, fmt: int):
+    """torch-only dequantise (multi-threaded on the host cores): the first half of the CPU
+    dequantise-then-matmul path that the benchmark times as the reference arm."""
+    import torch
+
+    rows = packed.shape[0]
+    K = packed.shape[1] // 3 * 4
+    b = packed.view(rows, -1, 3).to(torch.int32)
+    w = b[..., 0] | (b[..., 1] << 8) | (b[..., 2] << 16)
+    codes = torch.stack([w & 63, (w >> 6) & 63, (w >> 12) & 63, (w >> 18) & 63], dim=-1).view(rows, K)
+    lut = torch.from_numpy(decode_table(fmt))
+    vals = lut[codes.long()]
+    s = torch.from_numpy(e8m0_decode(np.arange(256, dtype=np.uint8)))[scales.long()]
+    return (vals.view(rows, K // 32, 32) * s.unsqueeze(-1)).view(rows, K)
+
+
+def gemm_cpu_path(a_packed, sfa, b_packed, sfb, fmt_a=E2M3, fmt_b=None):
+    """torch tensors in (uint8), bf16 tensor out: dequantise both operands, fp32 matmul, round to bf16."""
+    import torch
+
+    A = dequantize_torch(a_packed, sfa, fmt_a)
+    B = dequantize_torch(b_packed, sfb, fmt_a if fmt_b is None else fmt_b)
+    return (A @ B.t()).to(torch.bfloat16)
