@@ -41,8 +41,8 @@ NCU_TRAFFIC_BYTES_8192 = None
 def parse():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
-    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=1000)
+    ap.add_argument("--warmup", type=int, default=100)
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU baseline leg (N=1)")
     ap.add_argument("--small", action="store_true", help="1024^3 instead of 8192^3 (profiling aid, not a bench value)")
@@ -66,7 +66,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                          "-lms", "100", "-i", str(self.idx)], stdout=subprocess.PIPE,
+                                          "-lms", "20", "-i", str(self.idx)], stdout=subprocess.PIPE,
                                          stderr=subprocess.DEVNULL, text=True)
         except Exception:
             self.proc = None
@@ -299,12 +299,12 @@ def cpu_baseline(operands, M, N, K, budget_s):
 
     a, sa, b, sb = operands
     cores = torch.get_num_threads()
+    R.gemm_cpu_path(a[:64], sa[:64], b[:512], sb[:512])          # warm the thread pool
     t0 = time.perf_counter()
-    R.gemm_cpu_path(a[:64], sa[:64], b[:512], sb[:512])
-    probe = time.perf_counter() - t0
-    est_full = probe * (M / 64) * (N / 512)
+    R.gemm_cpu_path(a[:256], sa[:256], b, sb)
+    probe = time.perf_counter() - t0                              # 256 rows incl. the dequantisation of all of B
     rows = M
-    while rows > 128 and est_full * rows / M > budget_s:
+    while rows > 256 and probe * rows / 256 > budget_s:
         rows //= 2
     t0 = time.perf_counter()
     R.gemm_cpu_path(a[:rows], sa[:rows], b, sb)
@@ -339,11 +339,12 @@ def run_reference(args):
     pa, sa = R.c_quantize(xa, R.E2M3)
     del xa
     ta, tsa, tb, tsb = (torch.from_numpy(x) for x in (pa, sa, pb, sb))
+    R.gemm_cpu_path(ta[:64], tsa[:64], tb[:512], tsb[:512])      # warm the thread pool
     t0 = time.perf_counter()
-    R.gemm_cpu_path(ta[:64], tsa[:64], tb[:512], tsb[:512])
+    R.gemm_cpu_path(ta[:256], tsa[:256], tb, tsb)
     probe = time.perf_counter() - t0
     rows = rows_a
-    while rows > 128 and probe * (rows / 64) * (rows_b / 512) > budget:
+    while rows > 256 and probe * rows / 256 > budget:
         rows //= 2
     for _ in range(W):
         R.gemm_cpu_path(ta[:rows], tsa[:rows], tb, tsb)
