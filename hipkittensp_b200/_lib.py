@@ -6,7 +6,7 @@ import ctypes
 import os
 
 _PKG = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_PKG, "libmxfp6.so")
+LIB_PATH = os.environ.get("MXFP6_LIBRARY") or os.path.join(_PKG, "libmxfp6.so")   # MXFP6_LIBRARY: load another build of the library
 
 E2M3 = 0
 E3M2 = 1

@@ -12,8 +12,8 @@
 //            and raw E8M0 scale slabs into shared-memory rings
 //   warp 1   MMA issuer: copies the scale atoms into TMEM (tcgen05.cp) and issues
 //            tcgen05.mma.kind::mxf8f6f4.block_scale, accumulating in TMEM
-//   warp 2   scale re-tiler: row-major [rows, K/32] scale bytes -> the 32x16-byte atoms the MMA wants
-//   warp 3   idle
+//   warps 2-3 scale re-tilers: row-major [rows, K/32] scale bytes -> the 32x16-byte atoms the MMA wants,
+//            one group of 4 K-blocks at a time, the two warps alternating
 //   warps 4-7 epilogue: TMEM -> registers -> bf16 -> global (or fp32 partials for split tiles)
 //
 // Every wait on an mbarrier is bounded; on expiry the CTA records a status code and leaves cleanly.
@@ -49,6 +49,7 @@ struct GemmParams {
     int ws_slots;              // partial slots per tile
     int* status;               // device status word
     unsigned long long wait_cycles;  // budget of one wait in clock cycles
+    int dbg;                   // experiment switches, honoured only by builds with MXFP6_DEBUG_KNOBS
 };
 
 template <int BN_, bool SWAP_, bool STREAMK_>
@@ -61,20 +62,21 @@ struct GemmCfg {
     static constexpr int P_BYTES = BM * BK;
     static constexpr int Q_BYTES = BN * BK;
     static constexpr int STAGE_BYTES = P_BYTES + Q_BYTES;
-    static constexpr int STAGES = BN >= 256 ? 4 : BN >= 128 ? 6 : BN >= 64 ? 8 : 10;
+    static constexpr int STAGES = BN >= 256 ? 4 : BN >= 128 ? 6 : BN >= 64 ? 8 : BN >= 32 ? 9 : 10;
     static constexpr int QATOMS = (BN + 127) / 128;      // 128-row scale atoms on the Q side
     static constexpr int RAW_SLOTS = BN >= 256 ? 2 : 4;  // each raw slab covers 4 K-blocks (16 scale bytes per row)
     static constexpr int RAW_Q_ROWS = BN < 32 ? 32 : BN;
     static constexpr int RAW_BYTES = (BM + RAW_Q_ROWS) * 16;
     static constexpr int RAW_TX_BYTES = (BM + BN) * 16;
-    static constexpr int ATOM_SLOTS = 8;
-    static constexpr int ATOM_BYTES = 512 * (1 + QATOMS);
+    static constexpr int ATOM_BYTES = 512 * (1 + QATOMS);  // scale atoms of one K-block: P atom + Q atoms
+    static constexpr int GROUP_BYTES = 4 * ATOM_BYTES;     // a group = the 4 K-blocks one raw slab covers
+    static constexpr int ATOM_GROUPS = BN >= 256 ? 3 : 4;
     static constexpr bool OVERLAP = BN == 256;           // two 256-column accumulators share 32 columns
     static constexpr int ACC_COL1 = OVERLAP ? 224 : BN;
     static constexpr int SF_COL = OVERLAP ? 480 : 2 * BN;
     static constexpr int TMEM_COLS = 512;
-    static constexpr int NUM_BARS = 2 * STAGES + 2 * RAW_SLOTS + 2 * ATOM_SLOTS + 5;
-    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + RAW_SLOTS * RAW_BYTES + ATOM_SLOTS * ATOM_BYTES +
+    static constexpr int NUM_BARS = 2 * STAGES + 2 * RAW_SLOTS + 2 * ATOM_GROUPS + 5;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + RAW_SLOTS * RAW_BYTES + ATOM_GROUPS * GROUP_BYTES +
                                       NUM_BARS * 8 + 64;
     static constexpr int SMEM_ALLOC = SMEM_BYTES + 1024;  // slack for the 1024-byte alignment of the operand ring
     static constexpr int THREADS = 256;
@@ -178,14 +180,14 @@ mxfp6_gemm_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constan
     const uint32_t stage_base = smem_base;
     const uint32_t raw_base = stage_base + Cfg::STAGES * Cfg::STAGE_BYTES;
     const uint32_t atom_base = raw_base + Cfg::RAW_SLOTS * Cfg::RAW_BYTES;
-    const uint32_t bar_base = atom_base + Cfg::ATOM_SLOTS * Cfg::ATOM_BYTES;
+    const uint32_t bar_base = atom_base + Cfg::ATOM_GROUPS * Cfg::GROUP_BYTES;
     auto bar_full = [&](int s) { return bar_base + 8u * s; };
     auto bar_empty = [&](int s) { return bar_base + 8u * (Cfg::STAGES + s); };
     auto bar_raw_full = [&](int s) { return bar_base + 8u * (2 * Cfg::STAGES + s); };
     auto bar_raw_empty = [&](int s) { return bar_base + 8u * (2 * Cfg::STAGES + Cfg::RAW_SLOTS + s); };
     auto bar_atom_full = [&](int s) { return bar_base + 8u * (2 * Cfg::STAGES + 2 * Cfg::RAW_SLOTS + s); };
-    auto bar_atom_empty = [&](int s) { return bar_base + 8u * (2 * Cfg::STAGES + 2 * Cfg::RAW_SLOTS + Cfg::ATOM_SLOTS + s); };
-    const uint32_t bar_misc = bar_base + 8u * (2 * Cfg::STAGES + 2 * Cfg::RAW_SLOTS + 2 * Cfg::ATOM_SLOTS);
+    auto bar_atom_empty = [&](int s) { return bar_base + 8u * (2 * Cfg::STAGES + 2 * Cfg::RAW_SLOTS + Cfg::ATOM_GROUPS + s); };
+    const uint32_t bar_misc = bar_base + 8u * (2 * Cfg::STAGES + 2 * Cfg::RAW_SLOTS + 2 * Cfg::ATOM_GROUPS);
     auto bar_acc_full = [&](int b) { return bar_misc + 8u * b; };
     auto bar_acc_empty = [&](int b) { return bar_misc + 8u * (2 + b); };
     const uint32_t bar_ovl = bar_misc + 8u * 4;
@@ -199,7 +201,7 @@ mxfp6_gemm_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constan
     if (threadIdx.x == 0) {
         for (int s = 0; s < Cfg::STAGES; ++s) { mbar_init(bar_full(s), 1); mbar_init(bar_empty(s), 1); }
         for (int s = 0; s < Cfg::RAW_SLOTS; ++s) { mbar_init(bar_raw_full(s), 1); mbar_init(bar_raw_empty(s), 32); }
-        for (int s = 0; s < Cfg::ATOM_SLOTS; ++s) { mbar_init(bar_atom_full(s), 32); mbar_init(bar_atom_empty(s), 1); }
+        for (int s = 0; s < Cfg::ATOM_GROUPS; ++s) { mbar_init(bar_atom_full(s), 32); mbar_init(bar_atom_empty(s), 1); }
         for (int b = 0; b < 2; ++b) { mbar_init(bar_acc_full(b), 1); mbar_init(bar_acc_empty(b), 128); }
         mbar_init(bar_ovl, 128);
         *abort_flag = 0;
@@ -233,7 +235,7 @@ mxfp6_gemm_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constan
                     const uint32_t ph = (n_raw / Cfg::RAW_SLOTS) & 1;
                     ok = wait_bar_warp(bar_raw_empty(r), ph ^ 1, abort_flag, P, kStatusTimeoutProducer);
                     if (!ok) break;
-                    if (lane == 0) {
+                    if (elect_one_sync()) {
                         const uint32_t dst = raw_base + r * Cfg::RAW_BYTES;
                         mbar_arrive_expect_tx(bar_raw_full(r), Cfg::RAW_TX_BYTES);
                         tma_load_2d(dst, &tm_sfp, bar_raw_full(r), (kb >> 2) * 16, sg.p0);
@@ -245,7 +247,7 @@ mxfp6_gemm_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constan
                 const uint32_t ph = (n_stage / Cfg::STAGES) & 1;
                 ok = wait_bar_warp(bar_empty(s), ph ^ 1, abort_flag, P, kStatusTimeoutProducer);
                 if (!ok) break;
-                if (lane == 0) {
+                if (elect_one_sync()) {
                     const uint32_t dst = stage_base + s * Cfg::STAGE_BYTES;
                     mbar_arrive_expect_tx(bar_full(s), (uint32_t)P.stage_tx_bytes);
                     tma_load_2d(dst, &tm_p, bar_full(s), kb * Cfg::BK, sg.p0);
@@ -260,7 +262,7 @@ mxfp6_gemm_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constan
     else if (warp == 1) {
         SegIter<Cfg> it(P);
         Segment sg;
-        uint32_t n_kb = 0, n_seg = 0;
+        uint32_t n_kb = 0, n_seg = 0, n_grp = 0;
         bool ok = true;
         while (ok && it.next(sg)) {
             const int b = n_seg & 1;
@@ -274,15 +276,17 @@ mxfp6_gemm_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constan
             tc_fence_after();
             for (int kb = sg.k0; kb < sg.k1; ++kb) {
                 const int s = n_kb % Cfg::STAGES;
-                const int a = n_kb % Cfg::ATOM_SLOTS;
-                ok = wait_bar_warp(bar_full(s), (n_kb / Cfg::STAGES) & 1, abort_flag, P, kStatusTimeoutMma) &&
-                     wait_bar_warp(bar_atom_full(a), (n_kb / Cfg::ATOM_SLOTS) & 1, abort_flag, P, kStatusTimeoutMma);
+                const int g = n_grp % Cfg::ATOM_GROUPS;
+                // the scale atoms arrive per group of 4 K-blocks (one raw slab)
+                if (kb == sg.k0 || (kb & 3) == 0)
+                    ok = wait_bar_warp(bar_atom_full(g), (n_grp / Cfg::ATOM_GROUPS) & 1, abort_flag, P, kStatusTimeoutMma);
+                ok = ok && wait_bar_warp(bar_full(s), (n_kb / Cfg::STAGES) & 1, abort_flag, P, kStatusTimeoutMma);
                 if (!ok) break;
-                tc_fence_after();
-                if (lane == 0) {
+                const bool group_done = (kb & 3) == 3 || kb == sg.k1 - 1;
+                if (elect_one_sync()) {
                     const uint32_t sfa = tmem_base + Cfg::SF_COL + (n_kb & 1) * 16;
                     const uint32_t sfb = sfa + 4;
-                    const uint32_t atom = atom_base + a * Cfg::ATOM_BYTES;
+                    const uint32_t atom = atom_base + g * Cfg::GROUP_BYTES + (kb & 3) * Cfg::ATOM_BYTES;
                     tc_cp_32x128b_warpx4(sfa, smem_desc_sf(atom));
 #pragma unroll
                     for (int q = 0; q < Cfg::QATOMS; ++q) tc_cp_32x128b_warpx4(sfb + 4 * q, smem_desc_sf(atom + 512 * (1 + q)));
@@ -295,87 +299,93 @@ mxfp6_gemm_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constan
                                      sfa | (k << 30), sfb | (k << 30), (kb > sg.k0 || k > 0) ? 1u : 0u);
                     }
                     tc_commit(bar_empty(s));
-                    tc_commit(bar_atom_empty(a));
+                    if (group_done) tc_commit(bar_atom_empty(g));
                 }
                 __syncwarp();
                 ++n_kb;
+                if (group_done) ++n_grp;
             }
             if (!ok) break;
-            if (lane == 0) tc_commit(bar_acc_full(b));
+            if (elect_one_sync()) tc_commit(bar_acc_full(b));
             __syncwarp();
             ++n_seg;
         }
     }
-    // =========================================================== warp 2: scale re-tiler
-    else if (warp == 2) {
+    // =========================================================== warps 2-3: scale re-tilers
+    // Each group of 4 K-blocks (one raw slab of 16 scale bytes per row) is handled by one of the two warps,
+    // alternately: raw words -> registers -> the 4 x (1+QATOMS) atoms of the group -> one proxy fence ->
+    // one arrival.
+    else if (warp == 2 || warp == 3) {
         SegIter<Cfg> it(P);
         Segment sg;
-        uint32_t n_kb = 0, n_raw = 0;
+        uint32_t n_grp = 0;
         bool ok = true;
         constexpr int QG = (BN + 31) / 32;        // 32-row groups on the Q side
-        uint32_t rp[4][4];                          // [row group][k-block in slab] scale words of P rows
-        uint32_t rq[QG][4];
         while (ok && it.next(sg)) {
-            for (int kb = sg.k0; kb < sg.k1; ++kb) {
-                const int j = kb & 3;
-                uint32_t wp[4], wq[Cfg::QATOMS * 4];     // this K-block's scale words per 32-row group
-                if (P.sf_tma) {
-                    if (kb == sg.k0 || j == 0) {
-                        const int r = n_raw % Cfg::RAW_SLOTS;
-                        ok = wait_bar_warp(bar_raw_full(r), (n_raw / Cfg::RAW_SLOTS) & 1, abort_flag, P, kStatusTimeoutScale);
+            for (int kb = sg.k0; kb < sg.k1 && ok;) {
+                const int kb_next = min(sg.k1, (kb | 3) + 1);
+                if ((int)(n_grp & 1) == warp - 2) {
+                    uint32_t rp[4][4];                  // [32-row group][K-block of the slab]
+                    uint32_t rq[Cfg::QATOMS * 4][4];
+                    if (P.sf_tma) {
+                        const int r = n_grp % Cfg::RAW_SLOTS;
+                        ok = wait_bar_warp(bar_raw_full(r), (n_grp / Cfg::RAW_SLOTS) & 1, abort_flag, P, kStatusTimeoutScale);
                         if (!ok) break;
                         const uint8_t* raw = smem_gen + (raw_base - smem_base) + r * Cfg::RAW_BYTES;
 #pragma unroll
                         for (int c = 0; c < 4; ++c) {
-                            uint4 v = *reinterpret_cast<const uint4*>(raw + (lane + 32 * c) * 16);
+                            const uint4 v = *reinterpret_cast<const uint4*>(raw + (lane + 32 * c) * 16);
                             rp[c][0] = v.x; rp[c][1] = v.y; rp[c][2] = v.z; rp[c][3] = v.w;
                         }
 #pragma unroll
-                        for (int c = 0; c < QG; ++c) {
-                            uint4 v = *reinterpret_cast<const uint4*>(raw + Cfg::BM * 16 + (lane + 32 * c) * 16);
-                            rq[c][0] = v.x; rq[c][1] = v.y; rq[c][2] = v.z; rq[c][3] = v.w;
+                        for (int c = 0; c < Cfg::QATOMS * 4; ++c) {
+                            if (c < QG) {
+                                const uint4 v = *reinterpret_cast<const uint4*>(raw + Cfg::BM * 16 + (lane + 32 * c) * 16);
+                                rq[c][0] = v.x; rq[c][1] = v.y; rq[c][2] = v.z; rq[c][3] = v.w;
+                            } else {
+                                rq[c][0] = rq[c][1] = rq[c][2] = rq[c][3] = 0u;
+                            }
                         }
                         mbar_arrive(bar_raw_empty(r));
-                        ++n_raw;
-                    }
-                    // register arrays are indexed with compile-time constants only (no local memory)
+                    } else {
+                        const int kb4 = kb & ~3;
 #pragma unroll
-                    for (int c = 0; c < 4; ++c)
-                        wp[c] = j == 0 ? rp[c][0] : j == 1 ? rp[c][1] : j == 2 ? rp[c][2] : rp[c][3];
+                        for (int c = 0; c < 4; ++c) {
+                            const int row = sg.p0 + lane + 32 * c;
 #pragma unroll
-                    for (int c = 0; c < Cfg::QATOMS * 4; ++c) {
-                        if (c < QG) wq[c] = j == 0 ? rq[c < QG ? c : 0][0] : j == 1 ? rq[c < QG ? c : 0][1]
-                                          : j == 2 ? rq[c < QG ? c : 0][2] : rq[c < QG ? c : 0][3];
-                        else wq[c] = 0u;
-                    }
-                } else {
+                            for (int jj = 0; jj < 4; ++jj)
+                                rp[c][jj] = (row < P.p_rows && kb4 + jj < P.kblocks)
+                                    ? *reinterpret_cast<const uint32_t*>(P.sfp + (size_t)row * P.sf_ld + (kb4 + jj) * 4) : 0u;
+                        }
 #pragma unroll
-                    for (int c = 0; c < 4; ++c) {
-                        const int row = sg.p0 + lane + 32 * c;
-                        wp[c] = row < P.p_rows
-                            ? *reinterpret_cast<const uint32_t*>(P.sfp + (size_t)row * P.sf_ld + kb * 4) : 0u;
-                    }
+                        for (int c = 0; c < Cfg::QATOMS * 4; ++c) {
+                            const int row = sg.q0 + lane + 32 * c;
 #pragma unroll
-                    for (int c = 0; c < Cfg::QATOMS * 4; ++c) {
-                        const int row = sg.q0 + lane + 32 * c;
-                        wq[c] = (c < QG && row < P.q_rows)
-                            ? *reinterpret_cast<const uint32_t*>(P.sfq + (size_t)row * P.sf_ld + kb * 4) : 0u;
+                            for (int jj = 0; jj < 4; ++jj)
+                                rq[c][jj] = (c < QG && row < P.q_rows && kb4 + jj < P.kblocks)
+                                    ? *reinterpret_cast<const uint32_t*>(P.sfq + (size_t)row * P.sf_ld + (kb4 + jj) * 4) : 0u;
+                        }
                     }
+                    const int g = n_grp % Cfg::ATOM_GROUPS;
+                    ok = wait_bar_warp(bar_atom_empty(g), ((n_grp / Cfg::ATOM_GROUPS) & 1) ^ 1, abort_flag, P, kStatusTimeoutScale);
+                    if (!ok) break;
+                    uint8_t* grp = smem_gen + (atom_base - smem_base) + g * Cfg::GROUP_BYTES;
+                    // atom layout: 32 rows of 16 bytes; row (r%32) holds, for the four 32-row groups c = r/32,
+                    // the 4 scale bytes of one K-block: byte offset (r%32)*16 + c*4 + (k/32)%4
+#pragma unroll
+                    for (int jj = 0; jj < 4; ++jj) {
+                        uint8_t* atom = grp + jj * Cfg::ATOM_BYTES;
+                        *reinterpret_cast<uint4*>(atom + lane * 16) = make_uint4(rp[0][jj], rp[1][jj], rp[2][jj], rp[3][jj]);
+#pragma unroll
+                        for (int qa = 0; qa < Cfg::QATOMS; ++qa)
+                            *reinterpret_cast<uint4*>(atom + 512 * (1 + qa) + lane * 16) =
+                                make_uint4(rq[4 * qa][jj], rq[4 * qa + 1][jj], rq[4 * qa + 2][jj], rq[4 * qa + 3][jj]);
+                    }
+                    fence_proxy_async_smem();
+                    mbar_arrive(bar_atom_full(g));
                 }
-                const int a = n_kb % Cfg::ATOM_SLOTS;
-                ok = wait_bar_warp(bar_atom_empty(a), ((n_kb / Cfg::ATOM_SLOTS) & 1) ^ 1, abort_flag, P, kStatusTimeoutScale);
-                if (!ok) break;
-                uint8_t* atom = smem_gen + (atom_base - smem_base) + a * Cfg::ATOM_BYTES;
-                // atom layout: 32 rows of 16 bytes; row (r%32) holds, for the four 32-row groups c = r/32,
-                // the 4 scale bytes of this K-block: byte offset (r%32)*16 + c*4 + (k/32)%4.
-                *reinterpret_cast<uint4*>(atom + lane * 16) = make_uint4(wp[0], wp[1], wp[2], wp[3]);
-#pragma unroll
-                for (int qa = 0; qa < Cfg::QATOMS; ++qa)
-                    *reinterpret_cast<uint4*>(atom + 512 * (1 + qa) + lane * 16) =
-                        make_uint4(wq[4 * qa], wq[4 * qa + 1], wq[4 * qa + 2], wq[4 * qa + 3]);
-                fence_proxy_async_smem();
-                mbar_arrive(bar_atom_full(a));
-                ++n_kb;
+                ++n_grp;
+                kb = kb_next;
             }
         }
     }

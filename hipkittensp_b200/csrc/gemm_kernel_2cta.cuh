@@ -1,0 +1,365 @@
+// CTA-pair variant of the MX-FP6 GEMM for large problems: two CTAs of a cluster (one per SM) share one
+// 256x256 output tile through tcgen05 cta_group::2.
+//
+//   CTA rank r of the pair owns P rows p0+128r.. (its half of A, its 128x256 fp32 accumulator in its own
+//   TMEM, its half of the epilogue) and loads Q rows q0+128r.. (its half of B); the 256-row MMA issued by
+//   the even CTA reads A from both CTAs' shared memory and the two halves of B from the CTA that holds them.
+//
+// Per K-block of 128 each SM therefore loads 128+128 rows (24 KB of packed fp6) instead of 128+256, and a
+// pipeline stage is 32 KB, so 6 stages fit where the single-CTA kernel has 4.
+//
+// Synchronisation (all mbarriers live in shared memory of the CTA named):
+//   full[s]      even CTA   1 arrival (+ bytes of both CTAs' TMA loads)        waited by the MMA thread
+//   empty[s]     each CTA   1 arrival by multicast tcgen05.commit               waited by that CTA's producer
+//   raw_full/raw_empty[r]  each CTA, local scale-slab ring
+//   atom_full[g] even CTA   64 arrivals (scale warp lanes of both CTAs), one per group of 4 K-blocks
+//   atom_empty[g] each CTA  1 arrival by multicast commit
+//   acc_full[b]  each CTA   1 arrival by multicast commit                       waited by that CTA's epilogue
+//   ovl          even CTA   256 arrivals (epilogue threads of both CTAs)        waited by the MMA thread
+#pragma once
+#include "gemm_kernel.cuh"
+
+namespace mxfp6 {
+
+struct PairCfg {
+    static constexpr int BM = 128;                        // P rows per CTA (256 per pair)
+    static constexpr int BN = 256;                        // Q rows per pair (128 loaded by each CTA)
+    static constexpr int BK = 128;
+    static constexpr int P_BYTES = BM * BK;               // 16 KB
+    static constexpr int Q_BYTES = (BN / 2) * BK;         // 16 KB: this CTA's half of B
+    static constexpr int STAGE_BYTES = P_BYTES + Q_BYTES;
+    static constexpr int STAGES = 6;
+    static constexpr int RAW_SLOTS = 2;
+    static constexpr int RAW_BYTES = (BM + BN) * 16;      // own P rows + all 256 Q rows, 16 scale bytes each
+    static constexpr int ATOM_BYTES = 512 * 3;            // P atom + two Q atoms of one K-block
+    static constexpr int GROUP_BYTES = 4 * ATOM_BYTES;    // the 4 K-blocks one raw slab covers
+    static constexpr int ATOM_GROUPS = 3;
+    static constexpr int ACC_COL1 = 224;
+    static constexpr int SF_COL = 480;
+    static constexpr int TMEM_COLS = 512;
+    static constexpr int NUM_BARS = 2 * STAGES + 2 * RAW_SLOTS + 2 * ATOM_GROUPS + 3;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + RAW_SLOTS * RAW_BYTES + ATOM_GROUPS * GROUP_BYTES +
+                                      NUM_BARS * 8 + 64;
+    static constexpr int SMEM_ALLOC = SMEM_BYTES + 1024;
+    static constexpr int THREADS = 256;
+    static constexpr int GROUP_P = 4;                     // rasterisation: 4 pair-tiles (1024 rows) share Q tiles
+    static_assert(SMEM_ALLOC <= 232448, "exceeds the shared memory of a CTA");
+};
+
+// bounded wait on a barrier that CTAs of the pair arrive on remotely
+__device__ __forceinline__ bool wait_bar_cluster(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                                 const GemmParams& P, int code) {
+    if (mbar_try_wait_cluster(bar, parity)) return true;
+    long long t0 = clock64();
+    uint32_t n = 0;
+    while (!mbar_try_wait_cluster(bar, parity)) {
+        if ((++n & 255u) == 0) {
+            if (*abort_flag) return false;
+            if ((unsigned long long)(clock64() - t0) > P.wait_cycles) {
+                *abort_flag = 1;
+                atomicCAS(P.status, 0, code | ((int)blockIdx.x << 8));
+                return false;
+            }
+        }
+    }
+    return true;
+}
+__device__ __forceinline__ bool wait_bar_cluster_warp(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                                      const GemmParams& P, int code) {
+    return __all_sync(0xffffffffu, wait_bar_cluster(bar, parity, abort_flag, P, code));
+}
+
+// Pair tile t -> first P row / Q row of the pair.  tiles_p/tiles_q in P count 256x256 pair tiles.
+__device__ __forceinline__ void pair_coords(const GemmParams& P, int t, int& p0, int& q0) {
+    const int per_group = PairCfg::GROUP_P * P.tiles_q;
+    const int group = t / per_group, in = t % per_group;
+    const int first_p = group * PairCfg::GROUP_P;
+    const int gsz = min(P.tiles_p - first_p, PairCfg::GROUP_P);
+    p0 = (first_p + in % gsz) * 256;
+    q0 = (in / gsz) * 256;
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PairCfg::THREADS, 1)
+mxfp6_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__ CUtensorMap tm_q,
+                       const __grid_constant__ CUtensorMap tm_sfp, const __grid_constant__ CUtensorMap tm_sfq,
+                       const GemmParams P) {
+    using Cfg = PairCfg;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+
+    const uint32_t stage_base = smem_base;
+    const uint32_t raw_base = stage_base + Cfg::STAGES * Cfg::STAGE_BYTES;
+    const uint32_t atom_base = raw_base + Cfg::RAW_SLOTS * Cfg::RAW_BYTES;
+    const uint32_t bar_base = atom_base + Cfg::ATOM_GROUPS * Cfg::GROUP_BYTES;
+    auto bar_full = [&](int s) { return bar_base + 8u * s; };
+    auto bar_empty = [&](int s) { return bar_base + 8u * (Cfg::STAGES + s); };
+    auto bar_raw_full = [&](int s) { return bar_base + 8u * (2 * Cfg::STAGES + s); };
+    auto bar_raw_empty = [&](int s) { return bar_base + 8u * (2 * Cfg::STAGES + Cfg::RAW_SLOTS + s); };
+    auto bar_atom_full = [&](int s) { return bar_base + 8u * (2 * Cfg::STAGES + 2 * Cfg::RAW_SLOTS + s); };
+    auto bar_atom_empty = [&](int s) { return bar_base + 8u * (2 * Cfg::STAGES + 2 * Cfg::RAW_SLOTS + Cfg::ATOM_GROUPS + s); };
+    const uint32_t bar_misc = bar_base + 8u * (2 * Cfg::STAGES + 2 * Cfg::RAW_SLOTS + 2 * Cfg::ATOM_GROUPS);
+    auto bar_acc_full = [&](int b) { return bar_misc + 8u * b; };
+    const uint32_t bar_ovl = bar_misc + 8u * 2;
+    const uint32_t misc_off = (bar_base - smem_base) + Cfg::NUM_BARS * 8;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_gen + misc_off);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + misc_off + 4);
+    const uint32_t abort_addr = smem_base + misc_off + 4;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();              // 0 = even CTA (issues the MMAs), 1 = its peer
+    const bool leader = rank == 0;
+    const int cluster_id = blockIdx.x >> 1, n_clusters = gridDim.x >> 1;
+    const int num_tiles = P.tiles_p * P.tiles_q;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < Cfg::STAGES; ++s) { mbar_init(bar_full(s), 1); mbar_init(bar_empty(s), 1); }
+        for (int s = 0; s < Cfg::RAW_SLOTS; ++s) { mbar_init(bar_raw_full(s), 1); mbar_init(bar_raw_empty(s), 32); }
+        for (int s = 0; s < Cfg::ATOM_GROUPS; ++s) { mbar_init(bar_atom_full(s), 64); mbar_init(bar_atom_empty(s), 1); }
+        for (int b = 0; b < 2; ++b) mbar_init(bar_acc_full(b), 1);
+        mbar_init(bar_ovl, 256);
+        *abort_flag = 0;
+        fence_barrier_init();
+    }
+    if (warp == 0 && lane == 0) {
+        tma_prefetch_desc(&tm_p); tma_prefetch_desc(&tm_q); tma_prefetch_desc(&tm_sfp); tma_prefetch_desc(&tm_sfq);
+    }
+    if (warp == 1) {
+        tmem_alloc_pair(smem_u32(tmem_slot), Cfg::TMEM_COLS);
+        tmem_relinquish_pair();
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_arrive();            // barriers of both CTAs are initialised before anyone signals the peer
+    cluster_wait();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    auto signal_abort_to_peer = [&]() { st_shared_cluster_u32(mapa_shared(abort_addr, rank ^ 1), 1u); };
+
+    // =========================================================== warp 0: TMA producer (both CTAs)
+    if (warp == 0) {
+        uint32_t n_stage = 0, n_raw = 0;
+        bool ok = true;
+        for (int tile = cluster_id; tile < num_tiles && ok; tile += n_clusters) {
+            int p0, q0;
+            pair_coords(P, tile, p0, q0);
+            const int my_p = p0 + 128 * (int)rank, my_q = q0 + 128 * (int)rank;
+            for (int kb = 0; kb < P.kblocks && ok; ++kb) {
+#ifdef MXFP6_DEBUG_KNOBS
+                if ((kb & 3) == 0 && (P.dbg & 64) && n_raw >= (uint32_t)Cfg::ATOM_GROUPS) { ++n_raw; } else
+#endif
+                if ((kb & 3) == 0) {
+                    const int r = n_raw % Cfg::RAW_SLOTS;
+                    ok = wait_bar_warp(bar_raw_empty(r), ((n_raw / Cfg::RAW_SLOTS) & 1) ^ 1, abort_flag, P, kStatusTimeoutProducer);
+                    if (!ok) break;
+                    if (elect_one_sync()) {
+                        const uint32_t dst = raw_base + r * Cfg::RAW_BYTES;
+                        mbar_arrive_expect_tx(bar_raw_full(r), Cfg::RAW_BYTES);
+                        tma_load_2d(dst, &tm_sfp, bar_raw_full(r), (kb >> 2) * 16, my_p);
+                        tma_load_2d(dst + Cfg::BM * 16, &tm_sfq, bar_raw_full(r), (kb >> 2) * 16, q0);
+                    }
+                    ++n_raw;
+                }
+                const int s = n_stage % Cfg::STAGES;
+#ifdef MXFP6_DEBUG_KNOBS
+                if ((P.dbg & 4) && n_stage >= (uint32_t)Cfg::STAGES) { ++n_stage; continue; }
+#endif
+                ok = wait_bar_warp(bar_empty(s), ((n_stage / Cfg::STAGES) & 1) ^ 1, abort_flag, P, kStatusTimeoutProducer);
+                if (!ok) break;
+                if (elect_one_sync()) {
+                    const uint32_t dst = stage_base + s * Cfg::STAGE_BYTES;
+                    const uint32_t full0 = mapa_shared(bar_full(s), 0);
+                    // the even CTA announces the bytes of both CTAs' loads for this stage
+                    if (leader) mbar_arrive_expect_tx(bar_full(s), 2u * (uint32_t)P.stage_tx_bytes);
+                    tma_load_2d_pair(dst, &tm_p, full0, kb * Cfg::BK, my_p);
+                    tma_load_2d_pair(dst + Cfg::P_BYTES, &tm_q, full0, kb * Cfg::BK, my_q);
+                }
+                __syncwarp();
+                ++n_stage;
+            }
+        }
+        if (!ok && lane == 0) signal_abort_to_peer();
+    }
+    // =========================================================== warp 1: MMA issuer (even CTA only)
+    else if (warp == 1) {
+        if (leader) {
+            uint32_t n_kb = 0, n_seg = 0, n_grp = 0;
+            bool ok = true;
+            for (int tile = cluster_id; tile < num_tiles && ok; tile += n_clusters) {
+                const int b = n_seg & 1;
+                const uint32_t acc = tmem_base + (b ? Cfg::ACC_COL1 : 0);
+                if (n_seg > 0) ok = wait_bar_cluster_warp(bar_ovl, (n_seg - 1) & 1, abort_flag, P, kStatusTimeoutMma);
+                if (!ok) break;
+                tc_fence_after();
+                for (int kb = 0; kb < P.kblocks; ++kb) {
+                    const int s = n_kb % Cfg::STAGES;
+                    const int g = n_grp % Cfg::ATOM_GROUPS;
+#ifdef MXFP6_DEBUG_KNOBS
+                    if ((kb & 3) == 0 && !((P.dbg & 64) && n_grp >= (uint32_t)Cfg::ATOM_GROUPS))
+#else
+                    if ((kb & 3) == 0)
+#endif
+                        ok = wait_bar_cluster_warp(bar_atom_full(g), (n_grp / Cfg::ATOM_GROUPS) & 1, abort_flag, P, kStatusTimeoutMma);
+#ifdef MXFP6_DEBUG_KNOBS
+                    const bool skip_full = (P.dbg & 4) && n_kb >= (uint32_t)Cfg::STAGES;
+                    ok = ok && (skip_full || wait_bar_warp(bar_full(s), (n_kb / Cfg::STAGES) & 1, abort_flag, P, kStatusTimeoutMma));
+#else
+                    ok = ok && wait_bar_warp(bar_full(s), (n_kb / Cfg::STAGES) & 1, abort_flag, P, kStatusTimeoutMma);
+#endif
+                    if (!ok) break;
+                    const bool group_done = (kb & 3) == 3 || kb == P.kblocks - 1;
+                    if (elect_one_sync()) {
+                        const uint32_t sfa = tmem_base + Cfg::SF_COL + (n_kb & 1) * 16;
+                        const uint32_t sfb = sfa + 4;
+                        const uint32_t atom = atom_base + g * Cfg::GROUP_BYTES + (kb & 3) * Cfg::ATOM_BYTES;
+#ifdef MXFP6_DEBUG_KNOBS
+                        if (!(P.dbg & 1) || kb == 0)
+#endif
+                        {
+                        tc_cp_32x128b_warpx4_pair(sfa, smem_desc_sf(atom));
+                        tc_cp_32x128b_warpx4_pair(sfb, smem_desc_sf(atom + 512));
+                        tc_cp_32x128b_warpx4_pair(sfb + 4, smem_desc_sf(atom + 1024));
+                        }
+                        const uint32_t sp = stage_base + s * Cfg::STAGE_BYTES;
+                        const uint64_t adesc = smem_desc_sw128(sp);
+                        const uint64_t bdesc = smem_desc_sw128(sp + Cfg::P_BYTES);
+#pragma unroll
+                        for (uint32_t k = 0; k < 4; ++k) {
+#ifdef MXFP6_DEBUG_KNOBS
+                            if ((P.dbg & 16) && k > 0) break;
+#endif
+                            mma_mxf8f6f4_pair(acc, adesc + 2 * k, bdesc + 2 * k, idesc_with_sf(P.idesc, k),
+                                              sfa | (k << 30), sfb | (k << 30), (kb > 0 || k > 0) ? 1u : 0u);
+                        }
+#ifdef MXFP6_DEBUG_KNOBS
+                        if (!((P.dbg & 32) && (P.dbg & 4) && n_kb >= (uint32_t)Cfg::STAGES)) tc_commit_pair(bar_empty(s), 3);
+                        if (group_done && !(P.dbg & 64)) tc_commit_pair(bar_atom_empty(g), 3);
+#else
+                        tc_commit_pair(bar_empty(s), 3);
+                        if (group_done) tc_commit_pair(bar_atom_empty(g), 3);
+#endif
+                    }
+                    __syncwarp();
+                    ++n_kb;
+                    if (group_done) ++n_grp;
+                }
+                if (!ok) break;
+                if (elect_one_sync()) tc_commit_pair(bar_acc_full(b), 3);
+                __syncwarp();
+                ++n_seg;
+            }
+            if (!ok && lane == 0) signal_abort_to_peer();
+        }
+    }
+    // =========================================================== warps 2-3: scale re-tilers (both CTAs)
+    // groups of 4 K-blocks alternate between the two warps; each CTA builds the atoms of its own P rows and
+    // of all 256 Q rows (the scale copy into TMEM runs in both CTAs from their own shared memory)
+    else if (warp == 2 || warp == 3) {
+        uint32_t n_grp = 0;
+        bool ok = true;
+        for (int tile = cluster_id; tile < num_tiles && ok; tile += n_clusters) {
+            for (int kb = 0; kb < P.kblocks && ok; kb += 4, ++n_grp) {
+                if ((int)(n_grp & 1) != warp - 2) continue;
+#ifdef MXFP6_DEBUG_KNOBS
+                if ((P.dbg & 64) && n_grp >= (uint32_t)Cfg::ATOM_GROUPS) continue;
+#endif
+                uint32_t rp[4][4], rq[8][4];
+                const int r = n_grp % Cfg::RAW_SLOTS;
+                ok = wait_bar_warp(bar_raw_full(r), (n_grp / Cfg::RAW_SLOTS) & 1, abort_flag, P, kStatusTimeoutScale);
+                if (!ok) break;
+                const uint8_t* raw = smem_gen + (raw_base - smem_base) + r * Cfg::RAW_BYTES;
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    const uint4 v = *reinterpret_cast<const uint4*>(raw + (lane + 32 * c) * 16);
+                    rp[c][0] = v.x; rp[c][1] = v.y; rp[c][2] = v.z; rp[c][3] = v.w;
+                }
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    const uint4 v = *reinterpret_cast<const uint4*>(raw + Cfg::BM * 16 + (lane + 32 * c) * 16);
+                    rq[c][0] = v.x; rq[c][1] = v.y; rq[c][2] = v.z; rq[c][3] = v.w;
+                }
+                mbar_arrive(bar_raw_empty(r));
+                const int g = n_grp % Cfg::ATOM_GROUPS;
+                ok = wait_bar_warp(bar_atom_empty(g), ((n_grp / Cfg::ATOM_GROUPS) & 1) ^ 1, abort_flag, P, kStatusTimeoutScale);
+                if (!ok) break;
+                uint8_t* grp = smem_gen + (atom_base - smem_base) + g * Cfg::GROUP_BYTES;
+#pragma unroll
+                for (int jj = 0; jj < 4; ++jj) {
+                    uint8_t* atom = grp + jj * Cfg::ATOM_BYTES;
+                    *reinterpret_cast<uint4*>(atom + lane * 16) = make_uint4(rp[0][jj], rp[1][jj], rp[2][jj], rp[3][jj]);
+                    *reinterpret_cast<uint4*>(atom + 512 + lane * 16) = make_uint4(rq[0][jj], rq[1][jj], rq[2][jj], rq[3][jj]);
+                    *reinterpret_cast<uint4*>(atom + 1024 + lane * 16) = make_uint4(rq[4][jj], rq[5][jj], rq[6][jj], rq[7][jj]);
+                }
+                fence_proxy_async_smem();
+                mbar_arrive_cluster(mapa_shared(bar_atom_full(g), 0));
+            }
+        }
+        if (!ok && lane == 0) signal_abort_to_peer();
+    }
+    // =========================================================== warps 4-7: epilogue (both CTAs)
+    else if (warp >= 4) {
+        const int quad = warp & 3;
+        const int prow = quad * 32 + lane;
+        uint32_t n_seg = 0;
+        bool ok = true;
+        const uint32_t ovl0 = mapa_shared(bar_ovl, 0);
+        const bool vec = ((P.ldc & 7) == 0) && ((reinterpret_cast<uintptr_t>(P.c) & 15) == 0);
+        for (int tile = cluster_id; tile < num_tiles && ok; tile += n_clusters) {
+            int p0, q0;
+            pair_coords(P, tile, p0, q0);
+            const int b = n_seg & 1;
+            ok = wait_bar_warp(bar_acc_full(b), (n_seg >> 1) & 1, abort_flag, P, kStatusTimeoutEpilogue);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t tacc = tmem_base + ((uint32_t)(quad * 32) << 16) + (b ? Cfg::ACC_COL1 : 0);
+            const int p = p0 + 128 * (int)rank + prow;
+#pragma unroll 1
+            for (int ci = 0; ci < 8; ++ci) {
+                const int ch = b == 0 ? (ci + 7) % 8 : ci;          // the 32 shared columns are drained first
+                uint32_t v[32];
+                tmem_ld_x32(tacc + ch * 32, v);
+                tmem_ld_wait();
+                if (ci == 0) { tc_fence_before(); mbar_arrive_cluster(ovl0); }
+                const int qc = q0 + ch * 32;
+#ifdef MXFP6_DEBUG_KNOBS
+                if (P.dbg & 8) continue;
+#endif
+                if (p < P.c_rows) {
+                    __nv_bfloat16* dst = P.c + (size_t)p * P.ldc + qc;
+#pragma unroll
+                    for (int i = 0; i < 32; i += 8) {
+                        if (vec && qc + i + 8 <= P.c_cols) {
+                            uint4 o;
+                            o.x = pack_bf16x2(__uint_as_float(v[i + 0]), __uint_as_float(v[i + 1]));
+                            o.y = pack_bf16x2(__uint_as_float(v[i + 2]), __uint_as_float(v[i + 3]));
+                            o.z = pack_bf16x2(__uint_as_float(v[i + 4]), __uint_as_float(v[i + 5]));
+                            o.w = pack_bf16x2(__uint_as_float(v[i + 6]), __uint_as_float(v[i + 7]));
+                            *reinterpret_cast<uint4*>(dst + i) = o;
+                        } else {
+#pragma unroll
+                            for (int e = 0; e < 8; ++e)
+                                if (qc + i + e < P.c_cols) dst[i + e] = __float2bfloat16_rn(__uint_as_float(v[i + e]));
+                        }
+                    }
+                }
+            }
+            ++n_seg;
+        }
+        if (!ok && lane == 0) signal_abort_to_peer();
+    }
+
+    // ---- teardown
+    if (*abort_flag) {
+        const long long t0 = clock64();
+        while (clock64() - t0 < 400000) { __nanosleep(1000); }
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_arrive();            // neither CTA frees TMEM or exits while its peer may still touch it
+    cluster_wait();
+    tc_fence_after();
+    if (warp == 1) tmem_dealloc_pair(tmem_base, Cfg::TMEM_COLS);
+}
+
+}  // namespace mxfp6

@@ -16,7 +16,7 @@
 #include <string>
 #include <tuple>
 
-#include "gemm_kernel.cuh"
+#include "gemm_kernel_2cta.cuh"
 
 namespace mxfp6 {
 
@@ -135,6 +135,7 @@ static int make_map(const void* ptr, int64_t rows, int64_t inner, int box_rows, 
 // ---------------------------------------------------------------------------------- GEMM dispatch
 struct Plan {
     int bn; bool swap; bool streamk;
+    bool pair;                  // CTA-pair kernel (256x256 tile per cluster of 2)
     int grid;
     int tiles_p, tiles_q;
     int ws_slots;
@@ -146,12 +147,12 @@ static int ceil_div(int64_t a, int64_t b) { return (int)((a + b - 1) / b); }
 // Most output tiles a problem may have and still split tiles along K (bounds the counter region).
 constexpr int64_t kMaxSplitTiles = 65536;
 
-static Plan make_plan(int64_t M, int64_t N, int64_t K, int sm_count) {
+static Plan make_plan(int64_t M, int64_t N, int64_t K, int sm_count, bool allow_pair = true) {
     Plan p{};
     const int kb = (int)(K / 128);
-    const char* force = getenv("MXFP6_FORCE_CFG");   // "bn,swap,streamk", for tests
-    int fbn = 0, fswap = -1, fsk = -1;
-    if (force) sscanf(force, "%d,%d,%d", &fbn, &fswap, &fsk);
+    const char* force = getenv("MXFP6_FORCE_CFG");   // "bn,swap,streamk[,pair]", for tests
+    int fbn = 0, fswap = -1, fsk = -1, fpair = -1;
+    if (force) sscanf(force, "%d,%d,%d,%d", &fbn, &fswap, &fsk, &fpair);
     if (M <= 128 && N > M) {
         p.swap = true;
         p.streamk = (int64_t)ceil_div(N, 128) <= kMaxSplitTiles;
@@ -161,18 +162,28 @@ static Plan make_plan(int64_t M, int64_t N, int64_t K, int sm_count) {
         const int64_t t256 = (int64_t)ceil_div(M, 128) * ceil_div(N, 256);
         p.bn = (N >= 256 && t256 >= sm_count) ? 256 : 128;
     }
-    if (fbn) p.bn = fbn;
-    if (fswap >= 0) p.swap = fswap != 0;
-    if (fsk >= 0) p.streamk = fsk != 0;
+    // large problems: one 256x256 tile per CTA pair, if that still fills every pair at least once
+    p.pair = !p.swap && p.bn == 256 && (K / 32) % 16 == 0 &&
+             (int64_t)ceil_div(M, 256) * ceil_div(N, 256) >= sm_count / 2;
+    if (fbn) { p.bn = fbn; p.pair = false; }
+    if (fpair >= 0) p.pair = fpair != 0;
+    if (!allow_pair) p.pair = false;      // the pair kernel takes its scales by TMA only
+    if (p.pair) { p.bn = 256; p.swap = false; p.streamk = false; }
+    if (fswap >= 0 && !p.pair) p.swap = fswap != 0;
+    if (fsk >= 0 && !p.pair) p.streamk = fsk != 0;
     {
         const int64_t t = (int64_t)ceil_div(p.swap ? N : M, 128) * ceil_div(p.swap ? M : N, p.bn);
         if (t > kMaxSplitTiles) p.streamk = false;
     }
     const int64_t prow = p.swap ? N : M, qrow = p.swap ? M : N;
-    p.tiles_p = ceil_div(prow, 128);
+    p.tiles_p = ceil_div(prow, p.pair ? 256 : 128);
     p.tiles_q = ceil_div(qrow, p.bn);
     const int64_t tiles = (int64_t)p.tiles_p * p.tiles_q;
-    if (p.streamk) {
+    if (p.pair) {
+        const int64_t clusters = tiles < sm_count / 2 ? tiles : sm_count / 2;
+        p.grid = (int)(2 * clusters);
+        p.ws_slots = 0; p.ws_counter_bytes = 0; p.ws_bytes = 0;
+    } else if (p.streamk) {
         const int64_t U = tiles * kb;
         int64_t g = U / 4; if (g < 1) g = 1;
         p.grid = (int)(g < sm_count ? g : sm_count);
@@ -227,7 +238,8 @@ static int gemm_impl(const void* a, const void* sfa, const void* b, const void* 
     int rc = get_device_state(&dp);
     if (rc) return rc;
     DeviceState& d = *dp;
-    Plan pl = make_plan(M, N, K, d.sm_count);
+    const bool sf_tma_ok = ((K / 32) % 16 == 0) && !((uintptr_t)sfa & 15) && !((uintptr_t)sfb & 15) && !env_int("MXFP6_NO_SF_TMA", 0);
+    Plan pl = make_plan(M, N, K, d.sm_count, sf_tma_ok);
 
     if (pl.ws_bytes) {
         if (own_ws) {
@@ -253,11 +265,11 @@ static int gemm_impl(const void* a, const void* sfa, const void* b, const void* 
 
     CUtensorMap tp, tq, tsp, tsq;
     if ((rc = make_map(pp, prow, K, 128, 0, &tp))) return rc;
-    if ((rc = make_map(qp, qrow, K, pl.bn, 0, &tq))) return rc;
-    const bool sf_tma = ((K / 32) % 16 == 0) && !((uintptr_t)sp & 15) && !((uintptr_t)sq & 15) && !env_int("MXFP6_NO_SF_TMA", 0);
+    const bool sf_tma = sf_tma_ok;
+    if ((rc = make_map(qp, qrow, K, pl.pair ? 128 : pl.bn, 0, &tq))) return rc;
     if (sf_tma) {
         if ((rc = make_map(sp, prow, K / 32, 128, 1, &tsp))) return rc;
-        if ((rc = make_map(sq, qrow, K / 32, pl.bn, 1, &tsq))) return rc;
+        if ((rc = make_map(sq, qrow, K / 32, pl.bn, 1, &tsq))) return rc;   // pair kernel: all 256 Q rows per CTA
     } else {
         tsp = tp; tsq = tq;   // unused by the kernel in this mode
     }
@@ -267,10 +279,11 @@ static int gemm_impl(const void* a, const void* sfa, const void* b, const void* 
     P.kblocks = (int)(K / 128);
     P.tiles_p = pl.tiles_p; P.tiles_q = pl.tiles_q;
     P.ldc = (int)N; P.c_rows = (int)M; P.c_cols = (int)N;
-    P.idesc = make_idesc(fp == MXFP6_E2M3 ? kFmtE2M3 : kFmtE3M2, fq == MXFP6_E2M3 ? kFmtE2M3 : kFmtE3M2, (uint32_t)pl.bn);
+    P.idesc = make_idesc_m(fp == MXFP6_E2M3 ? kFmtE2M3 : kFmtE3M2, fq == MXFP6_E2M3 ? kFmtE2M3 : kFmtE3M2,
+                           pl.pair ? 256u : 128u, (uint32_t)pl.bn);
     P.sf_tma = sf_tma ? 1 : 0;
     P.sf_ld = (int)(K / 32);
-    P.stage_tx_bytes = (128 + pl.bn) * env_int("MXFP6_TX_BYTES_PER_ROW", 96);
+    P.stage_tx_bytes = (128 + (pl.pair ? 128 : pl.bn)) * env_int("MXFP6_TX_BYTES_PER_ROW", 96);
     P.sfp = (const uint8_t*)sp; P.sfq = (const uint8_t*)sq;
     P.c = (__nv_bfloat16*)c;
     P.ws_counter = (unsigned int*)ws;
@@ -278,7 +291,21 @@ static int gemm_impl(const void* a, const void* sfa, const void* b, const void* 
     P.ws_slots = pl.ws_slots;
     P.status = d.status;
     P.wait_cycles = d.wait_cycles;
+    P.dbg = env_int("MXFP6_DBG", 0);
 
+ if (pl.pair) {
+        auto kern = mxfp6_gemm_pair_kernel;
+        {
+            std::lock_guard<std::mutex> lk(g_mu);
+            if (!d.smem_attr_set[(const void*)kern]) {
+                CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, PairCfg::SMEM_ALLOC));
+                d.smem_attr_set[(const void*)kern] = true;
+            }
+        }
+        kern<<<pl.grid, PairCfg::THREADS, PairCfg::SMEM_ALLOC, st>>>(tp, tq, tsp, tsq, P);
+        CUDA_TRY(cudaGetLastError());
+        return MXFP6_OK;
+    }
 #define MXFP6_CASE(BN_, SWAP_, SK_)                                                              \
     if (pl.bn == BN_ && pl.swap == SWAP_ && pl.streamk == SK_)                                   \
         return launch_cfg<GemmCfg<BN_, SWAP_, SK_>>(d, pl, tp, tq, tsp, tsq, P, st);
