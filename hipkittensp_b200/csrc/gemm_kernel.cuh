@@ -62,7 +62,8 @@ struct GemmCfg {
     static constexpr int P_BYTES = BM * BK;
     static constexpr int Q_BYTES = BN * BK;
     static constexpr int STAGE_BYTES = P_BYTES + Q_BYTES;
-    static constexpr int STAGES = BN >= 256 ? 4 : BN >= 128 ? 6 : BN >= 64 ? 8 : BN >= 32 ? 9 : 10;
+    static constexpr int STAGES = BN >= 256 ? 4 : BN >= 128 ? 6 : BN >= 64 ? 8 : BN >= 32 ? 9 : 11;
+    static constexpr int LOAD_BATCH = SWAP_ ? (STAGES >= 8 ? 4 : 2) : 1;   // K-blocks the producer requests together
     static constexpr int QATOMS = (BN + 127) / 128;      // 128-row scale atoms on the Q side
     static constexpr int RAW_SLOTS = BN >= 256 ? 2 : 4;  // each raw slab covers 4 K-blocks (16 scale bytes per row)
     static constexpr int RAW_Q_ROWS = BN < 32 ? 32 : BN;
@@ -94,17 +95,22 @@ template <class Cfg>
 struct SegIter {
     const GemmParams& P;
     int num_tiles;
-    long long u, u_end;          // STREAMK: current / last K-block unit of this CTA
+    long long u_begin, u_end;    // STREAMK: this CTA's range of K-block units (tile-major)
+    int first_tile, nsegs, i;    // STREAMK: tiles the range touches; next position in the visiting order
     int tile;                    // !STREAMK: current tile
     __device__ SegIter(const GemmParams& p) : P(p) {
         num_tiles = P.tiles_p * P.tiles_q;
+        u_begin = u_end = 0; first_tile = nsegs = i = 0; tile = 0;
         if (Cfg::STREAMK) {
-            long long U = (long long)num_tiles * P.kblocks;
-            u = (U * blockIdx.x) / gridDim.x;
+            const long long U = (long long)num_tiles * P.kblocks;
+            u_begin = (U * blockIdx.x) / gridDim.x;
             u_end = (U * (blockIdx.x + 1)) / gridDim.x;
+            if (u_end > u_begin) {
+                first_tile = (int)(u_begin / P.kblocks);
+                nsegs = (int)((u_end - 1) / P.kblocks) - first_tile + 1;
+            }
         } else {
             tile = blockIdx.x;
-            u = u_end = 0;
         }
     }
     __device__ static int owner(long long unit, long long U, int G) { return (int)(((unit + 1) * G - 1) / U); }
@@ -118,18 +124,21 @@ struct SegIter {
     }
     __device__ bool next(Segment& s) {
         if (Cfg::STREAMK) {
-            if (u >= u_end) return false;
-            long long U = (long long)num_tiles * P.kblocks;
-            s.tile = (int)(u / P.kblocks);
-            s.k0 = (int)(u % P.kblocks);
-            long long left = u_end - u;
-            s.k1 = (int)min((long long)P.kblocks, s.k0 + left);
-            long long t0 = (long long)s.tile * P.kblocks;
-            int first = owner(t0, U, gridDim.x), last = owner(t0 + P.kblocks - 1, U, gridDim.x);
+            if (i >= nsegs) return false;
+            // Visiting order: the first and the last piece of the range (the ones that may share their tile
+            // with a neighbouring CTA) come first, whole tiles after them, so that split tiles are published
+            // and summed while the mainloop still runs and the kernel ends on a plain tile epilogue.
+            const int idx = i == 0 ? 0 : (i == 1 ? nsegs - 1 : i - 1);
+            ++i;
+            const long long U = (long long)num_tiles * P.kblocks;
+            s.tile = first_tile + idx;
+            const long long t0 = (long long)s.tile * P.kblocks;
+            s.k0 = idx == 0 ? (int)(u_begin - t0) : 0;
+            s.k1 = idx == nsegs - 1 ? (int)(u_end - t0) : P.kblocks;
+            const int first = owner(t0, U, gridDim.x), last = owner(t0 + P.kblocks - 1, U, gridDim.x);
             s.nseg = last - first + 1;
             s.segidx = (int)blockIdx.x - first;
             coords(s.tile, s.p0, s.q0);
-            u += s.k1 - s.k0;
             return true;
         } else {
             if (tile >= num_tiles) return false;
@@ -229,32 +238,56 @@ mxfp6_gemm_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constan
         uint32_t n_stage = 0, n_raw = 0;
         bool ok = true;
         while (ok && it.next(sg)) {
-            for (int kb = sg.k0; kb < sg.k1 && ok; ++kb) {
-                if (P.sf_tma && (kb == sg.k0 || (kb & 3) == 0)) {
-                    const int r = n_raw % Cfg::RAW_SLOTS;
-                    const uint32_t ph = (n_raw / Cfg::RAW_SLOTS) & 1;
-                    ok = wait_bar_warp(bar_raw_empty(r), ph ^ 1, abort_flag, P, kStatusTimeoutProducer);
-                    if (!ok) break;
-                    if (elect_one_sync()) {
-                        const uint32_t dst = raw_base + r * Cfg::RAW_BYTES;
-                        mbar_arrive_expect_tx(bar_raw_full(r), Cfg::RAW_TX_BYTES);
-                        tma_load_2d(dst, &tm_sfp, bar_raw_full(r), (kb >> 2) * 16, sg.p0);
-                        tma_load_2d(dst + Cfg::BM * 16, &tm_sfq, bar_raw_full(r), (kb >> 2) * 16, sg.q0);
+            for (int kb = sg.k0; kb < sg.k1 && ok;) {
+                // LOAD_BATCH K-blocks are requested back to back, so that each row's adjacent 96-byte pieces
+                // reach DRAM together (one page activation serves the whole run)
+                const int nb = min(Cfg::LOAD_BATCH, sg.k1 - kb);
+                for (int j = 0; j < nb && ok; ++j) {
+                    const int k = kb + j;
+                    if (P.sf_tma && (k == sg.k0 || (k & 3) == 0)) {
+                        const int r = n_raw % Cfg::RAW_SLOTS;
+                        const uint32_t ph = (n_raw / Cfg::RAW_SLOTS) & 1;
+                        ok = wait_bar_warp(bar_raw_empty(r), ph ^ 1, abort_flag, P, kStatusTimeoutProducer);
+                        if (!ok) break;
+                        if (elect_one_sync()) {
+                            const uint32_t dst = raw_base + r * Cfg::RAW_BYTES;
+                            mbar_arrive_expect_tx(bar_raw_full(r), Cfg::RAW_TX_BYTES);
+                            tma_load_2d(dst, &tm_sfp, bar_raw_full(r), (k >> 2) * 16, sg.p0);
+                            tma_load_2d(dst + Cfg::BM * 16, &tm_sfq, bar_raw_full(r), (k >> 2) * 16, sg.q0);
+                        }
+                        ++n_raw;
                     }
-                    ++n_raw;
                 }
-                const int s = n_stage % Cfg::STAGES;
-                const uint32_t ph = (n_stage / Cfg::STAGES) & 1;
-                ok = wait_bar_warp(bar_empty(s), ph ^ 1, abort_flag, P, kStatusTimeoutProducer);
+                if (!ok) break;
+                // stages are released in order: when the last one of the batch is free, all of them are
+                const uint32_t last = n_stage + nb - 1;
+                ok = wait_bar_warp(bar_empty(last % Cfg::STAGES), ((last / Cfg::STAGES) & 1) ^ 1, abort_flag, P, kStatusTimeoutProducer);
                 if (!ok) break;
                 if (elect_one_sync()) {
-                    const uint32_t dst = stage_base + s * Cfg::STAGE_BYTES;
-                    mbar_arrive_expect_tx(bar_full(s), (uint32_t)P.stage_tx_bytes);
-                    tma_load_2d(dst, &tm_p, bar_full(s), kb * Cfg::BK, sg.p0);
-                    tma_load_2d(dst + Cfg::P_BYTES, &tm_q, bar_full(s), kb * Cfg::BK, sg.q0);
+                    for (int j = 0; j < nb; ++j) {
+                        const int s = (n_stage + j) % Cfg::STAGES;
+                        const uint32_t dst = stage_base + s * Cfg::STAGE_BYTES;
+#ifdef MXFP6_DEBUG_KNOBS
+                        if ((P.dbg & 4) && n_stage + j >= (uint32_t)Cfg::STAGES) continue;
+                        if (P.dbg & 128) {        // P loads only
+                            mbar_arrive_expect_tx(bar_full(s), 128u * 96u);
+                            tma_load_2d(dst, &tm_p, bar_full(s), (kb + j) * Cfg::BK, sg.p0);
+                            continue;
+                        }
+                        if (P.dbg & 256) {        // Q loads only
+                            mbar_arrive_expect_tx(bar_full(s), (uint32_t)P.stage_tx_bytes - 128u * 96u);
+                            tma_load_2d(dst + Cfg::P_BYTES, &tm_q, bar_full(s), (kb + j) * Cfg::BK, sg.q0);
+                            continue;
+                        }
+#endif
+                        mbar_arrive_expect_tx(bar_full(s), (uint32_t)P.stage_tx_bytes);
+                        tma_load_2d(dst, &tm_p, bar_full(s), (kb + j) * Cfg::BK, sg.p0);
+                        tma_load_2d(dst + Cfg::P_BYTES, &tm_q, bar_full(s), (kb + j) * Cfg::BK, sg.q0);
+                    }
                 }
                 __syncwarp();
-                ++n_stage;
+                n_stage += nb;
+                kb += nb;
             }
         }
     }
@@ -280,6 +313,9 @@ mxfp6_gemm_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constan
                 // the scale atoms arrive per group of 4 K-blocks (one raw slab)
                 if (kb == sg.k0 || (kb & 3) == 0)
                     ok = wait_bar_warp(bar_atom_full(g), (n_grp / Cfg::ATOM_GROUPS) & 1, abort_flag, P, kStatusTimeoutMma);
+#ifdef MXFP6_DEBUG_KNOBS
+                if (!((P.dbg & 4) && n_kb >= (uint32_t)Cfg::STAGES))
+#endif
                 ok = ok && wait_bar_warp(bar_full(s), (n_kb / Cfg::STAGES) & 1, abort_flag, P, kStatusTimeoutMma);
                 if (!ok) break;
                 const bool group_done = (kb & 3) == 3 || kb == sg.k1 - 1;
@@ -287,17 +323,29 @@ mxfp6_gemm_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constan
                     const uint32_t sfa = tmem_base + Cfg::SF_COL + (n_kb & 1) * 16;
                     const uint32_t sfb = sfa + 4;
                     const uint32_t atom = atom_base + g * Cfg::GROUP_BYTES + (kb & 3) * Cfg::ATOM_BYTES;
+#ifdef MXFP6_DEBUG_KNOBS
+                    if (!(P.dbg & 1) || kb == sg.k0)
+#endif
+                    {
                     tc_cp_32x128b_warpx4(sfa, smem_desc_sf(atom));
 #pragma unroll
                     for (int q = 0; q < Cfg::QATOMS; ++q) tc_cp_32x128b_warpx4(sfb + 4 * q, smem_desc_sf(atom + 512 * (1 + q)));
+                    }
                     const uint32_t sp = stage_base + s * Cfg::STAGE_BYTES;
                     const uint64_t adesc = smem_desc_sw128(sp);
                     const uint64_t bdesc = smem_desc_sw128(sp + Cfg::P_BYTES);
 #pragma unroll
                     for (uint32_t k = 0; k < 4; ++k) {
+#ifdef MXFP6_DEBUG_KNOBS
+                        if ((P.dbg & 16) && k > 0) break;
+                        if (P.dbg & 512) break;
+#endif
                         mma_mxf8f6f4(acc, adesc + 2 * k, bdesc + 2 * k, idesc_with_sf(P.idesc, k),
                                      sfa | (k << 30), sfb | (k << 30), (kb > sg.k0 || k > 0) ? 1u : 0u);
                     }
+#ifdef MXFP6_DEBUG_KNOBS
+                    if (!(P.dbg & 1024))
+#endif
                     tc_commit(bar_empty(s));
                     if (group_done) tc_commit(bar_atom_empty(g));
                 }
@@ -465,16 +513,29 @@ mxfp6_gemm_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constan
                 asm volatile("bar.sync 1, 128;" ::: "memory");
                 if (last) {
                     __threadfence();
-                    const float* base = P.ws_partial + (size_t)sg.tile * P.ws_slots * (size_t)(BN * 128);
-                    for (int col = 0; col < BN; ++col) {
-                        float acc = 0.f;
-                        for (int sgi = 0; sgi < sg.nseg; ++sgi)
-                            acc += __ldcg(base + (size_t)sgi * (BN * 128) + (size_t)col * 128 + prow);
-                        const int q = sg.q0 + col;
-                        if (Cfg::SWAP) {
-                            if (p < P.c_cols && q < P.c_rows) P.c[(size_t)q * P.ldc + p] = __float2bfloat16_rn(acc);
-                        } else {
-                            if (p < P.c_rows && q < P.c_cols) P.c[(size_t)p * P.ldc + q] = __float2bfloat16_rn(acc);
+                    const float* base = P.ws_partial + (size_t)sg.tile * P.ws_slots * (size_t)(BN * 128) + prow;
+                    // 8 columns at a time: the loads of a chunk are independent and in flight together; each
+                    // element is still summed in slot order
+#pragma unroll 1
+                    for (int col0 = 0; col0 < BN; col0 += 8) {
+                        float acc[8];
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+                        for (int sgi = 0; sgi < sg.nseg; ++sgi) {
+                            float t[8];
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) t[j] = __ldcg(base + (size_t)sgi * (BN * 128) + (size_t)(col0 + j) * 128);
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) acc[j] += t[j];
+                        }
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            const int q = sg.q0 + col0 + j;
+                            if (Cfg::SWAP) {
+                                if (p < P.c_cols && q < P.c_rows) P.c[(size_t)q * P.ldc + p] = __float2bfloat16_rn(acc[j]);
+                            } else {
+                                if (p < P.c_rows && q < P.c_cols) P.c[(size_t)p * P.ldc + q] = __float2bfloat16_rn(acc[j]);
+                            }
                         }
                     }
                     if (etid == 0) P.ws_counter[sg.tile] = 0u;
