@@ -2,8 +2,10 @@
 tk_kernel Python extension (pybind11, same module/function names as the reference's binding,
 include/pyutils/pyutils.cuh:55-72 and kernels/gemm/bf16fp32/Makefile:41,51-52).
 
-    python -m hipkittensp_b200.build            # build what is out of date
-    python -m hipkittensp_b200.build --force
+    python hipkittensp_b200/build.py            # build what is out of date
+    python hipkittensp_b200/build.py --force
+
+(run as a script: importing the package needs the library this builds)
 """
 from __future__ import annotations
 
