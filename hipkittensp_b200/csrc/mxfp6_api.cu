@@ -454,6 +454,50 @@ extern "C" int mxfp6_gemm_ws(const void* a, const void* sfa, const void* b, cons
     return gemm_impl(a, sfa, b, sfb, c, M, N, K, fmt_a, fmt_b, workspace, workspace_bytes, false, stream);
 }
 
+// ---------------------------------------------------------------------------------- GEMM without allocation
+// Scratch that is part of the library image: every GPU that loads libmxfp6.so holds these 8 MiB until the
+// process exits.  In host code `g_builtin_scratch` is only a handle for the symbol, not a device address;
+// the address each device gave it is looked up once with cudaGetSymbolAddress and kept here.
+constexpr size_t kBuiltinScratchBytes = (size_t)8 << 20;
+static __device__ __align__(256) unsigned char g_builtin_scratch[kBuiltinScratchBytes];
+static void* g_builtin_scratch_addr[64];
+
+extern "C" int mxfp6_gemm_noalloc(const void* a, const void* sfa, const void* b, const void* sfb, void* c, int64_t M,
+                                  int64_t N, int64_t K, int fmt_a, int fmt_b, void* stream) {
+    // malformed or empty problems take the common path, which rejects or finishes them without any scratch
+    if (M <= 0 || N <= 0 || K <= 0 || K % 128 != 0)
+        return gemm_impl(a, sfa, b, sfb, c, M, N, K, fmt_a, fmt_b, nullptr, 0, false, stream);
+    DeviceState* d = nullptr;
+    int rc = get_device_state(&d);
+    if (rc) return rc;
+    int dev = 0;
+    CUDA_TRY(cudaGetDevice(&dev));
+    void* scratch = nullptr;
+    {
+        std::lock_guard<std::mutex> lk(g_mu);
+        if (!g_builtin_scratch_addr[dev]) {
+            // set-up, once per device, with that device current
+            void* p = nullptr;
+            CUDA_TRY(cudaGetSymbolAddress(&p, g_builtin_scratch));
+            g_builtin_scratch_addr[dev] = p;
+        }
+        scratch = g_builtin_scratch_addr[dev];
+    }
+    const bool sf_tma_ok = ((K / 32) % 16 == 0) && !((uintptr_t)sfa & 15) && !((uintptr_t)sfb & 15) && !env_int("MXFP6_NO_SF_TMA", 0);
+    const Plan pl = make_plan(M, N, K, d->sm_count, sf_tma_ok);
+    if (pl.ws_bytes > kBuiltinScratchBytes)
+        return fail(MXFP6_ERR_BAD_ARG,
+                    "mxfp6_gemm_noalloc: M=%lld N=%lld K=%lld needs %zu bytes of scratch but the built-in buffer holds %zu; "
+                    "use mxfp6_gemm or mxfp6_gemm_ws for this shape",
+                    (long long)M, (long long)N, (long long)K, pl.ws_bytes, kBuiltinScratchBytes);
+    if (pl.ws_bytes) {
+        // the buffer keeps whatever the previous call left: the arrival counters of this call's tiles must be zero
+        const size_t counters = (size_t)pl.tiles_p * pl.tiles_q * sizeof(unsigned int);
+        CUDA_TRY(cudaMemsetAsync(scratch, 0, counters, (cudaStream_t)stream));
+    }
+    return gemm_impl(a, sfa, b, sfb, c, M, N, K, fmt_a, fmt_b, scratch, kBuiltinScratchBytes, false, stream);
+}
+
 extern "C" int mxfp6_quantize(const void* src, int src_dtype, int64_t rows, int64_t K, int fmt, void* packed, void* scales,
                               void* stream) {
     if (rows < 0 || K < 0 || K % 32) return fail(MXFP6_ERR_BAD_ARG, "quantize: rows=%lld K=%lld (K must be a multiple of 32)", (long long)rows, (long long)K);

@@ -72,6 +72,24 @@ int mxfp6_gemm_ws(const void* a, const void* sfa, const void* b, const void* sfb
                   void* workspace, size_t workspace_bytes, void* stream);
 
 /*
+ * The same GEMM for hosts that must not allocate device memory while they run: servers that hand all of the
+ * GPU's memory to their own pool at start-up, control loops with a latency bound (cudaMalloc may synchronise
+ * the device, and may fail when memory is tight), or plug-ins whose host forbids allocation in the call path.
+ * Shapes that split output tiles along K take their scratch from an 8 MiB buffer built into the library image
+ * (held by every GPU that loads the library until the process exits) instead of cudaMalloc.  A shape that
+ * would need more is refused with MXFP6_ERR_BAD_ARG and a message that names both sizes; shapes that need no
+ * scratch are never refused.  This function calls neither cudaMalloc nor cudaFree nor any allocating
+ * library routine.  The first call on each device looks up the buffer's address and initialises the
+ * per-device state; make that first call with the device current and before any stream capture begins.
+ * All calls on a device share the one buffer: each call clears the counters it is about to use, on its
+ * stream, so the contents left by the previous call do not matter, but two calls that overlap on the GPU
+ * (different streams) would race on it -- serialise them or use mxfp6_gemm_ws with separate scratch.
+ * (No counterpart in the reference, which neither splits tiles nor allocates.)
+ */
+int mxfp6_gemm_noalloc(const void* a, const void* sfa, const void* b, const void* sfb, void* c,
+                       int64_t M, int64_t N, int64_t K, int fmt_a, int fmt_b, void* stream);
+
+/*
  * Block quantiser: src [rows, K] (src_dtype 0 = fp32, 1 = bf16), K % 32 == 0  ->
  * packed [rows, 3K/4] + scales [rows, K/32].  Scale exponent = floor(log2(amax)) - 2 (E2M3) or - 4
  * (E3M2), elements rounded to nearest even and saturated.  The step in front of the GEMM; the
