@@ -43,7 +43,9 @@ struct GemmParams {
     int stage_tx_bytes;        // bytes one operand stage reports to its mbarrier
     const uint8_t* sfp;        // scales of P / Q (row-major [rows, K/32])
     const uint8_t* sfq;
-    __nv_bfloat16* c;
+    __nv_bfloat16* c;          // first element of this GEMM's block inside destination 0 (row stride ldc)
+    __nv_bfloat16* c_more[7];  // the same position in further destinations (peer GPUs' copies of C)
+    int ndst;                  // number of destinations, 1..8
     float* ws_partial;         // split-tile partial sums: [tile][slot][BN][128] fp32
     unsigned int* ws_counter;  // per-tile arrival counters (zero between launches)
     int ws_slots;              // partial slots per tile
@@ -167,6 +169,19 @@ __device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, volatile
         }
     }
     return true;
+}
+
+// Agreement among the 128 epilogue threads (named barrier 1): true only if every one of them passes true.
+// The epilogue warps synchronise with each other inside a tile, so they must enter or skip it together.
+__device__ __forceinline__ bool epilogue_all(bool ok) {
+    uint32_t r;
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\t"
+        "setp.ne.u32 q, %1, 0;\n\t"
+        "bar.red.and.pred p, 1, 128, q;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(r) : "r"((uint32_t)ok) : "memory");
+    return r != 0;
 }
 
 // Same, for a whole converged warp: every lane waits, and all lanes agree on the outcome.
@@ -450,7 +465,7 @@ mxfp6_gemm_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constan
         constexpr int NCH = BN / CW;
         while (ok && it.next(sg)) {
             const int b = n_seg & 1;
-            ok = wait_bar_warp(bar_acc_full(b), (n_seg >> 1) & 1, abort_flag, P, kStatusTimeoutEpilogue);
+            ok = epilogue_all(wait_bar_warp(bar_acc_full(b), (n_seg >> 1) & 1, abort_flag, P, kStatusTimeoutEpilogue));
             if (!ok) break;
             tc_fence_after();
             const uint32_t tacc = tmem_base + ((uint32_t)(quad * 32) << 16) + (b ? Cfg::ACC_COL1 : 0);
@@ -481,9 +496,11 @@ mxfp6_gemm_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constan
                                 P.c[(size_t)(qc + i) * P.ldc + p] = __float2bfloat16_rn(__uint_as_float(v[i]));
                     }
                 } else {
-                    if (p < P.c_rows) {
-                        __nv_bfloat16* dst = P.c + (size_t)p * P.ldc + qc;
-                        const bool vec = ((P.ldc & 7) == 0) && ((reinterpret_cast<uintptr_t>(P.c) & 15) == 0);
+                    if (p < P.c_rows)
+                    for (int d = 0; d < P.ndst; ++d) {          // every destination gets the tile (d > 0: peer memory)
+                        __nv_bfloat16* cbase = d == 0 ? P.c : P.c_more[d - 1];
+                        __nv_bfloat16* dst = cbase + (size_t)p * P.ldc + qc;
+                        const bool vec = ((P.ldc & 7) == 0) && ((reinterpret_cast<uintptr_t>(cbase) & 15) == 0);
 #pragma unroll
                         for (int i = 0; i < CW; i += 8) {
                             if (vec && qc + i + 8 <= P.c_cols) {

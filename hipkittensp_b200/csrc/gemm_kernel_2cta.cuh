@@ -6,7 +6,10 @@
 //   the even CTA reads A from both CTAs' shared memory and the two halves of B from the CTA that holds them.
 //
 // Per K-block of 128 each SM therefore loads 128+128 rows (24 KB of packed fp6) instead of 128+256, and a
-// pipeline stage is 32 KB, so 6 stages fit where the single-CTA kernel has 4.
+// pipeline stage is 32 KB, so 5 stages plus two 16 KB output staging buffers fit where the single-CTA kernel
+// has 4 stages.  The epilogue packs bf16 into the staging buffers (128-byte swizzle) and one thread issues a
+// TMA store of each 128x64 piece to every destination of C: the local copy and, in the sharded
+// configuration, the copies held by the peer GPUs, so the gather travels with the tiles.
 //
 // Synchronisation (all mbarriers live in shared memory of the CTA named):
 //   full[s]      even CTA   1 arrival (+ bytes of both CTAs' TMA loads)        waited by the MMA thread
@@ -28,7 +31,9 @@ struct PairCfg {
     static constexpr int P_BYTES = BM * BK;               // 16 KB
     static constexpr int Q_BYTES = (BN / 2) * BK;         // 16 KB: this CTA's half of B
     static constexpr int STAGE_BYTES = P_BYTES + Q_BYTES;
-    static constexpr int STAGES = 6;
+    static constexpr int STAGES = 5;
+    static constexpr int OUT_COLS = 64;                   // columns of one output staging buffer (128 bytes of bf16)
+    static constexpr int OUT_BYTES = BM * OUT_COLS * 2;   // 16 KB, two of them
     static constexpr int RAW_SLOTS = 2;
     static constexpr int RAW_BYTES = (BM + BN) * 16;      // own P rows + all 256 Q rows, 16 scale bytes each
     static constexpr int ATOM_BYTES = 512 * 3;            // P atom + two Q atoms of one K-block
@@ -38,8 +43,8 @@ struct PairCfg {
     static constexpr int SF_COL = 480;
     static constexpr int TMEM_COLS = 512;
     static constexpr int NUM_BARS = 2 * STAGES + 2 * RAW_SLOTS + 2 * ATOM_GROUPS + 3;
-    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + RAW_SLOTS * RAW_BYTES + ATOM_GROUPS * GROUP_BYTES +
-                                      NUM_BARS * 8 + 64;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 2 * OUT_BYTES + RAW_SLOTS * RAW_BYTES +
+                                      ATOM_GROUPS * GROUP_BYTES + NUM_BARS * 8 + 64;
     static constexpr int SMEM_ALLOC = SMEM_BYTES + 1024;
     static constexpr int THREADS = 256;
     static constexpr int GROUP_P = 4;                     // rasterisation: 4 pair-tiles (1024 rows) share Q tiles
@@ -69,6 +74,11 @@ __device__ __forceinline__ bool wait_bar_cluster_warp(uint32_t bar, uint32_t par
     return __all_sync(0xffffffffu, wait_bar_cluster(bar, parity, abort_flag, P, code));
 }
 
+// Tensor maps of the destinations of C (this GEMM's [M,N] block inside each copy, bf16, box 64 x 128, 128-byte swizzle)
+struct CMaps {
+    CUtensorMap m[8];
+};
+
 // Pair tile t -> first P row / Q row of the pair.  tiles_p/tiles_q in P count 256x256 pair tiles.
 __device__ __forceinline__ void pair_coords(const GemmParams& P, int t, int& p0, int& q0) {
     const int per_group = PairCfg::GROUP_P * P.tiles_q;
@@ -82,14 +92,15 @@ __device__ __forceinline__ void pair_coords(const GemmParams& P, int t, int& p0,
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PairCfg::THREADS, 1)
 mxfp6_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__ CUtensorMap tm_q,
                        const __grid_constant__ CUtensorMap tm_sfp, const __grid_constant__ CUtensorMap tm_sfq,
-                       const GemmParams P) {
+                       const __grid_constant__ CMaps cmaps, const GemmParams P) {
     using Cfg = PairCfg;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
 
     const uint32_t stage_base = smem_base;
-    const uint32_t raw_base = stage_base + Cfg::STAGES * Cfg::STAGE_BYTES;
+    const uint32_t out_base = stage_base + Cfg::STAGES * Cfg::STAGE_BYTES;      // 1024-byte aligned
+    const uint32_t raw_base = out_base + 2 * Cfg::OUT_BYTES;
     const uint32_t atom_base = raw_base + Cfg::RAW_SLOTS * Cfg::RAW_BYTES;
     const uint32_t bar_base = atom_base + Cfg::ATOM_GROUPS * Cfg::GROUP_BYTES;
     auto bar_full = [&](int s) { return bar_base + 8u * s; };
@@ -301,51 +312,57 @@ mxfp6_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_co
     else if (warp >= 4) {
         const int quad = warp & 3;
         const int prow = quad * 32 + lane;
-        uint32_t n_seg = 0;
+        const int etid = threadIdx.x - 128;
+        uint32_t n_seg = 0, n_out = 0;
         bool ok = true;
         const uint32_t ovl0 = mapa_shared(bar_ovl, 0);
-        const bool vec = ((P.ldc & 7) == 0) && ((reinterpret_cast<uintptr_t>(P.c) & 15) == 0);
         for (int tile = cluster_id; tile < num_tiles && ok; tile += n_clusters) {
             int p0, q0;
             pair_coords(P, tile, p0, q0);
             const int b = n_seg & 1;
-            ok = wait_bar_warp(bar_acc_full(b), (n_seg >> 1) & 1, abort_flag, P, kStatusTimeoutEpilogue);
+            ok = epilogue_all(wait_bar_warp(bar_acc_full(b), (n_seg >> 1) & 1, abort_flag, P, kStatusTimeoutEpilogue));
             if (!ok) break;
             tc_fence_after();
             const uint32_t tacc = tmem_base + ((uint32_t)(quad * 32) << 16) + (b ? Cfg::ACC_COL1 : 0);
-            const int p = p0 + 128 * (int)rank + prow;
+            const int my_p0 = p0 + 128 * (int)rank;
 #pragma unroll 1
-            for (int ci = 0; ci < 8; ++ci) {
-                const int ch = b == 0 ? (ci + 7) % 8 : ci;          // the 32 shared columns are drained first
-                uint32_t v[32];
-                tmem_ld_x32(tacc + ch * 32, v);
+            for (int ci = 0; ci < 4; ++ci) {
+                // 64 columns per step; the piece that holds the 32 columns shared by the two accumulators goes first
+                const int piece = b == 0 ? (ci + 3) % 4 : ci;
+                const uint32_t buf = out_base + (n_out & 1) * Cfg::OUT_BYTES;
+                // the stores issued two steps ago have finished reading this buffer
+                if (etid == 0) bulk_wait_group_read<1>();
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                uint32_t v[64];
+                tmem_ld_x32(tacc + piece * 64, reinterpret_cast<uint32_t(&)[32]>(v[0]));
+                tmem_ld_x32(tacc + piece * 64 + 32, reinterpret_cast<uint32_t(&)[32]>(v[32]));
                 tmem_ld_wait();
                 if (ci == 0) { tc_fence_before(); mbar_arrive_cluster(ovl0); }
-                const int qc = q0 + ch * 32;
 #ifdef MXFP6_DEBUG_KNOBS
-                if (P.dbg & 8) continue;
+                if (P.dbg & 8) { ++n_out; continue; }
 #endif
-                if (p < P.c_rows) {
-                    __nv_bfloat16* dst = P.c + (size_t)p * P.ldc + qc;
+                // row prow of the 128x64 bf16 piece = 128 bytes = eight 16-byte chunks, chunk c stored at c ^ (row % 8)
+                const uint32_t rowaddr = buf + prow * 128;
 #pragma unroll
-                    for (int i = 0; i < 32; i += 8) {
-                        if (vec && qc + i + 8 <= P.c_cols) {
-                            uint4 o;
-                            o.x = pack_bf16x2(__uint_as_float(v[i + 0]), __uint_as_float(v[i + 1]));
-                            o.y = pack_bf16x2(__uint_as_float(v[i + 2]), __uint_as_float(v[i + 3]));
-                            o.z = pack_bf16x2(__uint_as_float(v[i + 4]), __uint_as_float(v[i + 5]));
-                            o.w = pack_bf16x2(__uint_as_float(v[i + 6]), __uint_as_float(v[i + 7]));
-                            *reinterpret_cast<uint4*>(dst + i) = o;
-                        } else {
-#pragma unroll
-                            for (int e = 0; e < 8; ++e)
-                                if (qc + i + e < P.c_cols) dst[i + e] = __float2bfloat16_rn(__uint_as_float(v[i + e]));
-                        }
-                    }
+                for (int c = 0; c < 8; ++c) {
+                    const uint32_t x0 = pack_bf16x2(__uint_as_float(v[8 * c + 0]), __uint_as_float(v[8 * c + 1]));
+                    const uint32_t x1 = pack_bf16x2(__uint_as_float(v[8 * c + 2]), __uint_as_float(v[8 * c + 3]));
+                    const uint32_t x2 = pack_bf16x2(__uint_as_float(v[8 * c + 4]), __uint_as_float(v[8 * c + 5]));
+                    const uint32_t x3 = pack_bf16x2(__uint_as_float(v[8 * c + 6]), __uint_as_float(v[8 * c + 7]));
+                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};"
+                                 ::"r"(rowaddr + ((c ^ (prow & 7)) << 4)), "r"(x0), "r"(x1), "r"(x2), "r"(x3) : "memory");
                 }
+                fence_proxy_async_smem();
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (etid == 0) {
+                    for (int d = 0; d < P.ndst; ++d) tma_store_2d(&cmaps.m[d], buf, q0 + piece * 64, my_p0);
+                    bulk_commit_group();
+                }
+                ++n_out;
             }
             ++n_seg;
         }
+        if (etid == 0) bulk_wait_group<0>();      // all stores (local and peer) are done before the CTA leaves
         if (!ok && lane == 0) signal_abort_to_peer();
     }
 

@@ -97,17 +97,19 @@ static int get_encode_fn() {
 }
 
 struct MapKey {
-    const void* ptr; int64_t rows, inner; int box_rows, kind;
+    const void* ptr; int64_t rows, inner, stride; int box_rows, kind;
     bool operator<(const MapKey& o) const {
-        return std::tie(ptr, rows, inner, box_rows, kind) < std::tie(o.ptr, o.rows, o.inner, o.box_rows, o.kind);
+        return std::tie(ptr, rows, inner, stride, box_rows, kind) < std::tie(o.ptr, o.rows, o.inner, o.stride, o.box_rows, o.kind);
     }
 };
 static std::map<MapKey, CUtensorMap> g_maps;
 
 // kind 0: packed 6-bit operand [rows, K] (inner = K elements), box 128 x box_rows, 128-byte swizzle
 // kind 1: scale bytes [rows, K/32] (inner = K/32 bytes), box 16 x box_rows, no swizzle
-static int make_map(const void* ptr, int64_t rows, int64_t inner, int box_rows, int kind, CUtensorMap* out) {
-    MapKey key{ptr, rows, inner, box_rows, kind};
+// kind 2: bf16 output block [rows, inner] with a row stride of stride_bytes, box 64 x box_rows, 128-byte swizzle
+static int make_map(const void* ptr, int64_t rows, int64_t inner, int box_rows, int kind, CUtensorMap* out,
+                    int64_t stride_bytes = 0) {
+    MapKey key{ptr, rows, inner, stride_bytes, box_rows, kind};
     {
         std::lock_guard<std::mutex> lk(g_mu);
         auto it = g_maps.find(key);
@@ -116,12 +118,14 @@ static int make_map(const void* ptr, int64_t rows, int64_t inner, int box_rows, 
     int rc = get_encode_fn();
     if (rc) return rc;
     cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)rows};
-    cuuint64_t strides[1] = {(cuuint64_t)(kind == 0 ? inner * 3 / 4 : inner)};
-    cuuint32_t box[2] = {(cuuint32_t)(kind == 0 ? 128 : 16), (cuuint32_t)box_rows};
+    cuuint64_t strides[1] = {(cuuint64_t)(kind == 0 ? inner * 3 / 4 : kind == 1 ? inner : stride_bytes)};
+    cuuint32_t box[2] = {(cuuint32_t)(kind == 0 ? 128 : kind == 1 ? 16 : 64), (cuuint32_t)box_rows};
     cuuint32_t estr[2] = {1, 1};
-    CUresult r = g_encode(out, kind == 0 ? CU_TENSOR_MAP_DATA_TYPE_16U6_ALIGN16B : CU_TENSOR_MAP_DATA_TYPE_UINT8, 2,
+    const CUtensorMapDataType dt = kind == 0 ? CU_TENSOR_MAP_DATA_TYPE_16U6_ALIGN16B
+                                 : kind == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+    CUresult r = g_encode(out, dt, 2,
                           const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                          kind == 0 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                          kind == 1 ? CU_TENSOR_MAP_SWIZZLE_NONE : CU_TENSOR_MAP_SWIZZLE_128B,
                           CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS)
         return fail(MXFP6_ERR_CUDA, "cuTensorMapEncodeTiled(kind=%d rows=%lld inner=%lld box_rows=%d) failed with %d",
@@ -147,13 +151,13 @@ static int ceil_div(int64_t a, int64_t b) { return (int)((a + b - 1) / b); }
 // Most output tiles a problem may have and still split tiles along K (bounds the counter region).
 constexpr int64_t kMaxSplitTiles = 65536;
 
-static Plan make_plan(int64_t M, int64_t N, int64_t K, int sm_count, bool allow_pair = true) {
+static Plan make_plan(int64_t M, int64_t N, int64_t K, int sm_count, bool allow_pair = true, bool plain = false) {
     Plan p{};
     const int kb = (int)(K / 128);
     const char* force = getenv("MXFP6_FORCE_CFG");   // "bn,swap,streamk[,pair]", for tests
     int fbn = 0, fswap = -1, fsk = -1, fpair = -1;
     if (force) sscanf(force, "%d,%d,%d,%d", &fbn, &fswap, &fsk, &fpair);
-    if (M <= 128 && N > M) {
+    if (M <= 128 && N > M && !plain) {      // plain: whole tiles, C stored untransposed (several destinations)
         p.swap = true;
         p.streamk = (int64_t)ceil_div(N, 128) <= kMaxSplitTiles;
         p.bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : 128;
@@ -171,6 +175,7 @@ static Plan make_plan(int64_t M, int64_t N, int64_t K, int sm_count, bool allow_
     if (p.pair) { p.bn = 256; p.swap = false; p.streamk = false; }
     if (fswap >= 0 && !p.pair) p.swap = fswap != 0;
     if (fsk >= 0 && !p.pair) p.streamk = fsk != 0;
+    if (plain) { p.swap = false; p.streamk = false; }
     {
         const int64_t t = (int64_t)ceil_div(p.swap ? N : M, 128) * ceil_div(p.swap ? M : N, p.bn);
         if (t > kMaxSplitTiles) p.streamk = false;
@@ -218,8 +223,17 @@ static int launch_cfg(DeviceState& d, const Plan& pl, const CUtensorMap& tp, con
     return MXFP6_OK;
 }
 
-static int gemm_impl(const void* a, const void* sfa, const void* b, const void* sfb, void* c, int64_t M, int64_t N,
+// Where the [M,N] result goes: n copies (the first is local, the others may be peer GPUs' memory), each the
+// first element of the block inside a row-major matrix with a row stride of ldc elements.
+struct Dest {
+    void* c[8];
+    int n;
+    int64_t ldc;
+};
+
+static int gemm_impl(const void* a, const void* sfa, const void* b, const void* sfb, const Dest& dst, int64_t M, int64_t N,
                      int64_t K, int fmt_a, int fmt_b, void* ws, size_t ws_bytes, bool own_ws, void* stream) {
+    void* c = dst.c[0];
     if (M < 0 || N < 0 || K < 0) return fail(MXFP6_ERR_BAD_ARG, "negative dimension (M=%lld N=%lld K=%lld)", (long long)M, (long long)N, (long long)K);
     if (K % 128 != 0) return fail(MXFP6_ERR_BAD_ARG, "K=%lld must be a multiple of 128", (long long)K);
     if ((fmt_a != MXFP6_E2M3 && fmt_a != MXFP6_E3M2) || (fmt_b != MXFP6_E2M3 && fmt_b != MXFP6_E3M2))
@@ -228,7 +242,17 @@ static int gemm_impl(const void* a, const void* sfa, const void* b, const void* 
     if (M == 0 || N == 0) return MXFP6_OK;
     if (!c) return fail(MXFP6_ERR_BAD_ARG, "null C");
     cudaStream_t st = (cudaStream_t)stream;
-    if (K == 0) { CUDA_TRY(cudaMemsetAsync(c, 0, (size_t)M * N * 2, st)); return MXFP6_OK; }
+    if (dst.n < 1 || dst.n > 8) return fail(MXFP6_ERR_BAD_ARG, "1 to 8 destinations, got %d", dst.n);
+    if (dst.ldc < N) return fail(MXFP6_ERR_BAD_ARG, "ldc=%lld is smaller than N=%lld", (long long)dst.ldc, (long long)N);
+    for (int i = 0; i < dst.n; ++i) {
+        if (!dst.c[i]) return fail(MXFP6_ERR_BAD_ARG, "null C (destination %d)", i);
+        if ((uintptr_t)dst.c[i] & 1) return fail(MXFP6_ERR_BAD_ARG, "C must be 2-byte aligned");
+    }
+    if (K == 0) {
+        for (int i = 0; i < dst.n; ++i)
+            CUDA_TRY(cudaMemset2DAsync(dst.c[i], (size_t)dst.ldc * 2, 0, (size_t)N * 2, (size_t)M, st));
+        return MXFP6_OK;
+    }
     if (!a || !b || !sfa || !sfb) return fail(MXFP6_ERR_BAD_ARG, "null operand pointer");
     if (((uintptr_t)a & 31) || ((uintptr_t)b & 31)) return fail(MXFP6_ERR_BAD_ARG, "packed operands must be 32-byte aligned");
     if (((uintptr_t)sfa & 3) || ((uintptr_t)sfb & 3)) return fail(MXFP6_ERR_BAD_ARG, "scale arrays must be 4-byte aligned");
@@ -239,7 +263,10 @@ static int gemm_impl(const void* a, const void* sfa, const void* b, const void* 
     if (rc) return rc;
     DeviceState& d = *dp;
     const bool sf_tma_ok = ((K / 32) % 16 == 0) && !((uintptr_t)sfa & 15) && !((uintptr_t)sfb & 15) && !env_int("MXFP6_NO_SF_TMA", 0);
-    Plan pl = make_plan(M, N, K, d.sm_count, sf_tma_ok);
+    // the pair kernel stores C by TMA: 16-byte aligned destinations and row stride
+    bool c_tma_ok = (dst.ldc % 8) == 0;
+    for (int i = 0; i < dst.n; ++i) c_tma_ok = c_tma_ok && !((uintptr_t)dst.c[i] & 15);
+    Plan pl = make_plan(M, N, K, d.sm_count, sf_tma_ok && c_tma_ok, dst.n > 1);
 
     if (pl.ws_bytes) {
         if (own_ws) {
@@ -278,7 +305,7 @@ static int gemm_impl(const void* a, const void* sfa, const void* b, const void* 
     P.p_rows = (int)prow; P.q_rows = (int)qrow;
     P.kblocks = (int)(K / 128);
     P.tiles_p = pl.tiles_p; P.tiles_q = pl.tiles_q;
-    P.ldc = (int)N; P.c_rows = (int)M; P.c_cols = (int)N;
+    P.ldc = (int)dst.ldc; P.c_rows = (int)M; P.c_cols = (int)N;
     P.idesc = make_idesc_m(fp == MXFP6_E2M3 ? kFmtE2M3 : kFmtE3M2, fq == MXFP6_E2M3 ? kFmtE2M3 : kFmtE3M2,
                            pl.pair ? 256u : 128u, (uint32_t)pl.bn);
     P.sf_tma = sf_tma ? 1 : 0;
@@ -286,6 +313,8 @@ static int gemm_impl(const void* a, const void* sfa, const void* b, const void* 
     P.stage_tx_bytes = (128 + (pl.pair ? 128 : pl.bn)) * env_int("MXFP6_TX_BYTES_PER_ROW", 96);
     P.sfp = (const uint8_t*)sp; P.sfq = (const uint8_t*)sq;
     P.c = (__nv_bfloat16*)c;
+    for (int i = 1; i < dst.n; ++i) P.c_more[i - 1] = (__nv_bfloat16*)dst.c[i];
+    P.ndst = dst.n;
     P.ws_counter = (unsigned int*)ws;
     P.ws_partial = ws ? (float*)((uint8_t*)ws + pl.ws_counter_bytes) : nullptr;
     P.ws_slots = pl.ws_slots;
@@ -302,7 +331,10 @@ static int gemm_impl(const void* a, const void* sfa, const void* b, const void* 
                 d.smem_attr_set[(const void*)kern] = true;
             }
         }
-        kern<<<pl.grid, PairCfg::THREADS, PairCfg::SMEM_ALLOC, st>>>(tp, tq, tsp, tsq, P);
+        CMaps cm;
+        for (int i = 0; i < 8; ++i)
+            if ((rc = make_map(dst.c[i < dst.n ? i : 0], M, N, 128, 2, &cm.m[i], dst.ldc * 2))) return rc;
+        kern<<<pl.grid, PairCfg::THREADS, PairCfg::SMEM_ALLOC, st>>>(tp, tq, tsp, tsq, cm, P);
         CUDA_TRY(cudaGetLastError());
         return MXFP6_OK;
     }
@@ -439,7 +471,7 @@ extern "C" const char* mxfp6_last_error(void) { return g_err.c_str(); }
 
 extern "C" int mxfp6_gemm(const void* a, const void* sfa, const void* b, const void* sfb, void* c, int64_t M, int64_t N,
                           int64_t K, int fmt_a, int fmt_b, void* stream) {
-    return gemm_impl(a, sfa, b, sfb, c, M, N, K, fmt_a, fmt_b, nullptr, 0, true, stream);
+    return gemm_impl(a, sfa, b, sfb, Dest{{c}, 1, N}, M, N, K, fmt_a, fmt_b, nullptr, 0, true, stream);
 }
 
 extern "C" size_t mxfp6_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K) {
@@ -451,7 +483,19 @@ extern "C" size_t mxfp6_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K) {
 
 extern "C" int mxfp6_gemm_ws(const void* a, const void* sfa, const void* b, const void* sfb, void* c, int64_t M, int64_t N,
                              int64_t K, int fmt_a, int fmt_b, void* workspace, size_t workspace_bytes, void* stream) {
-    return gemm_impl(a, sfa, b, sfb, c, M, N, K, fmt_a, fmt_b, workspace, workspace_bytes, false, stream);
+    return gemm_impl(a, sfa, b, sfb, Dest{{c}, 1, N}, M, N, K, fmt_a, fmt_b, workspace, workspace_bytes, false, stream);
+}
+
+extern "C" int mxfp6_gemm_multi(const void* a, const void* sfa, const void* b, const void* sfb, void* const* c_dst,
+                                int n_dst, int64_t ldc, int64_t M, int64_t N, int64_t K, int fmt_a, int fmt_b,
+                                void* stream) {
+    if (!c_dst) return fail(MXFP6_ERR_BAD_ARG, "null destination list");
+    if (n_dst < 1 || n_dst > 8) return fail(MXFP6_ERR_BAD_ARG, "1 to 8 destinations, got %d", n_dst);
+    Dest d{};
+    for (int i = 0; i < n_dst; ++i) d.c[i] = c_dst[i];
+    d.n = n_dst;
+    d.ldc = ldc;
+    return gemm_impl(a, sfa, b, sfb, d, M, N, K, fmt_a, fmt_b, nullptr, 0, true, stream);
 }
 
 // ---------------------------------------------------------------------------------- GEMM without allocation
@@ -466,7 +510,7 @@ extern "C" int mxfp6_gemm_noalloc(const void* a, const void* sfa, const void* b,
                                   int64_t N, int64_t K, int fmt_a, int fmt_b, void* stream) {
     // malformed or empty problems take the common path, which rejects or finishes them without any scratch
     if (M <= 0 || N <= 0 || K <= 0 || K % 128 != 0)
-        return gemm_impl(a, sfa, b, sfb, c, M, N, K, fmt_a, fmt_b, nullptr, 0, false, stream);
+        return gemm_impl(a, sfa, b, sfb, Dest{{c}, 1, N}, M, N, K, fmt_a, fmt_b, nullptr, 0, false, stream);
     DeviceState* d = nullptr;
     int rc = get_device_state(&d);
     if (rc) return rc;
@@ -495,7 +539,7 @@ extern "C" int mxfp6_gemm_noalloc(const void* a, const void* sfa, const void* b,
         const size_t counters = (size_t)pl.tiles_p * pl.tiles_q * sizeof(unsigned int);
         CUDA_TRY(cudaMemsetAsync(scratch, 0, counters, (cudaStream_t)stream));
     }
-    return gemm_impl(a, sfa, b, sfb, c, M, N, K, fmt_a, fmt_b, scratch, kBuiltinScratchBytes, false, stream);
+    return gemm_impl(a, sfa, b, sfb, Dest{{c}, 1, N}, M, N, K, fmt_a, fmt_b, scratch, kBuiltinScratchBytes, false, stream);
 }
 
 extern "C" int mxfp6_quantize(const void* src, int src_dtype, int64_t rows, int64_t K, int fmt, void* packed, void* scales,

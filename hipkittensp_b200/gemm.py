@@ -63,6 +63,33 @@ def dispatch_micro(A, B, C, scale_A, scale_B, fmt: int = E2M3, fmt_b: int | None
                              M, N, K, fmt, fmt if fmt_b is None else fmt_b, _stream_ptr()))
 
 
+def dispatch_multi(A, B, dests, col_offset: int, scale_A, scale_B, fmt: int = E2M3) -> None:
+    """The [M,N] product written into the column window [col_offset, col_offset+N) of every matrix in `dests`.
+
+    dests: bf16 tensors [M, ldc] that share one row stride; dests[0] is local, the others may be views of
+    peer GPUs' memory (symmetric memory): the kernel's epilogue pushes each finished tile to all of them."""
+    import ctypes
+
+    _accept(A, "A", torch.uint8)
+    _accept(B, "B", torch.uint8)
+    _accept(scale_A, "scale_A", torch.uint8)
+    _accept(scale_B, "scale_B", torch.uint8)
+    M, N = A.shape[0], B.shape[0]
+    K = A.shape[1] // 3 * 4
+    if not 1 <= len(dests) <= 8:
+        raise RuntimeError("1 to 8 destinations")
+    ldc = dests[0].stride(0)
+    for d in dests:
+        if d.dtype != torch.bfloat16 or d.dim() != 2 or d.stride(1) != 1 or d.stride(0) != ldc or d.shape[0] != M:
+            raise RuntimeError("destinations must be bf16 [M, ldc] matrices with one common row stride")
+        if col_offset < 0 or col_offset + N > d.shape[1]:
+            raise RuntimeError("column window outside the destination")
+    ptrs = (ctypes.c_void_p * len(dests))(*[d.data_ptr() + 2 * col_offset for d in dests])
+    with torch.cuda.device(A.device):
+        check(lib.mxfp6_gemm_multi(A.data_ptr(), scale_A.data_ptr(), B.data_ptr(), scale_B.data_ptr(), ptrs, len(dests),
+                                   ldc, M, N, K, fmt, fmt, _stream_ptr()))
+
+
 def gemm(A, scale_A, B, scale_B, fmt: int = E2M3, fmt_b: int | None = None, out=None):
     """Allocating convenience wrapper around dispatch_micro; returns C."""
     M, N = A.shape[0], B.shape[0]

@@ -72,6 +72,21 @@ int mxfp6_gemm_ws(const void* a, const void* sfa, const void* b, const void* sfb
                   void* workspace, size_t workspace_bytes, void* stream);
 
 /*
+ * The GEMM with its [M,N] result written to n_dst (1..8) destinations at once: c_dst[i] points at the first
+ * element of the block inside a row-major bf16 matrix whose row stride is ldc elements (ldc >= N), so a
+ * column-parallel shard can place its block in the right column window of the full C.  Destination 0 is
+ * local; the others may be peer GPUs' memory mapped into this process (CUDA IPC / symmetric memory): the
+ * epilogue then pushes every finished tile over NVLink while later tiles are still being computed, which is
+ * the gather of the sharded configuration fused into the GEMM.  With n_dst > 1 tiles are never split along K
+ * and C is never stored transposed.  The caller orders the peers' later reads after this call (a cross-GPU
+ * barrier on the stream).  Multi-GPU form of dispatch_micro in distributed-kernels/bf16_gemm/kernel.cpp:253-265,
+ * which stores through iris_ctx.store(ptr, val, rank) (:58-59).
+ */
+int mxfp6_gemm_multi(const void* a, const void* sfa, const void* b, const void* sfb, void* const* c_dst,
+                     int n_dst, int64_t ldc, int64_t M, int64_t N, int64_t K, int fmt_a, int fmt_b,
+                     void* stream);
+
+/*
  * The same GEMM for hosts that must not allocate device memory while they run: servers that hand all of the
  * GPU's memory to their own pool at start-up, control loops with a latency bound (cudaMalloc may synchronise
  * the device, and may fail when memory is tight), or plug-ins whose host forbids allocation in the call path.

@@ -163,3 +163,26 @@ def test_repeat_calls_are_deterministic():
     c1 = run_gpu(pa, sa, pb, sb, R.E2M3)
     c2 = run_gpu(pa, sa, pb, sb, R.E2M3)
     np.testing.assert_array_equal(c1, c2)
+
+
+@pytest.mark.parametrize("shape,force", [((512, 768, 1024), None), ((512, 768, 1024), "256,0,0,1"),
+                                         ((300, 520, 512), "256,0,0,1"), ((64, 256, 512), None),
+                                         ((1024, 512, 1024), "128,0,0,0")])
+def test_multi_destination_column_window(shape, force):
+    """mxfp6_gemm_multi: the block lands in the same column window of every destination and nowhere else."""
+    M, N, K = shape
+    if force:
+        os.environ["MXFP6_FORCE_CFG"] = force
+    pa, sa, pb, sb = quantized_inputs("lognormal", M, N, K, seed=11)
+    t = [torch.from_numpy(x).cuda() for x in (pa, sa, pb, sb)]
+    ldc, off = N + 264, 136
+    dests = [torch.full((M, ldc), float("nan"), dtype=torch.bfloat16, device="cuda") for _ in range(3)]
+    hk.dispatch_multi(t[0], t[2], dests, off, t[1], t[3], R.E2M3)
+    assert hk.device_status() == 0
+    ref, absdot = oracle_f64(pa, sa, pb, sb, R.E2M3)
+    for d in dests:
+        c = d[:, off:off + N].float().cpu().numpy()
+        check(c, ref, absdot)
+        assert torch.isnan(d[:, :off]).all() and torch.isnan(d[:, off + N:]).all(), "write outside the window"
+    assert torch.equal(dests[0][:, off:off + N], dests[1][:, off:off + N])
+    assert torch.equal(dests[0][:, off:off + N], dests[2][:, off:off + N])
