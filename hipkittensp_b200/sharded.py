@@ -6,8 +6,14 @@ rank ends with the full row-major C[M,N].  The reference's only multi-GPU GEMM s
 no exchange step (distributed-kernels/bf16_gemm/example.py:70,112); the column-parallel split with a
 gather is this path's own multi-GPU form.
 
-The exchange is one NCCL all-gather of the contiguous [M, N/g] shards into a [g, M, N/g] buffer followed
-by a strided device copy into row-major C (`gather="nccl"`).
+Two exchanges:
+
+* `gather="fused"` (default on GPUs): the full C of every rank lives in symmetric memory (peer-mapped over
+  NVLink); the GEMM kernel's epilogue stores each finished 128x64 piece by TMA into the right column window of
+  the local C and of every peer's C (`mxfp6_gemm_multi`), so the gather overlaps the remaining tiles and no
+  re-layout pass exists.  A cross-GPU barrier on the stream closes the step.
+* `gather="nccl"`: one NCCL (or gloo, on CPU) all-gather of the contiguous [M, N/g] shards into a [g, M, N/g]
+  buffer followed by a strided copy into row-major C.  The baseline, and the path the CPU tests use.
 """
 from __future__ import annotations
 
@@ -43,21 +49,45 @@ def assemble_columns(gathered: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
 class ColumnParallelGemm:
     """Holds the communicator and the reusable buffers of one sharded GEMM shape."""
 
-    def __init__(self, M: int, N: int, K: int, group=None, device=None, fmt: int = E2M3):
+    def __init__(self, M: int, N: int, K: int, group=None, device=None, fmt: int = E2M3, gather: str | None = None):
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         self.M, self.N, self.K, self.fmt = M, N, K, fmt
         self.lo, self.hi = shard_bounds(N, self.world, self.rank)
         self.device = device
-        self.c_shard = torch.empty((M, self.hi - self.lo), dtype=torch.bfloat16, device=device)
-        self.gathered = torch.empty((self.world, M, self.hi - self.lo), dtype=torch.bfloat16, device=device) \
-            if self.world > 1 else None
-        self.c_full = torch.empty((M, N), dtype=torch.bfloat16, device=device) if self.world > 1 else self.c_shard
+        on_gpu = device is not None and torch.device(device).type == "cuda"
+        if gather is None:
+            gather = "fused" if (on_gpu and self.world > 1) else "nccl"
+        if gather not in ("fused", "nccl"):
+            raise ValueError(gather)
+        self.mode = gather
+        self.symm = None
+        if self.mode == "fused" and self.world > 1:
+            import torch.distributed._symmetric_memory as symm
+
+            self.c_full = symm.empty((M, N), dtype=torch.bfloat16, device=device)
+            self.symm = symm.rendezvous(self.c_full, dist.group.WORLD if group is None else group)
+            # destination 0 is local, the rest are the peers' copies of C, rotated so that ranks do not all
+            # push to the same peer at the same moment
+            order = [(self.rank + i) % self.world for i in range(self.world)]
+            self.dests = [self.c_full] + [self.symm.get_buffer(r, (M, N), torch.bfloat16) for r in order[1:]]
+            self.c_shard = self.c_full[:, self.lo:self.hi]
+            self.gathered = None
+        else:
+            self.c_shard = torch.empty((M, self.hi - self.lo), dtype=torch.bfloat16, device=device)
+            self.gathered = torch.empty((self.world, M, self.hi - self.lo), dtype=torch.bfloat16, device=device) \
+                if self.world > 1 else None
+            self.c_full = torch.empty((M, N), dtype=torch.bfloat16, device=device) if self.world > 1 else self.c_shard
 
     def local_gemm(self, A, scale_A, B_shard, scale_B_shard) -> torch.Tensor:
-        """This rank's [M, N/g] block of C."""
-        dispatch_micro(A, B_shard, self.c_shard, scale_A, scale_B_shard, self.fmt)
+        """This rank's [M, N/g] block of C (no exchange)."""
+        if self.mode == "fused" and self.world > 1:
+            from .gemm import dispatch_multi
+
+            dispatch_multi(A, B_shard, self.dests[:1], self.lo, scale_A, scale_B_shard, self.fmt)
+        else:
+            dispatch_micro(A, B_shard, self.c_shard, scale_A, scale_B_shard, self.fmt)
         return self.c_shard
 
     def gather(self) -> torch.Tensor:
@@ -67,5 +97,11 @@ class ColumnParallelGemm:
         return assemble_columns(self.gathered, self.c_full)
 
     def __call__(self, A, scale_A, B_shard, scale_B_shard) -> torch.Tensor:
+        if self.mode == "fused" and self.world > 1:
+            from .gemm import dispatch_multi
+
+            dispatch_multi(A, B_shard, self.dests, self.lo, scale_A, scale_B_shard, self.fmt)
+            self.symm.barrier()          # every rank's pushes have landed before anyone reads C
+            return self.c_full
         self.local_gemm(A, scale_A, B_shard, scale_B_shard)
         return self.gather()
