@@ -51,6 +51,7 @@ struct GemmParams {
     int ws_slots;              // partial slots per tile
     int* status;               // device status word
     unsigned long long wait_cycles;  // budget of one wait in clock cycles
+    int group_p;               // pair kernel: P-tiles per rasterisation group
     int dbg;                   // experiment switches, honoured only by builds with MXFP6_DEBUG_KNOBS
 };
 

@@ -47,7 +47,6 @@ struct PairCfg {
                                       ATOM_GROUPS * GROUP_BYTES + NUM_BARS * 8 + 64;
     static constexpr int SMEM_ALLOC = SMEM_BYTES + 1024;
     static constexpr int THREADS = 256;
-    static constexpr int GROUP_P = 4;                     // rasterisation: 4 pair-tiles (1024 rows) share Q tiles
     static_assert(SMEM_ALLOC <= 232448, "exceeds the shared memory of a CTA");
 };
 
@@ -81,10 +80,10 @@ struct CMaps {
 
 // Pair tile t -> first P row / Q row of the pair.  tiles_p/tiles_q in P count 256x256 pair tiles.
 __device__ __forceinline__ void pair_coords(const GemmParams& P, int t, int& p0, int& q0) {
-    const int per_group = PairCfg::GROUP_P * P.tiles_q;
+    const int per_group = P.group_p * P.tiles_q;
     const int group = t / per_group, in = t % per_group;
-    const int first_p = group * PairCfg::GROUP_P;
-    const int gsz = min(P.tiles_p - first_p, PairCfg::GROUP_P);
+    const int first_p = group * P.group_p;
+    const int gsz = min(P.tiles_p - first_p, P.group_p);
     p0 = (first_p + in % gsz) * 256;
     q0 = (in / gsz) * 256;
 }

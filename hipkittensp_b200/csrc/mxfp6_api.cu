@@ -321,6 +321,8 @@ static int gemm_impl(const void* a, const void* sfa, const void* b, const void* 
     P.status = d.status;
     P.wait_cycles = d.wait_cycles;
     P.dbg = env_int("MXFP6_DBG", 0);
+    P.group_p = env_int("MXFP6_GROUP_P", 16);   // 16 pair-tiles (4096 rows of A) share each tile of B
+    if (P.group_p < 1) P.group_p = 1;
 
  if (pl.pair) {
         auto kern = mxfp6_gemm_pair_kernel;
