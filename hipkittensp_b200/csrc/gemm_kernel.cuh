@@ -52,6 +52,7 @@ struct GemmParams {
     int* status;               // device status word
     unsigned long long wait_cycles;  // budget of one wait in clock cycles
     int group_p;               // pair kernel: P-tiles per rasterisation group
+    unsigned long long* dbg_times;   // debug builds: per-CTA time stamps
     int dbg;                   // experiment switches, honoured only by builds with MXFP6_DEBUG_KNOBS
 };
 
@@ -191,6 +192,19 @@ __device__ __forceinline__ bool wait_bar_warp(uint32_t bar, uint32_t parity, vol
     return __all_sync(0xffffffffu, wait_bar(bar, parity, abort_flag, P, code));
 }
 
+#ifdef MXFP6_DEBUG_KNOBS
+__device__ __forceinline__ void dbg_stamp(const GemmParams& P, int slot) {
+    if (P.dbg_times) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+        P.dbg_times[blockIdx.x * 8 + slot] = t;
+    }
+}
+#define MXFP6_STAMP(slot) dbg_stamp(P, slot)
+#else
+#define MXFP6_STAMP(slot)
+#endif
+
 template <class Cfg>
 __global__ void __launch_bounds__(Cfg::THREADS, 1)
 mxfp6_gemm_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__ CUtensorMap tm_q,
@@ -222,6 +236,7 @@ mxfp6_gemm_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constan
     volatile int* ticket_slot = reinterpret_cast<volatile int*>(smem_gen + misc_off + 8);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) MXFP6_STAMP(0);
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < Cfg::STAGES; ++s) { mbar_init(bar_full(s), 1); mbar_init(bar_empty(s), 1); }
@@ -245,6 +260,7 @@ mxfp6_gemm_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constan
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    if (threadIdx.x == 0) MXFP6_STAMP(1);
 
     // =========================================================== warp 0: TMA producer
     if (warp == 0) {
@@ -334,6 +350,9 @@ mxfp6_gemm_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constan
 #endif
                 ok = ok && wait_bar_warp(bar_full(s), (n_kb / Cfg::STAGES) & 1, abort_flag, P, kStatusTimeoutMma);
                 if (!ok) break;
+#ifdef MXFP6_DEBUG_KNOBS
+                if (n_kb == 0 && lane == 0) MXFP6_STAMP(2);
+#endif
                 const bool group_done = (kb & 3) == 3 || kb == sg.k1 - 1;
                 if (elect_one_sync()) {
                     const uint32_t sfa = tmem_base + Cfg::SF_COL + (n_kb & 1) * 16;
@@ -372,6 +391,7 @@ mxfp6_gemm_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constan
             if (!ok) break;
             if (elect_one_sync()) tc_commit(bar_acc_full(b));
             __syncwarp();
+            if (lane == 0) MXFP6_STAMP(3);
             ++n_seg;
         }
     }
@@ -559,6 +579,7 @@ mxfp6_gemm_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constan
                     if (etid == 0) P.ws_counter[sg.tile] = 0u;
                 }
             }
+            if (etid == 0) MXFP6_STAMP(4);
             ++n_seg;
         }
     }
@@ -573,6 +594,7 @@ mxfp6_gemm_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constan
     __syncthreads();
     tc_fence_after();
     if (warp == 1) tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+    if (threadIdx.x == 32) MXFP6_STAMP(5);
 }
 
 }  // namespace mxfp6

@@ -321,6 +321,11 @@ static int gemm_impl(const void* a, const void* sfa, const void* b, const void* 
     P.status = d.status;
     P.wait_cycles = d.wait_cycles;
     P.dbg = env_int("MXFP6_DBG", 0);
+#ifdef MXFP6_DEBUG_KNOBS
+    P.dbg_times = (unsigned long long*)(uintptr_t)strtoull(getenv("MXFP6_DBG_TIMES") ? getenv("MXFP6_DBG_TIMES") : "0", nullptr, 0);
+#else
+    P.dbg_times = nullptr;
+#endif
     P.group_p = env_int("MXFP6_GROUP_P", 16);   // 16 pair-tiles (4096 rows of A) share each tile of B
     if (P.group_p < 1) P.group_p = 1;
 
