@@ -329,9 +329,7 @@ mxfp6_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_co
                 // 64 columns per step; the piece that holds the 32 columns shared by the two accumulators goes first
                 const int piece = b == 0 ? (ci + 3) % 4 : ci;
                 const uint32_t buf = out_base + (n_out & 1) * Cfg::OUT_BYTES;
-                // the stores issued two steps ago have finished reading this buffer
-                if (etid == 0) bulk_wait_group_read<1>();
-                asm volatile("bar.sync 1, 128;" ::: "memory");
+                // accumulator columns first: the shared columns are released to the next tile's MMA as early as possible
                 uint32_t v[64];
                 tmem_ld_x32(tacc + piece * 64, reinterpret_cast<uint32_t(&)[32]>(v[0]));
                 tmem_ld_x32(tacc + piece * 64 + 32, reinterpret_cast<uint32_t(&)[32]>(v[32]));
@@ -340,6 +338,9 @@ mxfp6_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_co
 #ifdef MXFP6_DEBUG_KNOBS
                 if (P.dbg & 8) { ++n_out; continue; }
 #endif
+                // the stores issued two steps ago have finished reading this staging buffer
+                if (etid == 0) bulk_wait_group_read<1>();
+                asm volatile("bar.sync 1, 128;" ::: "memory");
                 // row prow of the 128x64 bf16 piece = 128 bytes = eight 16-byte chunks, chunk c stored at c ^ (row % 8)
                 const uint32_t rowaddr = buf + prow * 128;
 #pragma unroll
