@@ -552,22 +552,34 @@ mxfp6_gemm_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constan
                 if (last) {
                     __threadfence();
                     const float* base = P.ws_partial + (size_t)sg.tile * P.ws_slots * (size_t)(BN * 128) + prow;
-                    // 8 columns at a time: the loads of a chunk are independent and in flight together; each
+                    // FC columns at a time: the loads of a chunk are independent and in flight together; each
                     // element is still summed in slot order
+                    constexpr int FC = BN >= 16 ? 16 : BN;
 #pragma unroll 1
-                    for (int col0 = 0; col0 < BN; col0 += 8) {
-                        float acc[8];
+                    for (int col0 = 0; col0 < BN; col0 += FC) {
+                        float acc[FC];
 #pragma unroll
-                        for (int j = 0; j < 8; ++j) acc[j] = 0.f;
-                        for (int sgi = 0; sgi < sg.nseg; ++sgi) {
-                            float t[8];
+                        for (int j = 0; j < FC; ++j) acc[j] = 0.f;
+                        if (sg.nseg == 2) {                       // the common case: both slots fetched at once
+                            float t0[FC], t1[FC];
 #pragma unroll
-                            for (int j = 0; j < 8; ++j) t[j] = __ldcg(base + (size_t)sgi * (BN * 128) + (size_t)(col0 + j) * 128);
+                            for (int j = 0; j < FC; ++j) {
+                                t0[j] = __ldcg(base + (size_t)(col0 + j) * 128);
+                                t1[j] = __ldcg(base + (size_t)(BN * 128) + (size_t)(col0 + j) * 128);
+                            }
 #pragma unroll
-                            for (int j = 0; j < 8; ++j) acc[j] += t[j];
+                            for (int j = 0; j < FC; ++j) acc[j] = (0.f + t0[j]) + t1[j];
+                        } else {
+                            for (int sgi = 0; sgi < sg.nseg; ++sgi) {
+                                float t[FC];
+#pragma unroll
+                                for (int j = 0; j < FC; ++j) t[j] = __ldcg(base + (size_t)sgi * (BN * 128) + (size_t)(col0 + j) * 128);
+#pragma unroll
+                                for (int j = 0; j < FC; ++j) acc[j] += t[j];
+                            }
                         }
 #pragma unroll
-                        for (int j = 0; j < 8; ++j) {
+                        for (int j = 0; j < FC; ++j) {
                             const int q = sg.q0 + col0 + j;
                             if (Cfg::SWAP) {
                                 if (p < P.c_cols && q < P.c_rows) P.c[(size_t)q * P.ldc + p] = __float2bfloat16_rn(acc[j]);
