@@ -237,6 +237,7 @@ mxfp6_gemm_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constan
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) MXFP6_STAMP(0);
+    pdl_launch_dependents();     // the next kernel may set itself up on SMs this grid has left
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < Cfg::STAGES; ++s) { mbar_init(bar_full(s), 1); mbar_init(bar_empty(s), 1); }
@@ -260,6 +261,7 @@ mxfp6_gemm_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constan
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    pdl_wait();                  // nothing above touches global memory; everything below may
     if (threadIdx.x == 0) MXFP6_STAMP(1);
 
     // =========================================================== warp 0: TMA producer

@@ -117,6 +117,7 @@ mxfp6_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_co
     const uint32_t abort_addr = smem_base + misc_off + 4;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    pdl_launch_dependents();     // the next kernel may set itself up on SMs this grid has left
     const uint32_t rank = cluster_ctarank();              // 0 = even CTA (issues the MMAs), 1 = its peer
     const bool leader = rank == 0;
     const int cluster_id = blockIdx.x >> 1, n_clusters = gridDim.x >> 1;
@@ -144,6 +145,7 @@ mxfp6_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_co
     cluster_wait();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    pdl_wait();                  // nothing above touches global memory; everything below may
 
     auto signal_abort_to_peer = [&]() { st_shared_cluster_u32(mapa_shared(abort_addr, rank ^ 1), 1u); };
 

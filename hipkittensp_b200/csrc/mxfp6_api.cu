@@ -210,6 +210,23 @@ static Plan make_plan(int64_t M, int64_t N, int64_t K, int sm_count, bool allow_
     return p;
 }
 
+// Launch configuration shared by the GEMM kernels.  Programmatic stream serialisation lets the next kernel of
+// the stream begin its set-up (barriers, TMEM, descriptor prefetch) before this one has drained; the kernels
+// call griddepcontrol.wait before their first global access.  MXFP6_PDL=0 turns it off.
+static cudaLaunchAttribute g_pdl_attr;
+static cudaLaunchConfig_t launch_config(int grid, int threads, int smem, cudaStream_t st) {
+    cudaLaunchConfig_t lc{};
+    lc.gridDim = dim3((unsigned)grid, 1, 1);
+    lc.blockDim = dim3((unsigned)threads, 1, 1);
+    lc.dynamicSmemBytes = (size_t)smem;
+    lc.stream = st;
+    g_pdl_attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    g_pdl_attr.val.programmaticStreamSerializationAllowed = 1;
+    lc.attrs = &g_pdl_attr;
+    lc.numAttrs = env_int("MXFP6_PDL", 1) ? 1 : 0;
+    return lc;
+}
+
 template <class Cfg>
 static int launch_cfg(DeviceState& d, const Plan& pl, const CUtensorMap& tp, const CUtensorMap& tq,
                       const CUtensorMap& tsp, const CUtensorMap& tsq, const GemmParams& P, cudaStream_t st) {
@@ -221,8 +238,8 @@ static int launch_cfg(DeviceState& d, const Plan& pl, const CUtensorMap& tp, con
             d.smem_attr_set[(const void*)kern] = true;
         }
     }
-    kern<<<pl.grid, Cfg::THREADS, Cfg::SMEM_ALLOC, st>>>(tp, tq, tsp, tsq, P);
-    CUDA_TRY(cudaGetLastError());
+    cudaLaunchConfig_t lc = launch_config(pl.grid, Cfg::THREADS, Cfg::SMEM_ALLOC, st);
+    CUDA_TRY(cudaLaunchKernelEx(&lc, kern, tp, tq, tsp, tsq, P));
     return MXFP6_OK;
 }
 
@@ -344,8 +361,8 @@ static int gemm_impl(const void* a, const void* sfa, const void* b, const void* 
         CMaps cm;
         for (int i = 0; i < 8; ++i)
             if ((rc = make_map(dst.c[i < dst.n ? i : 0], M, N, 128, 2, &cm.m[i], dst.ldc * 2))) return rc;
-        kern<<<pl.grid, PairCfg::THREADS, PairCfg::SMEM_ALLOC, st>>>(tp, tq, tsp, tsq, cm, P);
-        CUDA_TRY(cudaGetLastError());
+        cudaLaunchConfig_t lc = launch_config(pl.grid, PairCfg::THREADS, PairCfg::SMEM_ALLOC, st);
+        CUDA_TRY(cudaLaunchKernelEx(&lc, kern, tp, tq, tsp, tsq, cm, P));
         return MXFP6_OK;
     }
 #define MXFP6_CASE(BN_, SWAP_, SK_)                                                              \

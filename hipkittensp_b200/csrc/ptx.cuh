@@ -23,6 +23,12 @@ __device__ __forceinline__ bool elect_one_sync() {
     return pred != 0;
 }
 
+// Programmatic dependent launch: let the next kernel of the stream start its prologue while this grid is
+// still running (no-ops when the launch did not ask for it) ...
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+// ... and wait until the kernels this one depends on have completed and their writes are visible.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 // ------------------------------------------------------------------ mbarrier
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
