@@ -23,6 +23,8 @@
  * Format summary
  *   E2M3: s ee mmm, bias 1, no inf/nan.  e==0: +-m/8 ; e>0: +-2^(e-1)*(1+m/8); max 7.5
  *   E3M2: s eee mm, bias 3, no inf/nan.  e==0: +-m/16; e>0: +-2^(e-3)*(1+m/4); max 28
+ *   MX-FP8 operands (one byte per element) go through the same path: E4M3 (bias 7, max 448, 0x7f NaN) with
+ *   emax_elem 8, E5M2 (bias 15, max 57344, exponent 31 inf/nan) with emax_elem 15; format codes 2 and 3.
  *   E8M0: byte x -> 2^(x-127); 0xFF is NaN and is never produced.
  *   Block of 32 along K: scale exponent = floor(log2(amax)) - emax_elem, emax_elem = 2 (E2M3)
  *   or 4 (E3M2); stored byte = clamp(exp+127, 0, 254); amax==0 -> byte 0, all codes +-0.
@@ -47,36 +49,51 @@ static inline float pow2i(int e) {
     return bits_f32(1u << (uint32_t)(e + 149));
 }
 
+/* ---- format parameters ---------------------------------------------------- */
+#define MXFP8_E4M3 2
+#define MXFP8_E5M2 3
+typedef struct { int bits, mbits, bias, emax; float maxv; int maxcode; } fmt_t;
+static fmt_t fmt_of(int fmt) {
+    switch (fmt) {
+        case MXFP6_E2M3: { fmt_t f = {6, 3, 1, 2, 7.5f, 0x1f}; return f; }
+        case MXFP6_E3M2: { fmt_t f = {6, 2, 3, 4, 28.0f, 0x1f}; return f; }
+        case MXFP8_E4M3: { fmt_t f = {8, 3, 7, 8, 448.0f, 0x7e}; return f; }   /* 0x7f is NaN */
+        default:         { fmt_t f = {8, 2, 15, 15, 57344.0f, 0x7b}; return f; } /* exponent 31 is inf/nan */
+    }
+}
+
 /* ---- element decode ---------------------------------------------------- */
 float mxfp6_decode_elem(uint8_t code, int fmt) {
-    int mbits = (fmt == MXFP6_E2M3) ? 3 : 2;
-    int bias  = (fmt == MXFP6_E2M3) ? 1 : 3;
-    int sign  = (code >> 5) & 1;
-    int e     = (code >> mbits) & ((1 << (5 - mbits)) - 1);
-    int m     = code & ((1 << mbits) - 1);
+    fmt_t f = fmt_of(fmt);
+    int ebits = f.bits - 1 - f.mbits;
+    int sign  = (code >> (f.bits - 1)) & 1;
+    int e     = (code >> f.mbits) & ((1 << ebits) - 1);
+    int m     = code & ((1 << f.mbits) - 1);
     float mag;
-    if (e == 0) mag = (float)m * pow2i(1 - bias - mbits);
-    else        mag = (float)((1 << mbits) + m) * pow2i(e - bias - mbits);
+    if (fmt == MXFP8_E4M3 && e == 15 && m == 7) mag = NAN;
+    else if (fmt == MXFP8_E5M2 && e == 31) mag = m ? NAN : INFINITY;
+    else if (e == 0) mag = (float)m * pow2i(1 - f.bias - f.mbits);
+    else             mag = (float)((1 << f.mbits) + m) * pow2i(e - f.bias - f.mbits);
     return sign ? -mag : mag;
 }
 
 /* ---- element encode: RNE, saturating, input already divided by the block scale ---- */
 uint8_t mxfp6_encode_elem(float v, int fmt) {
-    int mbits = (fmt == MXFP6_E2M3) ? 3 : 2;
-    int bias  = (fmt == MXFP6_E2M3) ? 1 : 3;
-    float maxv = (fmt == MXFP6_E2M3) ? 7.5f : 28.0f;
-    uint8_t sign = (f32_bits(v) >> 31) ? 0x20 : 0;
+    fmt_t f = fmt_of(fmt);
+    int mbits = f.mbits, bias = f.bias;
+    float maxv = f.maxv;
+    uint8_t sign = (f32_bits(v) >> 31) ? (uint8_t)(1u << (f.bits - 1)) : 0;
     float a = fabsf(v);
-    if (!(a == a)) return (uint8_t)(sign | 0x1f);        /* NaN in -> max magnitude (no NaN code) */
-    if (a >= maxv) return (uint8_t)(sign | 0x1f);        /* saturate (also +-inf) */
-    /* quantum of the binade a lies in; subnormal range shares the quantum of the first binade */
+    if (!(a == a)) return (uint8_t)(sign | f.maxcode);   /* NaN in -> max magnitude */
+    if (a >= maxv) return (uint8_t)(sign | f.maxcode);   /* saturate (also +-inf) */
+    /* quantum of the binade a lies in; the subnormal range shares the quantum of the first binade */
     int ex = (int)((f32_bits(a) >> 23) & 0xff) - 127;    /* floor(log2 a) for normal fp32 */
-    if (a < pow2i(1 - bias)) ex = 1 - bias;              /* subnormal fp6 range (and tiny/zero) */
+    if (a < pow2i(1 - bias)) ex = 1 - bias;              /* subnormal range of the target (and tiny/zero) */
     float q = pow2i(ex - mbits);                         /* spacing of representable values */
     /* a/q is exact (power-of-two divide); nearbyintf rounds to nearest even in default mode */
     float n = nearbyintf(a / q);
     float r = n * q;                                     /* rounded magnitude, may carry to next binade */
-    if (r >= maxv) return (uint8_t)(sign | 0x1f);
+    if (r >= maxv) return (uint8_t)(sign | f.maxcode);
     if (r == 0.0f) return sign;                          /* the sign of zero is kept, as the toolkit and the hardware cvt do */
     int re = (int)((f32_bits(r) >> 23) & 0xff) - 127;
     uint8_t code;
@@ -98,7 +115,7 @@ float mxfp6_e8m0_decode(uint8_t x) {
 
 /* scale byte for a block whose max |x| is amax */
 uint8_t mxfp6_e8m0_from_amax(float amax, int fmt) {
-    int emax_elem = (fmt == MXFP6_E2M3) ? 2 : 4;
+    int emax_elem = fmt_of(fmt).emax;
     if (!(amax > 0.0f) || isinf(amax)) {
         if (isinf(amax)) return 254;
         return 0;
@@ -134,8 +151,10 @@ void mxfp6_unpack(const uint8_t* packed, int64_t n, uint8_t* codes) {
 }
 
 /* ---- block quantiser ------------------------------------------------------ */
-/* src [rows,K] fp32 row-major, K % 32 == 0 -> packed [rows,3K/4], scales [rows,K/32] */
+/* src [rows,K] fp32 row-major, K % 32 == 0 -> operand bytes (fp6: packed [rows,3K/4]; fp8: [rows,K]),
+ * scales [rows,K/32] */
 void mxfp6_quantize(const float* src, int64_t rows, int64_t K, int fmt, uint8_t* packed, uint8_t* scales) {
+    const int fp8 = fmt_of(fmt).bits == 8;
     #pragma omp parallel for schedule(static)
     for (int64_t r = 0; r < rows; ++r) {
         uint8_t codes[32];
@@ -150,20 +169,23 @@ void mxfp6_quantize(const float* src, int64_t rows, int64_t K, int fmt, uint8_t*
             int h = (-e) / 2;
             float f1 = pow2i(h), f2 = pow2i(-e - h);
             for (int i = 0; i < 32; ++i) codes[i] = mxfp6_encode_elem(x[i] * f1 * f2, fmt);
-            mxfp6_pack(codes, 32, packed + r * (K * 3 / 4) + kb * 24);
+            if (fp8) memcpy(packed + r * K + kb * 32, codes, 32);
+            else mxfp6_pack(codes, 32, packed + r * (K * 3 / 4) + kb * 24);
         }
     }
 }
 
-/* packed+scales -> fp32 [rows,K]; decode(code)*2^(scale-127), exact in fp32 for all finite cases */
+/* operand bytes + scales -> fp32 [rows,K]; decode(code)*2^(scale-127) */
 void mxfp6_dequantize(const uint8_t* packed, const uint8_t* scales, int64_t rows, int64_t K, int fmt, float* out) {
-    float lut[64];
-    for (int c = 0; c < 64; ++c) lut[c] = mxfp6_decode_elem((uint8_t)c, fmt);
+    const int fp8 = fmt_of(fmt).bits == 8;
+    float lut[256];
+    for (int c = 0; c < (fp8 ? 256 : 64); ++c) lut[c] = mxfp6_decode_elem((uint8_t)c, fmt);
     #pragma omp parallel for schedule(static)
     for (int64_t r = 0; r < rows; ++r) {
         uint8_t codes[32];
         for (int64_t kb = 0; kb < K / 32; ++kb) {
-            mxfp6_unpack(packed + r * (K * 3 / 4) + kb * 24, 32, codes);
+            if (fp8) memcpy(codes, packed + r * K + kb * 32, 32);
+            else mxfp6_unpack(packed + r * (K * 3 / 4) + kb * 24, 32, codes);
             float s = mxfp6_e8m0_decode(scales[r * (K / 32) + kb]);
             for (int i = 0; i < 32; ++i) out[r * K + kb * 32 + i] = lut[codes[i]] * s;
         }

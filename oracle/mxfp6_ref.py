@@ -25,23 +25,38 @@ import numpy as np
 
 E2M3 = 0
 E3M2 = 1
+E4M3 = 2   # MX-FP8, OCP e4m3 ("fn": no infinities, 0x7f/0xff are NaN), one byte per element
+E5M2 = 3   # MX-FP8, OCP e5m2 (IEEE-like: exponent 31 is inf/nan), one byte per element
 
+# bits = container width; ncodes = finite non-negative codes (they ascend with the value, so the index of a
+# magnitude in the table of finite magnitudes is its code)
 _FMT = {
-    E2M3: dict(mbits=3, bias=1, emax=2, maxv=7.5),
-    E3M2: dict(mbits=2, bias=3, emax=4, maxv=28.0),
+    E2M3: dict(bits=6, mbits=3, bias=1, emax=2, maxv=7.5, nfinite=32),
+    E3M2: dict(bits=6, mbits=2, bias=3, emax=4, maxv=28.0, nfinite=32),
+    E4M3: dict(bits=8, mbits=3, bias=7, emax=8, maxv=448.0, nfinite=127),
+    E5M2: dict(bits=8, mbits=2, bias=15, emax=15, maxv=57344.0, nfinite=124),
 }
+
+
+def is_fp8(fmt: int) -> bool:
+    return _FMT[fmt]["bits"] == 8
 
 
 # --------------------------------------------------------------------------- tables
 def decode_table(fmt: int) -> np.ndarray:
-    """All 64 code -> fp32 values."""
+    """All 64 (fp6) or 256 (fp8) code -> fp32 values; fp8 NaN/inf codes decode to nan/inf."""
     p = _FMT[fmt]
-    mb, bias = p["mbits"], p["bias"]
-    c = np.arange(64, dtype=np.int64)
-    s = (c >> 5) & 1
-    e = (c >> mb) & ((1 << (5 - mb)) - 1)
+    mb, bias, bits = p["mbits"], p["bias"], p["bits"]
+    eb = bits - 1 - mb
+    c = np.arange(1 << bits, dtype=np.int64)
+    s = (c >> (bits - 1)) & 1
+    e = (c >> mb) & ((1 << eb) - 1)
     m = c & ((1 << mb) - 1)
     mag = np.where(e == 0, m * 2.0 ** (1 - bias - mb), ((1 << mb) + m) * 2.0 ** (e - bias - mb))
+    if fmt == E4M3:
+        mag = np.where((e == 15) & (m == 7), np.nan, mag)
+    if fmt == E5M2:
+        mag = np.where(e == 31, np.where(m == 0, np.inf, np.nan), mag)
     return np.where(s == 1, -mag, mag).astype(np.float32)
 
 
@@ -55,23 +70,23 @@ def e8m0_decode(b: np.ndarray) -> np.ndarray:
 
 # --------------------------------------------------------------------------- element encode
 def encode_elems(v: np.ndarray, fmt: int) -> np.ndarray:
-    """fp32 (already divided by the block scale) -> 6-bit codes, RNE + saturate."""
+    """fp32 (already divided by the block scale) -> codes, RNE + saturate to the largest finite value."""
     p = _FMT[fmt]
-    mb, bias, maxv = p["mbits"], p["bias"], p["maxv"]
+    maxv, nfin, bits = p["maxv"], p["nfinite"], p["bits"]
     v = np.asarray(v, dtype=np.float32)
-    sign = (v.view(np.uint32) >> 31).astype(np.uint8) << 5
+    sign = ((v.view(np.uint32) >> 31).astype(np.uint8) << (bits - 1)).astype(np.uint8)
     a = np.abs(v).astype(np.float64)
-    # positive representable magnitudes, ascending (32 of them, index == code)
-    grid = decode_table(fmt)[:32].astype(np.float64)
+    # finite non-negative magnitudes, ascending (index == code)
+    grid = decode_table(fmt)[:nfin].astype(np.float64)
     # nearest grid point with ties to even code (even code == even mantissa lsb)
-    idx_hi = np.searchsorted(grid, a, side="left").clip(0, 31)
-    idx_lo = (idx_hi - 1).clip(0, 31)
+    idx_hi = np.searchsorted(grid, a, side="left").clip(0, nfin - 1)
+    idx_lo = (idx_hi - 1).clip(0, nfin - 1)
     d_hi = np.abs(grid[idx_hi] - a)
     d_lo = np.abs(a - grid[idx_lo])
     pick_lo = (d_lo < d_hi) | ((d_lo == d_hi) & (idx_lo % 2 == 0))
     code = np.where(pick_lo, idx_lo, idx_hi).astype(np.uint8)
-    code = np.where(a >= maxv, 31, code).astype(np.uint8)
-    code = np.where(np.isnan(a), 31, code).astype(np.uint8)
+    code = np.where(a >= maxv, nfin - 1, code).astype(np.uint8)
+    code = np.where(np.isnan(a), nfin - 1, code).astype(np.uint8)
     return (sign | code).astype(np.uint8)  # the sign of zero is kept (toolkit / hardware cvt behaviour)
 
 
@@ -109,7 +124,7 @@ def unpack_codes(packed: np.ndarray) -> np.ndarray:
 
 # --------------------------------------------------------------------------- quantise / dequantise
 def quantize(x: np.ndarray, fmt: int):
-    """fp32 [rows,K] -> (packed uint8 [rows,3K/4], scales uint8 [rows,K/32])."""
+    """fp32 [rows,K] -> (packed uint8 [rows,3K/4] for fp6 or [rows,K] for fp8, scales uint8 [rows,K/32])."""
     x = np.ascontiguousarray(x, dtype=np.float32)
     rows, K = x.shape
     assert K % 32 == 0
@@ -118,17 +133,23 @@ def quantize(x: np.ndarray, fmt: int):
     sb = scale_bytes_from_amax(amax, fmt)
     e = sb.astype(np.int32) - 127
     v = np.ldexp(xb.astype(np.float64), -e[..., None]).astype(np.float32)  # exact power-of-two scaling
-    codes = encode_elems(v, fmt)
-    return pack_codes(codes.reshape(rows, K)), sb
+    codes = encode_elems(v, fmt).reshape(rows, K)
+    return (codes if is_fp8(fmt) else pack_codes(codes)), sb
+
+
+def codes_of(packed: np.ndarray, fmt: int) -> np.ndarray:
+    """Operand bytes -> one code per element."""
+    return np.asarray(packed, dtype=np.uint8) if is_fp8(fmt) else unpack_codes(packed)
 
 
 def dequantize(packed: np.ndarray, scales: np.ndarray, fmt: int) -> np.ndarray:
-    """(packed [rows,3K/4], scales [rows,K/32]) -> fp32 [rows,K]."""
-    codes = unpack_codes(packed)
+    """(operand bytes, scales [rows,K/32]) -> fp32 [rows,K]."""
+    codes = codes_of(packed, fmt)
     rows, K = codes.shape
     vals = decode_table(fmt)[codes].reshape(rows, K // 32, 32)
     s = e8m0_decode(scales).reshape(rows, K // 32, 1)
-    return (vals * s).reshape(rows, K).astype(np.float32)
+    with np.errstate(over="ignore", invalid="ignore"):
+        return (vals * s).reshape(rows, K).astype(np.float32)
 
 
 def gemm_ref_torch(a_packed, sfa, b_packed, sfb, fmt_a=E2M3, fmt_b=None, threads=None, return_f32=False):
@@ -264,7 +285,7 @@ def _p(a, t):
 def c_quantize(x: np.ndarray, fmt: int):
     x = np.ascontiguousarray(x, dtype=np.float32)
     rows, K = x.shape
-    packed = np.empty((rows, K * 3 // 4), np.uint8)
+    packed = np.empty((rows, K if is_fp8(fmt) else K * 3 // 4), np.uint8)
     scales = np.empty((rows, K // 32), np.uint8)
     c_oracle().mxfp6_quantize(_p(x, ctypes.c_float), rows, K, fmt, _p(packed, ctypes.c_uint8), _p(scales, ctypes.c_uint8))
     return packed, scales
@@ -273,7 +294,7 @@ def c_quantize(x: np.ndarray, fmt: int):
 def c_dequantize(packed: np.ndarray, scales: np.ndarray, fmt: int) -> np.ndarray:
     packed = np.ascontiguousarray(packed, dtype=np.uint8)
     scales = np.ascontiguousarray(scales, dtype=np.uint8)
-    rows, K = packed.shape[0], packed.shape[1] * 4 // 3
+    rows, K = packed.shape[0], (packed.shape[1] if is_fp8(fmt) else packed.shape[1] * 4 // 3)
     out = np.empty((rows, K), np.float32)
     c_oracle().mxfp6_dequantize(_p(packed, ctypes.c_uint8), _p(scales, ctypes.c_uint8), rows, K, fmt, _p(out, ctypes.c_float))
     return out
@@ -287,7 +308,8 @@ def c_gemm_ref(a_packed, sfa, b_packed, sfb, fmt_a=E2M3, fmt_b=None, acc_mode=0,
     b_packed = np.ascontiguousarray(b_packed, np.uint8)
     sfa = np.ascontiguousarray(sfa, np.uint8)
     sfb = np.ascontiguousarray(sfb, np.uint8)
-    M, N, K = a_packed.shape[0], b_packed.shape[0], a_packed.shape[1] * 4 // 3
+    M, N = a_packed.shape[0], b_packed.shape[0]
+    K = a_packed.shape[1] if is_fp8(fmt_a) else a_packed.shape[1] * 4 // 3
     cb = np.empty((M, N), np.uint16)
     cf = np.empty((M, N), np.float32)
     ad = np.empty((M, N), np.float32) if want_absdot else None
@@ -309,10 +331,14 @@ def dequantize_torch(packed, scales, fmt: int):
     import torch
 
     rows = packed.shape[0]
-    K = packed.shape[1] // 3 * 4
-    b = packed.view(rows, -1, 3).to(torch.int32)
-    w = b[..., 0] | (b[..., 1] << 8) | (b[..., 2] << 16)
-    codes = torch.stack([w & 63, (w >> 6) & 63, (w >> 12) & 63, (w >> 18) & 63], dim=-1).view(rows, K)
+    if is_fp8(fmt):
+        K = packed.shape[1]
+        codes = packed
+    else:
+        K = packed.shape[1] // 3 * 4
+        b = packed.view(rows, -1, 3).to(torch.int32)
+        w = b[..., 0] | (b[..., 1] << 8) | (b[..., 2] << 16)
+        codes = torch.stack([w & 63, (w >> 6) & 63, (w >> 12) & 63, (w >> 18) & 63], dim=-1).view(rows, K)
     lut = torch.from_numpy(decode_table(fmt))
     vals = lut[codes.long()]
     s = torch.from_numpy(e8m0_decode(np.arange(256, dtype=np.uint8)))[scales.long()]

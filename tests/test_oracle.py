@@ -178,3 +178,68 @@ def test_mixed_format_gemm():
     _, cf, _ = R.c_gemm_ref(pa, sa, pb, sb, fmt_a=R.E3M2, fmt_b=R.E2M3, acc_mode=1)
     want = R.dequantize(pa, sa, R.E3M2).astype(np.float64) @ R.dequantize(pb, sb, R.E2M3).astype(np.float64).T
     np.testing.assert_allclose(cf, want, rtol=1e-6)
+
+
+# ------------------------------------------------------------------------------- MX-FP8 operands
+@pytest.fixture(scope="module")
+def kat8():
+    with open(os.path.join(GOLD, "toolkit_fp8_kat.json")) as f:
+        return json.load(f)
+
+
+def test_fp8_decode_tables_match_toolkit_and_torch(kat8):
+    import torch
+    for fmt, key, tdt in ((R.E4M3, "decode_e4m3", torch.float8_e4m3fn), (R.E5M2, "decode_e5m2", torch.float8_e5m2)):
+        mine = R.decode_table(fmt)
+        tk = _f32(kat8[key])
+        th = torch.arange(256, dtype=torch.uint8).view(tdt).float().numpy()
+        fin = np.isfinite(mine)
+        np.testing.assert_array_equal(mine[fin], tk[fin])
+        np.testing.assert_array_equal(mine[fin], th[fin])
+        assert (np.isnan(mine) == np.isnan(th)).all()
+        L = R.c_oracle()
+        for c in range(256):
+            v = L.mxfp6_decode_elem(c, fmt)
+            assert (np.isnan(v) and np.isnan(mine[c])) or v == mine[c]
+
+
+def test_fp8_encode_matches_toolkit(kat8):
+    enc = np.array(kat8["encode"], dtype=np.uint32)
+    x = enc[:, 0].copy().view(np.float32)
+    np.testing.assert_array_equal(R.encode_elems(x, R.E4M3), enc[:, 1].astype(np.uint8))
+    np.testing.assert_array_equal(R.encode_elems(x, R.E5M2), enc[:, 2].astype(np.uint8))
+    L = R.c_oracle()
+    got4 = np.array([L.mxfp6_encode_elem(float(v), R.E4M3) for v in x], dtype=np.uint8)
+    got5 = np.array([L.mxfp6_encode_elem(float(v), R.E5M2) for v in x], dtype=np.uint8)
+    np.testing.assert_array_equal(got4, enc[:, 1].astype(np.uint8))
+    np.testing.assert_array_equal(got5, enc[:, 2].astype(np.uint8))
+
+
+@pytest.mark.parametrize("fmt", [R.E4M3, R.E5M2])
+def test_fp8_quantize_numpy_equals_c_and_block_rule(fmt):
+    A, _ = R.make_inputs("lognormal", 40, 8, 256, seed=4)
+    p1, s1 = R.quantize(A, fmt)
+    p2, s2 = R.c_quantize(A, fmt)
+    assert p1.shape == (40, 256)
+    np.testing.assert_array_equal(s1, s2)
+    np.testing.assert_array_equal(p1, p2)
+    np.testing.assert_array_equal(R.dequantize(p1, s1, fmt), R.c_dequantize(p1, s1, fmt))
+    x = np.zeros((2, 64), np.float32)
+    x[0, :32] = 1.0
+    x[1, 0] = 500.0 if fmt == R.E4M3 else 60000.0     # scaled value lands between max and the next power of two
+    p, s = R.quantize(x, fmt)
+    emax = 8 if fmt == R.E4M3 else 15
+    assert s[0, 0] == 127 - emax
+    d = R.dequantize(p, s, fmt)
+    assert d[1, 0] == (448.0 if fmt == R.E4M3 else 57344.0) * 2.0 ** (int(s[1, 0]) - 127)
+    p2, s2 = R.quantize(d, fmt)
+    np.testing.assert_array_equal(p2[0, :32], p[0, :32])
+
+
+def test_mixed_fp8_fp6_gemm_oracles_agree():
+    A, B = R.make_inputs("ffn", 8, 16, 128, seed=2)
+    pa, sa = R.quantize(A, R.E4M3)
+    pb, sb = R.quantize(B, R.E2M3)
+    _, cf, _ = R.c_gemm_ref(pa, sa, pb, sb, fmt_a=R.E4M3, fmt_b=R.E2M3, acc_mode=1)
+    want = R.dequantize(pa, sa, R.E4M3).astype(np.float64) @ R.dequantize(pb, sb, R.E2M3).astype(np.float64).T
+    np.testing.assert_allclose(cf, want, rtol=1e-6)
