@@ -10,6 +10,8 @@ LIB_PATH = os.environ.get("MXFP6_LIBRARY") or os.path.join(_PKG, "libmxfp6.so") 
 
 E2M3 = 0
 E3M2 = 1
+E4M3 = 2   # MX-FP8
+E5M2 = 3   # MX-FP8
 
 OK, ERR_BAD_ARG, ERR_CUDA, ERR_DEVICE_WAIT, ERR_UNSUPPORTED = 0, 1, 2, 3, 4
 

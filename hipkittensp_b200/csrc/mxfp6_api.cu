@@ -5,6 +5,7 @@
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_fp6.h>
+#include <cuda_fp8.h>
 #include <cuda_runtime.h>
 
 #include <cstdarg>
@@ -106,6 +107,7 @@ static std::map<MapKey, CUtensorMap> g_maps;
 
 // kind 0: packed 6-bit operand [rows, K] (inner = K elements), box 128 x box_rows, 128-byte swizzle
 // kind 1: scale bytes [rows, K/32] (inner = K/32 bytes), box 16 x box_rows, no swizzle
+// kind 3: fp8 operand [rows, K] (inner = K bytes), box 128 x box_rows, 128-byte swizzle
 // kind 2: bf16 output block [rows, inner] with a row stride of stride_bytes, box 64 x box_rows, 128-byte swizzle
 static int make_map(const void* ptr, int64_t rows, int64_t inner, int box_rows, int kind, CUtensorMap* out,
                     int64_t stride_bytes = 0) {
@@ -118,11 +120,11 @@ static int make_map(const void* ptr, int64_t rows, int64_t inner, int box_rows, 
     int rc = get_encode_fn();
     if (rc) return rc;
     cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)rows};
-    cuuint64_t strides[1] = {(cuuint64_t)(kind == 0 ? inner * 3 / 4 : kind == 1 ? inner : stride_bytes)};
-    cuuint32_t box[2] = {(cuuint32_t)(kind == 0 ? 128 : kind == 1 ? 16 : 64), (cuuint32_t)box_rows};
+    cuuint64_t strides[1] = {(cuuint64_t)(kind == 0 ? inner * 3 / 4 : kind == 2 ? stride_bytes : inner)};
+    cuuint32_t box[2] = {(cuuint32_t)(kind == 1 ? 16 : kind == 2 ? 64 : 128), (cuuint32_t)box_rows};
     cuuint32_t estr[2] = {1, 1};
     const CUtensorMapDataType dt = kind == 0 ? CU_TENSOR_MAP_DATA_TYPE_16U6_ALIGN16B
-                                 : kind == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+                                 : kind == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
     CUresult r = g_encode(out, dt, 2,
                           const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                           kind == 1 ? CU_TENSOR_MAP_SWIZZLE_NONE : CU_TENSOR_MAP_SWIZZLE_128B,
@@ -134,6 +136,14 @@ static int make_map(const void* ptr, int64_t rows, int64_t inner, int box_rows, 
     if (g_maps.size() > 256) g_maps.clear();
     g_maps[key] = *out;
     return MXFP6_OK;
+}
+
+// ---------------------------------------------------------------------------------- operand formats
+static bool fmt_valid(int f) { return f == MXFP6_E2M3 || f == MXFP6_E3M2 || f == MXFP8_E4M3 || f == MXFP8_E5M2; }
+static bool fmt_is_fp8(int f) { return f == MXFP8_E4M3 || f == MXFP8_E5M2; }
+static int fmt_row_bytes_per_128(int f) { return fmt_is_fp8(f) ? 128 : 96; }   // bytes of 128 elements in HBM
+static uint32_t fmt_mma_code(int f) {      // operand format field of kind::mxf8f6f4
+    return f == MXFP6_E2M3 ? kFmtE2M3 : f == MXFP6_E3M2 ? kFmtE3M2 : f == MXFP8_E4M3 ? 0u : 1u;
 }
 
 // ---------------------------------------------------------------------------------- GEMM dispatch
@@ -256,8 +266,8 @@ static int gemm_impl(const void* a, const void* sfa, const void* b, const void* 
     void* c = dst.c[0];
     if (M < 0 || N < 0 || K < 0) return fail(MXFP6_ERR_BAD_ARG, "negative dimension (M=%lld N=%lld K=%lld)", (long long)M, (long long)N, (long long)K);
     if (K % 128 != 0) return fail(MXFP6_ERR_BAD_ARG, "K=%lld must be a multiple of 128", (long long)K);
-    if ((fmt_a != MXFP6_E2M3 && fmt_a != MXFP6_E3M2) || (fmt_b != MXFP6_E2M3 && fmt_b != MXFP6_E3M2))
-        return fail(MXFP6_ERR_BAD_ARG, "format must be MXFP6_E2M3 (0) or MXFP6_E3M2 (1)");
+    if (!fmt_valid(fmt_a) || !fmt_valid(fmt_b))
+        return fail(MXFP6_ERR_BAD_ARG, "format must be MXFP6_E2M3 (0), MXFP6_E3M2 (1), MXFP8_E4M3 (2) or MXFP8_E5M2 (3)");
     if (M > 0x7fffff00LL || N > 0x7fffff00LL || K > 0x7fffff00LL) return fail(MXFP6_ERR_BAD_ARG, "dimension too large");
     if (M == 0 || N == 0) return MXFP6_OK;
     if (!c) return fail(MXFP6_ERR_BAD_ARG, "null C");
@@ -274,7 +284,8 @@ static int gemm_impl(const void* a, const void* sfa, const void* b, const void* 
         return MXFP6_OK;
     }
     if (!a || !b || !sfa || !sfb) return fail(MXFP6_ERR_BAD_ARG, "null operand pointer");
-    if (((uintptr_t)a & 31) || ((uintptr_t)b & 31)) return fail(MXFP6_ERR_BAD_ARG, "packed operands must be 32-byte aligned");
+    if (((uintptr_t)a & (fmt_is_fp8(fmt_a) ? 15 : 31)) || ((uintptr_t)b & (fmt_is_fp8(fmt_b) ? 15 : 31)))
+        return fail(MXFP6_ERR_BAD_ARG, "operands must be 32-byte aligned (fp6) / 16-byte aligned (fp8)");
     if (((uintptr_t)sfa & 3) || ((uintptr_t)sfb & 3)) return fail(MXFP6_ERR_BAD_ARG, "scale arrays must be 4-byte aligned");
     if ((uintptr_t)c & 1) return fail(MXFP6_ERR_BAD_ARG, "C must be 2-byte aligned");
 
@@ -311,9 +322,9 @@ static int gemm_impl(const void* a, const void* sfa, const void* b, const void* 
     const int fp = pl.swap ? fmt_b : fmt_a, fq = pl.swap ? fmt_a : fmt_b;
 
     CUtensorMap tp, tq, tsp, tsq;
-    if ((rc = make_map(pp, prow, K, 128, 0, &tp))) return rc;
+    if ((rc = make_map(pp, prow, K, 128, fmt_is_fp8(fp) ? 3 : 0, &tp))) return rc;
     const bool sf_tma = sf_tma_ok;
-    if ((rc = make_map(qp, qrow, K, pl.pair ? 128 : pl.bn, 0, &tq))) return rc;
+    if ((rc = make_map(qp, qrow, K, pl.pair ? 128 : pl.bn, fmt_is_fp8(fq) ? 3 : 0, &tq))) return rc;
     if (sf_tma) {
         if ((rc = make_map(sp, prow, K / 32, 128, 1, &tsp))) return rc;
         if ((rc = make_map(sq, qrow, K / 32, pl.bn, 1, &tsq))) return rc;   // pair kernel: all 256 Q rows per CTA
@@ -326,11 +337,11 @@ static int gemm_impl(const void* a, const void* sfa, const void* b, const void* 
     P.kblocks = (int)(K / 128);
     P.tiles_p = pl.tiles_p; P.tiles_q = pl.tiles_q;
     P.ldc = (int)dst.ldc; P.c_rows = (int)M; P.c_cols = (int)N;
-    P.idesc = make_idesc_m(fp == MXFP6_E2M3 ? kFmtE2M3 : kFmtE3M2, fq == MXFP6_E2M3 ? kFmtE2M3 : kFmtE3M2,
-                           pl.pair ? 256u : 128u, (uint32_t)pl.bn);
+    P.idesc = make_idesc_m(fmt_mma_code(fp), fmt_mma_code(fq), pl.pair ? 256u : 128u, (uint32_t)pl.bn);
     P.sf_tma = sf_tma ? 1 : 0;
     P.sf_ld = (int)(K / 32);
-    P.stage_tx_bytes = (128 + (pl.pair ? 128 : pl.bn)) * env_int("MXFP6_TX_BYTES_PER_ROW", 96);
+    // bytes a stage's two loads credit to its mbarrier: the global bytes of the boxes (fp6: 96 per 128 elements)
+    P.stage_tx_bytes = 128 * fmt_row_bytes_per_128(fp) + (pl.pair ? 128 : pl.bn) * fmt_row_bytes_per_128(fq);
     P.sfp = (const uint8_t*)sp; P.sfq = (const uint8_t*)sq;
     P.c = (__nv_bfloat16*)c;
     for (int i = 1; i < dst.n; ++i) P.c_more[i - 1] = (__nv_bfloat16*)dst.c[i];
@@ -400,7 +411,8 @@ template <> __device__ __forceinline__ void load4<__nv_bfloat16>(const __nv_bflo
 template <typename T, int FMT>
 __global__ void __launch_bounds__(256) quantize_kernel(const T* __restrict__ src, int64_t n_quads, uint32_t* __restrict__ packed_words,
                                                        uint8_t* __restrict__ scales) {
-    constexpr int EMAX = FMT == MXFP6_E2M3 ? 2 : 4;
+    constexpr int EMAX = FMT == MXFP6_E2M3 ? 2 : FMT == MXFP6_E3M2 ? 4 : FMT == MXFP8_E4M3 ? 8 : 15;
+    constexpr bool FP8 = FMT == MXFP8_E4M3 || FMT == MXFP8_E5M2;
     const int lane = threadIdx.x & 31;
     // n_quads is a multiple of 8, so whole warps share the loop trip count up to the tail handled by `live`
     for (int64_t q0 = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) & ~31LL; q0 < n_quads; q0 += (int64_t)gridDim.x * blockDim.x) {
@@ -424,15 +436,23 @@ __global__ void __launch_bounds__(256) quantize_kernel(const T* __restrict__ src
         const int h = (-e) / 2;
         const float f1 = __uint_as_float((uint32_t)(h + 127) << 23), f2 = __uint_as_float((uint32_t)(-e - h + 127) << 23);
         uint32_t w = 0;
+        if constexpr (FP8) {
+            // one byte per element: this thread's 4 codes are one 32-bit word of the operand
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const uint32_t code = __nv_cvt_float_to_fp6(x[i] * f1 * f2, FMT == MXFP6_E2M3 ? __NV_E2M3 : __NV_E3M2, cudaRoundNearest) & 63u;
-            w |= code << (6 * i);
+            for (int i = 0; i < 4; ++i)
+                w |= (uint32_t)__nv_cvt_float_to_fp8(x[i] * f1 * f2, __NV_SATFINITE, FMT == MXFP8_E4M3 ? __NV_E4M3 : __NV_E5M2) << (8 * i);
+            if (live) packed_words[q] = w;
+        } else {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const uint32_t code = __nv_cvt_float_to_fp6(x[i] * f1 * f2, FMT == MXFP6_E2M3 ? __NV_E2M3 : __NV_E3M2, cudaRoundNearest) & 63u;
+                w |= code << (6 * i);
+            }
+            // 4 lanes hold 4 x 24 bits = three 32-bit words of the packed stream
+            const uint32_t wn = __shfl_down_sync(0xffffffffu, w, 1);
+            const int i4 = lane & 3;
+            if (live && i4 < 3) packed_words[(q >> 2) * 3 + i4] = (w >> (8 * i4)) | (wn << (24 - 8 * i4));
         }
-        // 4 lanes hold 4 x 24 bits = three 32-bit words of the packed stream
-        const uint32_t wn = __shfl_down_sync(0xffffffffu, w, 1);
-        const int i4 = lane & 3;
-        if (live && i4 < 3) packed_words[(q >> 2) * 3 + i4] = (w >> (8 * i4)) | (wn << (24 - 8 * i4));
         if (live && (lane & 7) == 0) scales[q >> 3] = (uint8_t)sb;
     }
 }
@@ -440,11 +460,19 @@ __global__ void __launch_bounds__(256) quantize_kernel(const T* __restrict__ src
 template <int FMT>
 __global__ void __launch_bounds__(256) dequantize_kernel(const uint8_t* __restrict__ packed, const uint8_t* __restrict__ scales,
                                                          int64_t n_quads, float* __restrict__ out) {
-    constexpr int MB = FMT == MXFP6_E2M3 ? 3 : 2;
-    constexpr int BIAS = FMT == MXFP6_E2M3 ? 1 : 3;
+    constexpr bool FP8 = FMT == MXFP8_E4M3 || FMT == MXFP8_E5M2;
+    constexpr int BITS = FP8 ? 8 : 6;
+    constexpr int MB = (FMT == MXFP6_E2M3 || FMT == MXFP8_E4M3) ? 3 : 2;
+    constexpr int EB = BITS - 1 - MB;
+    constexpr int BIAS = FMT == MXFP6_E2M3 ? 1 : FMT == MXFP6_E3M2 ? 3 : FMT == MXFP8_E4M3 ? 7 : 15;
     for (int64_t q = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; q < n_quads; q += (int64_t)gridDim.x * blockDim.x) {
-        const uint8_t* p = packed + q * 3;
-        const uint32_t w = (uint32_t)p[0] | ((uint32_t)p[1] << 8) | ((uint32_t)p[2] << 16);
+        uint32_t w;
+        if constexpr (FP8) {
+            w = *reinterpret_cast<const uint32_t*>(packed + q * 4);
+        } else {
+            const uint8_t* p = packed + q * 3;
+            w = (uint32_t)p[0] | ((uint32_t)p[1] << 8) | ((uint32_t)p[2] << 16);
+        }
         const uint32_t sbyte = scales[q >> 3];
         // 2^(sbyte-127) as fp32 (sbyte 0 -> 2^-127, an fp32 subnormal)
         const float s = sbyte == 255 ? __uint_as_float(0x7fc00000u) : sbyte == 0 ? __uint_as_float(0x00400000u) : __uint_as_float(sbyte << 23);
@@ -452,11 +480,13 @@ __global__ void __launch_bounds__(256) dequantize_kernel(const uint8_t* __restri
         float* of = reinterpret_cast<float*>(&o);
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-            const uint32_t c = (w >> (6 * i)) & 63u;
-            const uint32_t e = (c >> MB) & ((1u << (5 - MB)) - 1), m = c & ((1u << MB) - 1);
+            const uint32_t c = (w >> (BITS * i)) & ((1u << BITS) - 1);
+            const uint32_t e = (c >> MB) & ((1u << EB) - 1), m = c & ((1u << MB) - 1);
             float mag = e ? __uint_as_float(((e - BIAS + 127) << 23) | (m << (23 - MB)))
                           : (float)m * __uint_as_float((uint32_t)(1 - BIAS - MB + 127) << 23);
-            of[i] = ((c >> 5) ? -mag : mag) * s;
+            if (FMT == MXFP8_E4M3 && e == 15 && m == 7) mag = __uint_as_float(0x7fc00000u);
+            if (FMT == MXFP8_E5M2 && e == 31) mag = m ? __uint_as_float(0x7fc00000u) : __uint_as_float(0x7f800000u);
+            of[i] = ((c >> (BITS - 1)) ? -mag : mag) * s;
         }
         *reinterpret_cast<float4*>(out + q * 4) = o;
     }
@@ -572,7 +602,7 @@ extern "C" int mxfp6_gemm_noalloc(const void* a, const void* sfa, const void* b,
 extern "C" int mxfp6_quantize(const void* src, int src_dtype, int64_t rows, int64_t K, int fmt, void* packed, void* scales,
                               void* stream) {
     if (rows < 0 || K < 0 || K % 32) return fail(MXFP6_ERR_BAD_ARG, "quantize: rows=%lld K=%lld (K must be a multiple of 32)", (long long)rows, (long long)K);
-    if (fmt != MXFP6_E2M3 && fmt != MXFP6_E3M2) return fail(MXFP6_ERR_BAD_ARG, "quantize: bad format %d", fmt);
+    if (!fmt_valid(fmt)) return fail(MXFP6_ERR_BAD_ARG, "quantize: bad format %d", fmt);
     if (src_dtype != 0 && src_dtype != 1) return fail(MXFP6_ERR_BAD_ARG, "quantize: src_dtype must be 0 (fp32) or 1 (bf16)");
     if (rows == 0 || K == 0) return MXFP6_OK;
     if (!src || !packed || !scales) return fail(MXFP6_ERR_BAD_ARG, "quantize: null pointer");
@@ -586,8 +616,13 @@ extern "C" int mxfp6_quantize(const void* src, int src_dtype, int64_t rows, int6
     if (blocks > cap) blocks = cap;
     cudaStream_t st = (cudaStream_t)stream;
 #define QK(T, F) quantize_kernel<T, F><<<(unsigned)blocks, 256, 0, st>>>((const T*)src, nq, (uint32_t*)packed, (uint8_t*)scales)
-    if (src_dtype == 0) { if (fmt == MXFP6_E2M3) QK(float, MXFP6_E2M3); else QK(float, MXFP6_E3M2); }
-    else { if (fmt == MXFP6_E2M3) QK(__nv_bfloat16, MXFP6_E2M3); else QK(__nv_bfloat16, MXFP6_E3M2); }
+    if (src_dtype == 0) {
+        if (fmt == MXFP6_E2M3) QK(float, MXFP6_E2M3); else if (fmt == MXFP6_E3M2) QK(float, MXFP6_E3M2);
+        else if (fmt == MXFP8_E4M3) QK(float, MXFP8_E4M3); else QK(float, MXFP8_E5M2);
+    } else {
+        if (fmt == MXFP6_E2M3) QK(__nv_bfloat16, MXFP6_E2M3); else if (fmt == MXFP6_E3M2) QK(__nv_bfloat16, MXFP6_E3M2);
+        else if (fmt == MXFP8_E4M3) QK(__nv_bfloat16, MXFP8_E4M3); else QK(__nv_bfloat16, MXFP8_E5M2);
+    }
 #undef QK
     CUDA_TRY(cudaGetLastError());
     return MXFP6_OK;
@@ -596,7 +631,7 @@ extern "C" int mxfp6_quantize(const void* src, int src_dtype, int64_t rows, int6
 extern "C" int mxfp6_dequantize(const void* packed, const void* scales, int64_t rows, int64_t K, int fmt, void* out_f32,
                                 void* stream) {
     if (rows < 0 || K < 0 || K % 32) return fail(MXFP6_ERR_BAD_ARG, "dequantize: rows=%lld K=%lld (K must be a multiple of 32)", (long long)rows, (long long)K);
-    if (fmt != MXFP6_E2M3 && fmt != MXFP6_E3M2) return fail(MXFP6_ERR_BAD_ARG, "dequantize: bad format %d", fmt);
+    if (!fmt_valid(fmt)) return fail(MXFP6_ERR_BAD_ARG, "dequantize: bad format %d", fmt);
     if (rows == 0 || K == 0) return MXFP6_OK;
     if (!packed || !scales || !out_f32) return fail(MXFP6_ERR_BAD_ARG, "dequantize: null pointer");
     if ((uintptr_t)out_f32 & 15) return fail(MXFP6_ERR_BAD_ARG, "dequantize: output must be 16-byte aligned");
@@ -608,8 +643,10 @@ extern "C" int mxfp6_dequantize(const void* packed, const void* scales, int64_t 
     const int64_t cap = (int64_t)d->sm_count * 16;
     if (blocks > cap) blocks = cap;
     cudaStream_t st = (cudaStream_t)stream;
-    if (fmt == MXFP6_E2M3) dequantize_kernel<MXFP6_E2M3><<<(unsigned)blocks, 256, 0, st>>>((const uint8_t*)packed, (const uint8_t*)scales, nq, (float*)out_f32);
-    else dequantize_kernel<MXFP6_E3M2><<<(unsigned)blocks, 256, 0, st>>>((const uint8_t*)packed, (const uint8_t*)scales, nq, (float*)out_f32);
+#define DQ(F) dequantize_kernel<F><<<(unsigned)blocks, 256, 0, st>>>((const uint8_t*)packed, (const uint8_t*)scales, nq, (float*)out_f32)
+    if (fmt == MXFP6_E2M3) DQ(MXFP6_E2M3); else if (fmt == MXFP6_E3M2) DQ(MXFP6_E3M2);
+    else if (fmt == MXFP8_E4M3) DQ(MXFP8_E4M3); else DQ(MXFP8_E5M2);
+#undef DQ
     CUDA_TRY(cudaGetLastError());
     return MXFP6_OK;
 }

@@ -50,16 +50,17 @@ void dispatch_micro(py::object A, py::object B, py::object C, py::object scale_A
         if (t->shape[0] != 1 || t->shape[1] != 1) throw std::runtime_error("Expected 2-D tensors");
     // M from A, N from C, K from A -- the reference's rule (256_256_64_32_with16x32.cpp:52-54)
     const int64_t M = a.shape[2], N = c.shape[3];
-    if (a.shape[3] % 3 != 0) throw std::runtime_error("A.shape[1] must be 3K/4 bytes");
-    const int64_t K = a.shape[3] / 3 * 4;
+    const bool fp8 = fmt == MXFP8_E4M3 || fmt == MXFP8_E5M2;
+    if (!fp8 && a.shape[3] % 3 != 0) throw std::runtime_error("A.shape[1] must be 3K/4 bytes");
+    const int64_t K = fp8 ? a.shape[3] : a.shape[3] / 3 * 4;
     if (K % 128 != 0) throw std::runtime_error("K must be a multiple of 128");
     if (c.shape[2] != M) throw std::runtime_error("C.shape[0] must equal A.shape[0]");
-    if (b.shape[2] != N || b.shape[3] != a.shape[3]) throw std::runtime_error("B must be [N, 3K/4]");
+    if (b.shape[2] != N || b.shape[3] != a.shape[3]) throw std::runtime_error("B must be [N, 3K/4] (fp6) or [N, K] (fp8)");
     if (sa.shape[2] != M || sa.shape[3] != K / 32) throw std::runtime_error("scale_A must be [M, K/32]");
     if (sb.shape[2] != N || sb.shape[3] != K / 32) throw std::runtime_error("scale_B must be [N, K/32]");
     if (a.device != b.device || a.device != c.device || a.device != sa.device || a.device != sb.device)
         throw std::runtime_error("all tensors must be on the same device");
-    if (fmt != MXFP6_E2M3 && fmt != MXFP6_E3M2) throw std::runtime_error("fmt must be 0 (E2M3) or 1 (E3M2)");
+    if (fmt < 0 || fmt > 3) throw std::runtime_error("fmt must be 0 (E2M3), 1 (E3M2), 2 (fp8 E4M3) or 3 (fp8 E5M2)");
 
     // launch on torch's current stream of the tensors' device, with that device current
     py::module_ cuda = py::module_::import("torch").attr("cuda");

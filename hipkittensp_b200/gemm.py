@@ -11,7 +11,7 @@ from __future__ import annotations
 import torch
 
 from . import _lib
-from ._lib import E2M3, E3M2, check, lib
+from ._lib import E2M3, E3M2, E4M3, E5M2, check, lib
 
 
 def _accept(t, name: str, dtype) -> None:
@@ -29,6 +29,15 @@ def _accept(t, name: str, dtype) -> None:
         raise RuntimeError(f"{name} must be 2-D")
 
 
+def _k_of(t, fmt: int, name: str) -> int:
+    """K of an operand [rows, bytes]: 4 elements per 3 bytes for fp6, 1 per byte for fp8."""
+    if fmt in (E4M3, E5M2):
+        return t.shape[1]
+    if t.shape[1] % 3:
+        raise RuntimeError(f"{name}.shape[1] must be 3K/4 bytes")
+    return t.shape[1] // 3 * 4
+
+
 def _stream_ptr() -> int:
     return torch.cuda.current_stream().cuda_stream
 
@@ -36,7 +45,8 @@ def _stream_ptr() -> int:
 def dispatch_micro(A, B, C, scale_A, scale_B, fmt: int = E2M3, fmt_b: int | None = None) -> None:
     """C[M,N] (bf16, in place) = A[M,K] @ B[N,K]^T.
 
-    A [M,3K/4] u8 and B [N,3K/4] u8 are packed fp6 (format `fmt`; `fmt_b` if B differs),
+    A [M,3K/4] u8 and B [N,3K/4] u8 are packed fp6, or [rows,K] u8 for the fp8 formats (format `fmt`; `fmt_b` if
+    B differs),
     scale_A [M,K/32] u8 and scale_B [N,K/32] u8 are E8M0 bytes.  M is taken from A, N from C,
     K from A, as the reference does (256_256_64_32_with16x32.cpp:52-54)."""
     _accept(A, "A", torch.uint8)
@@ -45,15 +55,14 @@ def dispatch_micro(A, B, C, scale_A, scale_B, fmt: int = E2M3, fmt_b: int | None
     _accept(scale_A, "scale_A", torch.uint8)
     _accept(scale_B, "scale_B", torch.uint8)
     M, N = A.shape[0], C.shape[1]
-    if A.shape[1] % 3:
-        raise RuntimeError("A.shape[1] must be 3K/4 bytes")
-    K = A.shape[1] // 3 * 4
+    fb = fmt if fmt_b is None else fmt_b
+    K = _k_of(A, fmt, "A")
     if K % 128:
         raise RuntimeError("K must be a multiple of 128")
     if C.shape[0] != M:
         raise RuntimeError("C.shape[0] must equal A.shape[0]")
-    if tuple(B.shape) != (N, A.shape[1]):
-        raise RuntimeError("B must be [N, 3K/4]")
+    if B.shape[0] != N or _k_of(B, fb, "B") != K:
+        raise RuntimeError("B must be [N, 3K/4] (fp6) or [N, K] (fp8) with the K of A")
     if tuple(scale_A.shape) != (M, K // 32) or tuple(scale_B.shape) != (N, K // 32):
         raise RuntimeError("scales must be [rows, K/32]")
     if len({t.device for t in (A, B, C, scale_A, scale_B)}) != 1:
@@ -75,7 +84,7 @@ def dispatch_multi(A, B, dests, col_offset: int, scale_A, scale_B, fmt: int = E2
     _accept(scale_A, "scale_A", torch.uint8)
     _accept(scale_B, "scale_B", torch.uint8)
     M, N = A.shape[0], B.shape[0]
-    K = A.shape[1] // 3 * 4
+    K = _k_of(A, fmt, "A")
     if not 1 <= len(dests) <= 8:
         raise RuntimeError("1 to 8 destinations")
     ldc = dests[0].stride(0)
@@ -100,7 +109,7 @@ def gemm(A, scale_A, B, scale_B, fmt: int = E2M3, fmt_b: int | None = None, out=
 
 
 def quantize(x: torch.Tensor, fmt: int = E2M3):
-    """fp32 or bf16 [rows,K] on the GPU -> (packed u8 [rows,3K/4], scales u8 [rows,K/32])."""
+    """fp32 or bf16 [rows,K] on the GPU -> (operand bytes u8 [rows,3K/4] for fp6 / [rows,K] for fp8, scales u8 [rows,K/32])."""
     if x.device.type == "cpu":
         raise RuntimeError("Tensor must be on CUDA device")
     if x.dtype not in (torch.float32, torch.bfloat16) or x.dim() != 2 or not x.is_contiguous():
@@ -108,7 +117,7 @@ def quantize(x: torch.Tensor, fmt: int = E2M3):
     rows, K = x.shape
     if K % 32:
         raise RuntimeError("K must be a multiple of 32")
-    packed = torch.empty((rows, K * 3 // 4), dtype=torch.uint8, device=x.device)
+    packed = torch.empty((rows, K if fmt in (E4M3, E5M2) else K * 3 // 4), dtype=torch.uint8, device=x.device)
     scales = torch.empty((rows, K // 32), dtype=torch.uint8, device=x.device)
     with torch.cuda.device(x.device):
         check(lib.mxfp6_quantize(x.data_ptr(), 0 if x.dtype == torch.float32 else 1, rows, K, fmt,
@@ -120,7 +129,7 @@ def dequantize(packed: torch.Tensor, scales: torch.Tensor, fmt: int = E2M3) -> t
     """(packed, scales) on the GPU -> fp32 [rows,K]."""
     _accept(packed, "packed", torch.uint8)
     _accept(scales, "scales", torch.uint8)
-    rows, K = packed.shape[0], packed.shape[1] // 3 * 4
+    rows, K = packed.shape[0], _k_of(packed, fmt, "packed")
     out = torch.empty((rows, K), dtype=torch.float32, device=packed.device)
     with torch.cuda.device(packed.device):
         check(lib.mxfp6_dequantize(packed.data_ptr(), scales.data_ptr(), rows, K, fmt, out.data_ptr(), _stream_ptr()))

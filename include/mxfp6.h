@@ -32,6 +32,11 @@ extern "C" {
 
 #define MXFP6_E2M3 0
 #define MXFP6_E3M2 1
+/* MX-FP8 operands run through the same instruction (kind::mxf8f6f4) and the same entry points: one byte per
+ * element, row-major [rows, K], 16-byte aligned, same E8M0 scale per 32 elements.  A and B may differ in format.
+ * (The reference's main-branch GEMMs are fp8: kernels/gemm/fp8fp32/FP8_8wave/8_wave.cu.) */
+#define MXFP8_E4M3 2
+#define MXFP8_E5M2 3
 
 #define MXFP6_OK 0
 #define MXFP6_ERR_BAD_ARG 1      /* shape / alignment / format / null pointer */
@@ -51,8 +56,8 @@ const char* mxfp6_last_error(void);
  * (kernels/gemm/bf16fp32/256_256_64_32_with16x32.cpp:383-387) with the operand set of
  * micro_globals (:47-58) extended by the two scale tensors in the argument order of the
  * reference's scale-taking kernel (kernels/torch_scaled/scaled_matmul.cu:17-18).
- *   a   [M, 3K/4] u8   sfa [M, K/32] u8    fmt_a MXFP6_E2M3 | MXFP6_E3M2
- *   b   [N, 3K/4] u8   sfb [N, K/32] u8    fmt_b likewise
+ *   a   [M, 3K/4] u8 (fp6) or [M, K] u8 (fp8)   sfa [M, K/32] u8    fmt_a one of the four format codes
+ *   b   [N, 3K/4] u8 (fp6) or [N, K] u8 (fp8)   sfb [N, K/32] u8    fmt_b likewise
  *   c   [M, N] bf16, written in place
  * Shapes that split output tiles along K use a per-device scratch buffer that the library
  * allocates on first need (cudaMalloc) and keeps; concurrent calls on different streams of one
@@ -106,8 +111,8 @@ int mxfp6_gemm_noalloc(const void* a, const void* sfa, const void* b, const void
 
 /*
  * Block quantiser: src [rows, K] (src_dtype 0 = fp32, 1 = bf16), K % 32 == 0  ->
- * packed [rows, 3K/4] + scales [rows, K/32].  Scale exponent = floor(log2(amax)) - 2 (E2M3) or - 4
- * (E3M2), elements rounded to nearest even and saturated.  The step in front of the GEMM; the
+ * packed [rows, 3K/4] (fp6) or [rows, K] (fp8) + scales [rows, K/32].  Scale exponent = floor(log2(amax)) - 2
+ * (E2M3), - 4 (E3M2), - 8 (E4M3) or - 15 (E5M2); elements rounded to nearest even and saturated.  The step in front of the GEMM; the
  * reference's fp8 harness does it on the host (kernels/gemm/fp8fp32/FP8_8wave/8_wave.cu:258-268).
  */
 int mxfp6_quantize(const void* src, int src_dtype, int64_t rows, int64_t K, int fmt,

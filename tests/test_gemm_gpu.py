@@ -206,3 +206,18 @@ def test_host_gemm_pipeline_matches_direct_calls():
         h = [t.cuda() for t in sets[i % 3]]
         want = hk.gemm(h[0], h[1], h[2], h[3]).cpu()
         assert torch.equal(outs[i].view(torch.int16), want.view(torch.int16))
+
+
+# ------------------------------------------------------------------------------- MX-FP8 operands
+@pytest.mark.parametrize("fmt", [R.E4M3, R.E5M2])
+@pytest.mark.parametrize("shape,force", [((256, 384, 512), None), ((512, 768, 1024), "256,0,0,1"),
+                                         ((16, 2048, 1024), None), ((129, 200, 384), None)])
+def test_fp8_operands(fmt, shape, force):
+    M, N, K = shape
+    _case("lognormal", M, N, K, fmt=fmt, seed=3, force=force)
+
+
+@pytest.mark.parametrize("fa,fb", [(R.E4M3, R.E2M3), (R.E3M2, R.E5M2), (R.E2M3, R.E4M3)])
+def test_mixed_fp8_fp6_operands(fa, fb):
+    _case("ffn", 256, 512, 1024, fmt=fa, fmt_b=fb, seed=8)
+    _case("decode", 16, 1024, 512, fmt=fa, fmt_b=fb, seed=9)

@@ -67,3 +67,27 @@ def test_roundtrip_large_property():
     p2, s2 = hk.quantize(d, R.E2M3)
     assert torch.equal(p, p2) and torch.equal(s, s2)
     assert hk.device_status() == 0
+
+
+@pytest.mark.parametrize("fmt", [R.E4M3, R.E5M2])
+@pytest.mark.parametrize("config", ["normal", "lognormal", "ffn"])
+def test_fp8_quantize_bit_exact(fmt, config):
+    A, B = R.make_inputs(config, 96, 200, 512, seed=7)
+    for x in (A, B):
+        pa, sa = R.quantize(x, fmt)
+        gp, gs = hk.quantize(torch.from_numpy(x).cuda(), fmt)
+        np.testing.assert_array_equal(gs.cpu().numpy(), sa)
+        np.testing.assert_array_equal(gp.cpu().numpy(), pa)
+
+
+@pytest.mark.parametrize("fmt", [R.E4M3, R.E5M2])
+def test_fp8_dequantize_bit_exact(fmt):
+    rng = np.random.default_rng(2)
+    codes = rng.integers(0, 256, size=(32, 512), dtype=np.uint8)
+    codes[0, :256] = np.arange(256)
+    scales = rng.integers(1, 254, size=(32, 16), dtype=np.uint8)
+    want = R.dequantize(codes, scales, fmt)
+    got = hk.dequantize(torch.from_numpy(codes).cuda(), torch.from_numpy(scales).cuda(), fmt).cpu().numpy()
+    fin = np.isfinite(want)
+    np.testing.assert_array_equal(got[fin].view(np.uint32), want[fin].view(np.uint32))
+    assert (np.isnan(got) == np.isnan(want)).all()
