@@ -52,6 +52,7 @@ struct GemmParams {
     int* status;               // device status word
     unsigned long long wait_cycles;  // budget of one wait in clock cycles
     int group_p;               // pair kernel: P-tiles per rasterisation group
+    int early_p;               // swapped form: P (the weights) may be read before the preceding kernel has finished
     unsigned long long* dbg_times;   // debug builds: per-CTA time stamps
     int dbg;                   // experiment switches, honoured only by builds with MXFP6_DEBUG_KNOBS
 };
@@ -261,7 +262,10 @@ mxfp6_gemm_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constan
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    pdl_wait();                  // nothing above touches global memory; everything below may
+    // Nothing above touches global memory; everything below may.  With early_p the producer warp alone goes
+    // ahead and requests the first stages of P (weights that the preceding kernel does not write) before it waits.
+    const bool early = Cfg::SWAP && P.early_p != 0;
+    if (!(early && warp == 0)) pdl_wait();
     if (threadIdx.x == 0) MXFP6_STAMP(1);
 
     // =========================================================== warp 0: TMA producer
@@ -270,7 +274,35 @@ mxfp6_gemm_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constan
         SegIter<Cfg> it(P);
         Segment sg;
         uint32_t n_stage = 0, n_raw = 0;
+        uint32_t pre_stage = 0, pre_raw = 0;      // stages / scale slabs whose P half is already on its way
         bool ok = true;
+        if (early) {
+            SegIter<Cfg> it2(P);
+            Segment s2;
+            bool slabs = P.sf_tma != 0;
+            while (pre_stage < (uint32_t)Cfg::STAGES && it2.next(s2)) {
+                for (int k = s2.k0; k < s2.k1 && pre_stage < (uint32_t)Cfg::STAGES; ++k) {
+                    if (P.sf_tma && (k == s2.k0 || (k & 3) == 0)) {
+                        if (slabs && pre_raw < (uint32_t)Cfg::RAW_SLOTS) {
+                            if (elect_one_sync()) {
+                                mbar_arrive_expect_tx(bar_raw_full(pre_raw), Cfg::RAW_TX_BYTES);
+                                tma_load_2d(raw_base + pre_raw * Cfg::RAW_BYTES, &tm_sfp, bar_raw_full(pre_raw), (k >> 2) * 16, s2.p0);
+                            }
+                            ++pre_raw;
+                        } else {
+                            slabs = false;
+                        }
+                    }
+                    if (elect_one_sync()) {
+                        mbar_arrive_expect_tx(bar_full(pre_stage), (uint32_t)P.stage_tx_bytes);
+                        tma_load_2d(stage_base + pre_stage * Cfg::STAGE_BYTES, &tm_p, bar_full(pre_stage), k * Cfg::BK, s2.p0);
+                    }
+                    __syncwarp();
+                    ++pre_stage;
+                }
+            }
+            pdl_wait();          // the Q halves (activations) and all stores come after the preceding kernel
+        }
         while (ok && it.next(sg)) {
             for (int kb = sg.k0; kb < sg.k1 && ok;) {
                 // LOAD_BATCH K-blocks are requested back to back, so that each row's adjacent 96-byte pieces
@@ -285,8 +317,10 @@ mxfp6_gemm_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constan
                         if (!ok) break;
                         if (elect_one_sync()) {
                             const uint32_t dst = raw_base + r * Cfg::RAW_BYTES;
-                            mbar_arrive_expect_tx(bar_raw_full(r), Cfg::RAW_TX_BYTES);
-                            tma_load_2d(dst, &tm_sfp, bar_raw_full(r), (k >> 2) * 16, sg.p0);
+                            if (n_raw >= pre_raw) {
+                                mbar_arrive_expect_tx(bar_raw_full(r), Cfg::RAW_TX_BYTES);
+                                tma_load_2d(dst, &tm_sfp, bar_raw_full(r), (k >> 2) * 16, sg.p0);
+                            }
                             tma_load_2d(dst + Cfg::BM * 16, &tm_sfq, bar_raw_full(r), (k >> 2) * 16, sg.q0);
                         }
                         ++n_raw;
@@ -314,8 +348,10 @@ mxfp6_gemm_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constan
                             continue;
                         }
 #endif
-                        mbar_arrive_expect_tx(bar_full(s), (uint32_t)P.stage_tx_bytes);
-                        tma_load_2d(dst, &tm_p, bar_full(s), (kb + j) * Cfg::BK, sg.p0);
+                        if (n_stage + j >= pre_stage) {
+                            mbar_arrive_expect_tx(bar_full(s), (uint32_t)P.stage_tx_bytes);
+                            tma_load_2d(dst, &tm_p, bar_full(s), (kb + j) * Cfg::BK, sg.p0);
+                        }
                         tma_load_2d(dst + Cfg::P_BYTES, &tm_q, bar_full(s), (kb + j) * Cfg::BK, sg.q0);
                     }
                 }

@@ -262,7 +262,8 @@ struct Dest {
 };
 
 static int gemm_impl(const void* a, const void* sfa, const void* b, const void* sfb, const Dest& dst, int64_t M, int64_t N,
-                     int64_t K, int fmt_a, int fmt_b, void* ws, size_t ws_bytes, bool own_ws, void* stream) {
+                     int64_t K, int fmt_a, int fmt_b, void* ws, size_t ws_bytes, bool own_ws, void* stream,
+                     unsigned flags = 0) {
     void* c = dst.c[0];
     if (M < 0 || N < 0 || K < 0) return fail(MXFP6_ERR_BAD_ARG, "negative dimension (M=%lld N=%lld K=%lld)", (long long)M, (long long)N, (long long)K);
     if (K % 128 != 0) return fail(MXFP6_ERR_BAD_ARG, "K=%lld must be a multiple of 128", (long long)K);
@@ -357,6 +358,9 @@ static int gemm_impl(const void* a, const void* sfa, const void* b, const void* 
 #else
     P.dbg_times = nullptr;
 #endif
+    // B is the P operand of the swapped (skinny-M) form; with programmatic dependent launch its first stages may be
+    // requested while the preceding kernel is still draining
+    P.early_p = (pl.swap && (flags & MXFP6_FLAG_B_STATIC) && env_int("MXFP6_PDL", 1)) ? 1 : 0;
     P.group_p = env_int("MXFP6_GROUP_P", 16);   // 16 pair-tiles (4096 rows of A) share each tile of B
     if (P.group_p < 1) P.group_p = 1;
 
@@ -541,6 +545,12 @@ extern "C" size_t mxfp6_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K) {
 extern "C" int mxfp6_gemm_ws(const void* a, const void* sfa, const void* b, const void* sfb, void* c, int64_t M, int64_t N,
                              int64_t K, int fmt_a, int fmt_b, void* workspace, size_t workspace_bytes, void* stream) {
     return gemm_impl(a, sfa, b, sfb, Dest{{c}, 1, N}, M, N, K, fmt_a, fmt_b, workspace, workspace_bytes, false, stream);
+}
+
+extern "C" int mxfp6_gemm_ex(const void* a, const void* sfa, const void* b, const void* sfb, void* c, int64_t M, int64_t N,
+                             int64_t K, int fmt_a, int fmt_b, unsigned flags, void* stream) {
+    if (flags & ~(unsigned)MXFP6_FLAG_B_STATIC) return fail(MXFP6_ERR_BAD_ARG, "unknown flag bits 0x%x", flags);
+    return gemm_impl(a, sfa, b, sfb, Dest{{c}, 1, N}, M, N, K, fmt_a, fmt_b, nullptr, 0, true, stream, flags);
 }
 
 extern "C" int mxfp6_gemm_multi(const void* a, const void* sfa, const void* b, const void* sfb, void* const* c_dst,

@@ -42,13 +42,14 @@ def _stream_ptr() -> int:
     return torch.cuda.current_stream().cuda_stream
 
 
-def dispatch_micro(A, B, C, scale_A, scale_B, fmt: int = E2M3, fmt_b: int | None = None) -> None:
+def dispatch_micro(A, B, C, scale_A, scale_B, fmt: int = E2M3, fmt_b: int | None = None, b_static: bool = False) -> None:
     """C[M,N] (bf16, in place) = A[M,K] @ B[N,K]^T.
 
     A [M,3K/4] u8 and B [N,3K/4] u8 are packed fp6, or [rows,K] u8 for the fp8 formats (format `fmt`; `fmt_b` if
     B differs),
     scale_A [M,K/32] u8 and scale_B [N,K/32] u8 are E8M0 bytes.  M is taken from A, N from C,
-    K from A, as the reference does (256_256_64_32_with16x32.cpp:52-54)."""
+    K from A, as the reference does (256_256_64_32_with16x32.cpp:52-54).  b_static=True promises that B and
+    scale_B are not written by the work queued just before this call (see MXFP6_FLAG_B_STATIC)."""
     _accept(A, "A", torch.uint8)
     _accept(B, "B", torch.uint8)
     _accept(C, "C", torch.bfloat16)
@@ -68,8 +69,8 @@ def dispatch_micro(A, B, C, scale_A, scale_B, fmt: int = E2M3, fmt_b: int | None
     if len({t.device for t in (A, B, C, scale_A, scale_B)}) != 1:
         raise RuntimeError("all tensors must be on the same device")
     with torch.cuda.device(A.device):
-        check(lib.mxfp6_gemm(A.data_ptr(), scale_A.data_ptr(), B.data_ptr(), scale_B.data_ptr(), C.data_ptr(),
-                             M, N, K, fmt, fmt if fmt_b is None else fmt_b, _stream_ptr()))
+        check(lib.mxfp6_gemm_ex(A.data_ptr(), scale_A.data_ptr(), B.data_ptr(), scale_B.data_ptr(), C.data_ptr(),
+                                M, N, K, fmt, fb, _lib.FLAG_B_STATIC if b_static else 0, _stream_ptr()))
 
 
 def dispatch_multi(A, B, dests, col_offset: int, scale_A, scale_B, fmt: int = E2M3) -> None:

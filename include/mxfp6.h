@@ -66,6 +66,17 @@ const char* mxfp6_last_error(void);
 int mxfp6_gemm(const void* a, const void* sfa, const void* b, const void* sfb, void* c,
                int64_t M, int64_t N, int64_t K, int fmt_a, int fmt_b, void* stream);
 
+/*
+ * mxfp6_gemm with option flags.  MXFP6_FLAG_B_STATIC promises that B and its scales are not written by the work
+ * queued on the stream directly before this call (weights of a layer): for skinny M, where B is the operand that
+ * is streamed from HBM, the kernel then starts requesting B while the preceding kernel is still finishing
+ * (programmatic dependent launch) and only the reads of A and all writes wait for it.  Without the flag nothing
+ * is read before the preceding kernel has completed.  (No counterpart in the reference.)
+ */
+#define MXFP6_FLAG_B_STATIC 1u
+int mxfp6_gemm_ex(const void* a, const void* sfa, const void* b, const void* sfb, void* c,
+                  int64_t M, int64_t N, int64_t K, int fmt_a, int fmt_b, unsigned flags, void* stream);
+
 /* Scratch bytes mxfp6_gemm_ws needs for this shape on the current device (0 if none). */
 size_t mxfp6_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K);
 

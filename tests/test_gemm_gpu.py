@@ -221,3 +221,21 @@ def test_fp8_operands(fmt, shape, force):
 def test_mixed_fp8_fp6_operands(fa, fb):
     _case("ffn", 256, 512, 1024, fmt=fa, fmt_b=fb, seed=8)
     _case("decode", 16, 1024, 512, fmt=fa, fmt_b=fb, seed=9)
+
+
+@pytest.mark.parametrize("M", [1, 16, 64])
+def test_b_static_flag_back_to_back(M):
+    """MXFP6_FLAG_B_STATIC: weights are requested before the preceding kernel has drained; results of
+    back-to-back calls (each depending on nothing but its own inputs) stay bit-identical to the plain call."""
+    N, K = 3584, 2048
+    pa, sa, pb, sb = quantized_inputs("decode", M, N, K, seed=M)
+    t = [torch.from_numpy(x).cuda() for x in (pa, sa, pb, sb)]
+    want = hk.gemm(t[0], t[1], t[2], t[3])
+    outs = [torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda") for _ in range(6)]
+    for o in outs:                                   # six launches queued without a host sync in between
+        hk.dispatch_micro(t[0], t[2], o, t[1], t[3], R.E2M3, b_static=True)
+    assert hk.device_status() == 0
+    for o in outs:
+        assert torch.equal(o.view(torch.int16), want.view(torch.int16))
+    ref, absdot = oracle_f64(pa, sa, pb, sb, R.E2M3)
+    check(want.float().cpu().numpy(), ref, absdot)
