@@ -19,6 +19,7 @@
 // Every wait on an mbarrier is bounded; on expiry the CTA records a status code and leaves cleanly.
 #pragma once
 #include "ptx.cuh"
+#include "quant.cuh"
 
 namespace mxfp6 {
 
@@ -46,6 +47,10 @@ struct GemmParams {
     __nv_bfloat16* c;          // first element of this GEMM's block inside destination 0 (row stride ldc)
     __nv_bfloat16* c_more[7];  // the same position in further destinations (peer GPUs' copies of C)
     int ndst;                  // number of destinations, 1..8
+    uint8_t* q_out;            // re-quantised output instead of bf16 C: operand bytes [M, 3N/4 or N] ...
+    uint8_t* q_scales;         // ... and E8M0 scales [M, N/32], blocks of 32 along N
+    long long q_ld;            // row stride of q_out in bytes
+    int q_fmt;                 // format code of the re-quantised output, -1 = store bf16 C
     float* ws_partial;         // split-tile partial sums: [tile][slot][BN][128] fp32
     unsigned int* ws_counter;  // per-tile arrival counters (zero between launches)
     int ws_slots;              // partial slots per tile
@@ -553,6 +558,12 @@ mxfp6_gemm_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constan
                         for (int i = 0; i < CW; ++i)
                             if (qc + i < P.c_rows)
                                 P.c[(size_t)(qc + i) * P.ldc + p] = __float2bfloat16_rn(__uint_as_float(v[i]));
+                    }
+                } else if (P.q_fmt >= 0) {
+                    // the result leaves as an MX operand of the next layer: this thread's 32 columns are one block
+                    if constexpr (CW == 32) {
+                        if (p < P.c_rows && qc < P.c_cols)
+                            quant_store32(v, P.q_fmt, P.q_out, (size_t)P.q_ld, P.q_scales, P.c_cols, p, qc);
                     }
                 } else {
                     if (p < P.c_rows)

@@ -340,6 +340,20 @@ mxfp6_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_co
 #ifdef MXFP6_DEBUG_KNOBS
                 if (P.dbg & 8) { ++n_out; continue; }
 #endif
+                if (P.q_fmt >= 0) {
+                    // the result leaves as an MX operand of the next layer: 64 columns = two blocks of 32
+                    const int row = my_p0 + prow;
+                    if (row < P.c_rows) {
+#pragma unroll
+                        for (int hb = 0; hb < 2; ++hb) {
+                            const int col = q0 + piece * 64 + 32 * hb;
+                            if (col < P.c_cols)
+                                quant_store32(v + 32 * hb, P.q_fmt, P.q_out, (size_t)P.q_ld, P.q_scales, P.c_cols, row, col);
+                        }
+                    }
+                    ++n_out;
+                    continue;
+                }
                 // the stores issued two steps ago have finished reading this staging buffer
                 if (etid == 0) bulk_wait_group_read<1>();
                 asm volatile("bar.sync 1, 128;" ::: "memory");

@@ -263,7 +263,7 @@ struct Dest {
 
 static int gemm_impl(const void* a, const void* sfa, const void* b, const void* sfb, const Dest& dst, int64_t M, int64_t N,
                      int64_t K, int fmt_a, int fmt_b, void* ws, size_t ws_bytes, bool own_ws, void* stream,
-                     unsigned flags = 0) {
+                     unsigned flags = 0, void* q_out = nullptr, void* q_scales = nullptr, int q_fmt = -1) {
     void* c = dst.c[0];
     if (M < 0 || N < 0 || K < 0) return fail(MXFP6_ERR_BAD_ARG, "negative dimension (M=%lld N=%lld K=%lld)", (long long)M, (long long)N, (long long)K);
     if (K % 128 != 0) return fail(MXFP6_ERR_BAD_ARG, "K=%lld must be a multiple of 128", (long long)K);
@@ -298,7 +298,7 @@ static int gemm_impl(const void* a, const void* sfa, const void* b, const void* 
     // the pair kernel stores C by TMA: 16-byte aligned destinations and row stride
     bool c_tma_ok = (dst.ldc % 8) == 0;
     for (int i = 0; i < dst.n; ++i) c_tma_ok = c_tma_ok && !((uintptr_t)dst.c[i] & 15);
-    Plan pl = make_plan(M, N, K, d.sm_count, sf_tma_ok && c_tma_ok, dst.n > 1);
+    Plan pl = make_plan(M, N, K, d.sm_count, sf_tma_ok && c_tma_ok, dst.n > 1 || q_fmt >= 0);
 
     if (pl.ws_bytes) {
         if (own_ws) {
@@ -347,6 +347,8 @@ static int gemm_impl(const void* a, const void* sfa, const void* b, const void* 
     P.c = (__nv_bfloat16*)c;
     for (int i = 1; i < dst.n; ++i) P.c_more[i - 1] = (__nv_bfloat16*)dst.c[i];
     P.ndst = dst.n;
+    P.q_out = (uint8_t*)q_out; P.q_scales = (uint8_t*)q_scales; P.q_fmt = q_fmt;
+    P.q_ld = q_fmt < 0 ? 0 : (fmt_is_fp8(q_fmt) ? N : N * 3 / 4);
     P.ws_counter = (unsigned int*)ws;
     P.ws_partial = ws ? (float*)((uint8_t*)ws + pl.ws_counter_bytes) : nullptr;
     P.ws_slots = pl.ws_slots;
@@ -551,6 +553,20 @@ extern "C" int mxfp6_gemm_ex(const void* a, const void* sfa, const void* b, cons
                              int64_t K, int fmt_a, int fmt_b, unsigned flags, void* stream) {
     if (flags & ~(unsigned)MXFP6_FLAG_B_STATIC) return fail(MXFP6_ERR_BAD_ARG, "unknown flag bits 0x%x", flags);
     return gemm_impl(a, sfa, b, sfb, Dest{{c}, 1, N}, M, N, K, fmt_a, fmt_b, nullptr, 0, true, stream, flags);
+}
+
+extern "C" int mxfp6_gemm_requant(const void* a, const void* sfa, const void* b, const void* sfb, void* out, void* out_scales,
+                                  int64_t M, int64_t N, int64_t K, int fmt_a, int fmt_b, int out_fmt, void* stream) {
+    if (!fmt_valid(out_fmt)) return fail(MXFP6_ERR_BAD_ARG, "requant: bad output format %d", out_fmt);
+    if (N % 64 != 0) return fail(MXFP6_ERR_BAD_ARG, "requant: N=%lld must be a multiple of 64", (long long)N);
+    if (M > 0 && N > 0 && (!out || !out_scales)) return fail(MXFP6_ERR_BAD_ARG, "requant: null output");
+    if ((uintptr_t)out & 15) return fail(MXFP6_ERR_BAD_ARG, "requant: output must be 16-byte aligned");
+    if (K == 0 && M > 0 && N > 0) {   // all-zero result: codes 0, scale byte 0
+        CUDA_TRY(cudaMemsetAsync(out, 0, (size_t)M * (fmt_is_fp8(out_fmt) ? N : N * 3 / 4), (cudaStream_t)stream));
+        CUDA_TRY(cudaMemsetAsync(out_scales, 0, (size_t)M * (N / 32), (cudaStream_t)stream));
+        return MXFP6_OK;
+    }
+    return gemm_impl(a, sfa, b, sfb, Dest{{out}, 1, N}, M, N, K, fmt_a, fmt_b, nullptr, 0, true, stream, 0, out, out_scales, out_fmt);
 }
 
 extern "C" int mxfp6_gemm_multi(const void* a, const void* sfa, const void* b, const void* sfb, void* const* c_dst,

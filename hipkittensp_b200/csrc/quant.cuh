@@ -1,0 +1,92 @@
+// Block quantisation of 32 consecutive fp32 values to an MX format inside a kernel (used by the GEMM epilogues
+// that hand their result to the next layer already quantised).  Same rule as the stand-alone quantiser:
+// scale exponent = floor(log2(amax)) - emax_elem, clamp to [0,254], elements RNE + saturate by the hardware cvt.
+#pragma once
+#include <cuda_fp6.h>
+#include <cuda_fp8.h>
+#include <stdint.h>
+
+namespace mxfp6 {
+
+// format codes of the C ABI
+constexpr int kE2M3 = 0, kE3M2 = 1, kE4M3 = 2, kE5M2 = 3;
+
+__device__ __forceinline__ int quant_emax(int fmt) { return fmt == kE2M3 ? 2 : fmt == kE3M2 ? 4 : fmt == kE4M3 ? 8 : 15; }
+
+// E8M0 byte of a block whose largest magnitude is amax
+__device__ __forceinline__ int quant_scale_byte(float amax, int fmt) {
+    const uint32_t u = __float_as_uint(amax);
+    int fl = (int)((u >> 23) & 0xff) - 127;
+    if (((u >> 23) & 0xff) == 0) fl = 31 - __clz(u & 0x7fffff) - 149;     // fp32 subnormal
+    int sb = fl - quant_emax(fmt) + 127;
+    sb = sb < 0 ? 0 : sb > 254 ? 254 : sb;
+    if (!(amax > 0.f)) sb = 0;
+    if (isinf(amax)) sb = 254;
+    return sb;
+}
+
+// v[0..31] (fp32) -> out[0..5] (fp6: 24 bytes) or out[0..7] (fp8: 32 bytes); returns the scale byte
+template <int FMT>
+__device__ __forceinline__ int quant_block32(const float* v, uint32_t* out) {
+    float amax = 0.f;
+#pragma unroll
+    for (int i = 0; i < 32; ++i) amax = fmaxf(amax, fabsf(v[i]));
+    const int sb = quant_scale_byte(amax, FMT);
+    const int e = sb - 127;
+    const int h = (-e) / 2;          // 2^-e applied in two exact steps that stay inside fp32
+    const float f1 = __uint_as_float((uint32_t)(h + 127) << 23), f2 = __uint_as_float((uint32_t)(-e - h + 127) << 23);
+    if constexpr (FMT == kE4M3 || FMT == kE5M2) {
+#pragma unroll
+        for (int g = 0; g < 8; ++g) {
+            uint32_t w = 0;
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+                w |= (uint32_t)__nv_cvt_float_to_fp8(v[4 * g + i] * f1 * f2, __NV_SATFINITE, FMT == kE4M3 ? __NV_E4M3 : __NV_E5M2) << (8 * i);
+            out[g] = w;
+        }
+    } else {
+        uint32_t w24[8];
+#pragma unroll
+        for (int g = 0; g < 8; ++g) {
+            uint32_t w = 0;
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+                w |= ((uint32_t)__nv_cvt_float_to_fp6(v[4 * g + i] * f1 * f2, FMT == kE2M3 ? __NV_E2M3 : __NV_E3M2, cudaRoundNearest) & 63u) << (6 * i);
+            w24[g] = w;
+        }
+#pragma unroll
+        for (int h4 = 0; h4 < 2; ++h4) {      // 4 x 24 bits -> 3 words, twice
+            const uint32_t* q = w24 + 4 * h4;
+            out[3 * h4 + 0] = q[0] | (q[1] << 24);
+            out[3 * h4 + 1] = (q[1] >> 8) | (q[2] << 16);
+            out[3 * h4 + 2] = (q[2] >> 16) | (q[3] << 8);
+        }
+    }
+    return sb;
+}
+
+// Quantise 32 consecutive columns [col, col+32) of row `row` and store codes + scale.
+//   q_out: operand bytes, row stride q_ld bytes; q_scales: [rows, n_cols/32]
+__device__ __forceinline__ void quant_store32(const uint32_t* vbits, int fmt, uint8_t* q_out, size_t q_ld, uint8_t* q_scales,
+                                              int n_cols, int row, int col) {
+    float v[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(vbits[i]);
+    uint32_t w[8];
+    int sb;
+    const bool fp8 = fmt == kE4M3 || fmt == kE5M2;
+    if (fmt == kE2M3) sb = quant_block32<kE2M3>(v, w);
+    else if (fmt == kE3M2) sb = quant_block32<kE3M2>(v, w);
+    else if (fmt == kE4M3) sb = quant_block32<kE4M3>(v, w);
+    else sb = quant_block32<kE5M2>(v, w);
+    uint8_t* dst = q_out + (size_t)row * q_ld + (fp8 ? col : col / 4 * 3);
+    // 24 (fp6) or 32 (fp8) bytes; 8-byte aligned in both cases when q_ld % 8 == 0 and col % 32 == 0
+    uint2* d2 = reinterpret_cast<uint2*>(dst);
+    d2[0] = make_uint2(w[0], w[1]);
+    d2[1] = make_uint2(w[2], w[3]);
+    d2[2] = make_uint2(w[4], w[5]);
+    if (fp8) d2[3] = make_uint2(w[6], w[7]);
+    q_scales[(size_t)row * (n_cols / 32) + col / 32] = (uint8_t)sb;
+}
+
+}  // namespace mxfp6

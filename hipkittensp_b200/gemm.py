@@ -100,6 +100,27 @@ def dispatch_multi(A, B, dests, col_offset: int, scale_A, scale_B, fmt: int = E2
                                    ldc, M, N, K, fmt, fmt, _stream_ptr()))
 
 
+def gemm_requant(A, scale_A, B, scale_B, fmt: int = E2M3, fmt_b: int | None = None, out_fmt: int = E2M3):
+    """C = A @ B^T delivered as an MX operand for the next layer: (operand bytes [M, 3N/4 | N], scales [M, N/32]),
+    quantised in the GEMM epilogue from the fp32 accumulators (blocks of 32 along N)."""
+    _accept(A, "A", torch.uint8)
+    _accept(B, "B", torch.uint8)
+    _accept(scale_A, "scale_A", torch.uint8)
+    _accept(scale_B, "scale_B", torch.uint8)
+    fb = fmt if fmt_b is None else fmt_b
+    M, N, K = A.shape[0], B.shape[0], _k_of(A, fmt, "A")
+    if _k_of(B, fb, "B") != K:
+        raise RuntimeError("A and B disagree on K")
+    if N % 64:
+        raise RuntimeError("N must be a multiple of 64")
+    out = torch.empty((M, N if out_fmt in (E4M3, E5M2) else N * 3 // 4), dtype=torch.uint8, device=A.device)
+    scales = torch.empty((M, N // 32), dtype=torch.uint8, device=A.device)
+    with torch.cuda.device(A.device):
+        check(lib.mxfp6_gemm_requant(A.data_ptr(), scale_A.data_ptr(), B.data_ptr(), scale_B.data_ptr(), out.data_ptr(),
+                                     scales.data_ptr(), M, N, K, fmt, fb, out_fmt, _stream_ptr()))
+    return out, scales
+
+
 def gemm(A, scale_A, B, scale_B, fmt: int = E2M3, fmt_b: int | None = None, out=None):
     """Allocating convenience wrapper around dispatch_micro; returns C."""
     M, N = A.shape[0], B.shape[0]

@@ -77,6 +77,17 @@ int mxfp6_gemm(const void* a, const void* sfa, const void* b, const void* sfb, v
 int mxfp6_gemm_ex(const void* a, const void* sfa, const void* b, const void* sfb, void* c,
                   int64_t M, int64_t N, int64_t K, int fmt_a, int fmt_b, unsigned flags, void* stream);
 
+/*
+ * The GEMM with its result handed to the next layer already quantised: instead of bf16 C the epilogue writes
+ * C as an MX operand, blocks of 32 along N (the next layer's K): out [M, 3N/4] (fp6) or [M, N] (fp8) bytes and
+ * out_scales [M, N/32] E8M0 bytes, quantised from the fp32 accumulators with the rule of mxfp6_quantize
+ * (so a 2-byte round trip of C through HBM and a quantiser launch disappear).  N % 64 == 0, out 16-byte
+ * aligned.  (No counterpart in the reference; the nearest is the epilogue scaling of
+ * kernels/torch_scaled/scaled_matmul.cu:253-265.)
+ */
+int mxfp6_gemm_requant(const void* a, const void* sfa, const void* b, const void* sfb, void* out, void* out_scales,
+                       int64_t M, int64_t N, int64_t K, int fmt_a, int fmt_b, int out_fmt, void* stream);
+
 /* Scratch bytes mxfp6_gemm_ws needs for this shape on the current device (0 if none). */
 size_t mxfp6_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K);
 

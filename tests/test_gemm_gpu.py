@@ -239,3 +239,59 @@ def test_b_static_flag_back_to_back(M):
         assert torch.equal(o.view(torch.int16), want.view(torch.int16))
     ref, absdot = oracle_f64(pa, sa, pb, sb, R.E2M3)
     check(want.float().cpu().numpy(), ref, absdot)
+
+
+# ------------------------------------------------------------------------------- re-quantising epilogue
+def _exact_inputs(M, N, K, seed):
+    """Operands whose products and partial sums are small integers times a power of two: every accumulation order
+    gives the same fp32 result, so the fused quantiser must agree with the oracle bit for bit."""
+    rng = np.random.default_rng(seed)
+    A = rng.integers(-3, 4, size=(M, K)).astype(np.float32)
+    B = rng.integers(-3, 4, size=(N, K)).astype(np.float32)
+    A *= 2.0 ** rng.integers(-2, 3, size=(M, 1))
+    B *= 2.0 ** rng.integers(-2, 3, size=(N, 1))
+    return A, B
+
+
+@pytest.mark.parametrize("out_fmt", [R.E2M3, R.E3M2, R.E4M3, R.E5M2])
+@pytest.mark.parametrize("shape,force", [((256, 512, 512), None), ((512, 768, 1024), "256,0,0,1"),
+                                         ((130, 192, 256), None), ((16, 256, 512), None)])
+def test_requant_epilogue_bit_exact_on_exact_sums(out_fmt, shape, force):
+    M, N, K = shape
+    if force:
+        os.environ["MXFP6_FORCE_CFG"] = force
+    A, B = _exact_inputs(M, N, K, seed=M + out_fmt)
+    pa, sa = R.quantize(A, R.E2M3)
+    pb, sb = R.quantize(B, R.E2M3)
+    c32 = (R.dequantize(pa, sa, R.E2M3).astype(np.float64) @ R.dequantize(pb, sb, R.E2M3).astype(np.float64).T).astype(np.float32)
+    want_p, want_s = R.quantize(c32, out_fmt)
+    t = [torch.from_numpy(x).cuda() for x in (pa, sa, pb, sb)]
+    got_p, got_s = hk.gemm_requant(t[0], t[1], t[2], t[3], R.E2M3, out_fmt=out_fmt)
+    assert hk.device_status() == 0
+    np.testing.assert_array_equal(got_s.cpu().numpy(), want_s)
+    np.testing.assert_array_equal(got_p.cpu().numpy(), want_p)
+
+
+def test_requant_epilogue_random_inputs_within_one_step():
+    """On general inputs the fp32 sums differ in the last bits from the oracle's, so a value may land on the
+    neighbouring code; after dequantisation the two results agree to within one quantisation step."""
+    M, N, K = 512, 1024, 2048
+    pa, sa, pb, sb = quantized_inputs("lognormal", M, N, K, seed=21)
+    ref, _ = oracle_f64(pa, sa, pb, sb, R.E2M3)
+    want_p, want_s = R.quantize(ref.astype(np.float32), R.E4M3)
+    t = [torch.from_numpy(x).cuda() for x in (pa, sa, pb, sb)]
+    got_p, got_s = hk.gemm_requant(t[0], t[1], t[2], t[3], R.E2M3, out_fmt=R.E4M3)
+    assert hk.device_status() == 0
+    got = R.dequantize(got_p.cpu().numpy(), got_s.cpu().numpy(), R.E4M3)
+    want = R.dequantize(want_p, want_s, R.E4M3)
+    step = 2.0 ** (want_s.astype(np.int32) - 127 + 8 - 3).repeat(32, axis=1)     # coarsest e4m3 spacing in the block
+    assert (np.abs(got - want) <= step).all()
+    assert (got_s.cpu().numpy() == want_s).mean() > 0.999
+    # and it feeds the next GEMM directly: layer 2 = requantised activations [M, N] x W2 [256, N]
+    W2, _ = R.make_inputs("normal", 256, 8, N, seed=5)
+    pw, sw = R.quantize(W2, R.E4M3)
+    C2 = hk.gemm(got_p, got_s, torch.from_numpy(pw).cuda(), torch.from_numpy(sw).cuda(), R.E4M3, fmt_b=R.E4M3)
+    assert hk.device_status() == 0
+    ref2 = got.astype(np.float64) @ R.dequantize(pw, sw, R.E4M3).astype(np.float64).T
+    absdot2 = np.abs(got).astype(np.float64) @ np.abs(R.dequantize(pw, sw, R.E4M3)).astype(np.float64).T
+    check(C2.float().cpu().numpy(), ref2, absdot2)
