@@ -13,6 +13,25 @@ constexpr int kE2M3 = 0, kE3M2 = 1, kE4M3 = 2, kE5M2 = 3;
 
 __device__ __forceinline__ int quant_emax(int fmt) { return fmt == kE2M3 ? 2 : fmt == kE3M2 ? 4 : fmt == kE4M3 ? 8 : 15; }
 
+// Hardware conversion of two fp32 values at once (round to nearest even, saturate to the largest finite value):
+// returns code(x0) | code(x1) << 8, fp6 codes in the low 6 bits of their byte.
+template <int FMT>
+__device__ __forceinline__ uint32_t cvt_pair(float x0, float x1) {
+    uint16_t r;
+    if constexpr (FMT == kE2M3) asm("cvt.rn.satfinite.e2m3x2.f32 %0, %1, %2;" : "=h"(r) : "f"(x1), "f"(x0));
+    else if constexpr (FMT == kE3M2) asm("cvt.rn.satfinite.e3m2x2.f32 %0, %1, %2;" : "=h"(r) : "f"(x1), "f"(x0));
+    else if constexpr (FMT == kE4M3) asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(r) : "f"(x1), "f"(x0));
+    else asm("cvt.rn.satfinite.e5m2x2.f32 %0, %1, %2;" : "=h"(r) : "f"(x1), "f"(x0));
+    return r;
+}
+// four values -> 4 codes: fp8 one per byte (32 bits), fp6 6 bits each (24 bits)
+template <int FMT>
+__device__ __forceinline__ uint32_t cvt_quad(float x0, float x1, float x2, float x3) {
+    const uint32_t lo = cvt_pair<FMT>(x0, x1), hi = cvt_pair<FMT>(x2, x3);
+    if constexpr (FMT == kE4M3 || FMT == kE5M2) return lo | (hi << 16);
+    else return (lo & 63u) | ((lo >> 8) << 6) | ((hi & 63u) << 12) | ((hi >> 8) << 18);
+}
+
 // E8M0 byte of a block whose largest magnitude is amax
 __device__ __forceinline__ int quant_scale_byte(float amax, int fmt) {
     const uint32_t u = __float_as_uint(amax);
@@ -37,23 +56,13 @@ __device__ __forceinline__ int quant_block32(const float* v, uint32_t* out) {
     const float f1 = __uint_as_float((uint32_t)(h + 127) << 23), f2 = __uint_as_float((uint32_t)(-e - h + 127) << 23);
     if constexpr (FMT == kE4M3 || FMT == kE5M2) {
 #pragma unroll
-        for (int g = 0; g < 8; ++g) {
-            uint32_t w = 0;
-#pragma unroll
-            for (int i = 0; i < 4; ++i)
-                w |= (uint32_t)__nv_cvt_float_to_fp8(v[4 * g + i] * f1 * f2, __NV_SATFINITE, FMT == kE4M3 ? __NV_E4M3 : __NV_E5M2) << (8 * i);
-            out[g] = w;
-        }
+        for (int g = 0; g < 8; ++g)
+            out[g] = cvt_quad<FMT>(v[4 * g] * f1 * f2, v[4 * g + 1] * f1 * f2, v[4 * g + 2] * f1 * f2, v[4 * g + 3] * f1 * f2);
     } else {
         uint32_t w24[8];
 #pragma unroll
-        for (int g = 0; g < 8; ++g) {
-            uint32_t w = 0;
-#pragma unroll
-            for (int i = 0; i < 4; ++i)
-                w |= ((uint32_t)__nv_cvt_float_to_fp6(v[4 * g + i] * f1 * f2, FMT == kE2M3 ? __NV_E2M3 : __NV_E3M2, cudaRoundNearest) & 63u) << (6 * i);
-            w24[g] = w;
-        }
+        for (int g = 0; g < 8; ++g)
+            w24[g] = cvt_quad<FMT>(v[4 * g] * f1 * f2, v[4 * g + 1] * f1 * f2, v[4 * g + 2] * f1 * f2, v[4 * g + 3] * f1 * f2);
 #pragma unroll
         for (int h4 = 0; h4 < 2; ++h4) {      // 4 x 24 bits -> 3 words, twice
             const uint32_t* q = w24 + 4 * h4;
