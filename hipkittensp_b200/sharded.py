@@ -105,3 +105,42 @@ class ColumnParallelGemm:
             return self.c_full
         self.local_gemm(A, scale_A, B_shard, scale_B_shard)
         return self.gather()
+
+
+class RowParallelGemm:
+    """The reference's own multi-GPU split (distributed-kernels/bf16_gemm/example.py:70,112): A is sharded by rows,
+    B is replicated, rank r owns rows [r*M/g, (r+1)*M/g) of C and there is no exchange.  With `gather=True` the row
+    blocks are additionally pushed to every peer by the GEMM epilogue (symmetric memory), so that each rank ends
+    with all of C; row blocks are contiguous, so no re-layout is involved either way."""
+
+    def __init__(self, M: int, N: int, K: int, group=None, device=None, fmt: int = E2M3, gather: bool = False):
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.M, self.N, self.K, self.fmt = M, N, K, fmt
+        self.lo, self.hi = shard_bounds(M, self.world, self.rank)
+        self.push = gather and self.world > 1
+        self.symm = None
+        if self.push:
+            import torch.distributed._symmetric_memory as symm
+
+            self.c_full = symm.empty((M, N), dtype=torch.bfloat16, device=device)
+            self.symm = symm.rendezvous(self.c_full, dist.group.WORLD if group is None else group)
+            order = [(self.rank + i) % self.world for i in range(self.world)]
+            bufs = [self.c_full] + [self.symm.get_buffer(r, (M, N), torch.bfloat16) for r in order[1:]]
+            self.dests = [b[self.lo:self.hi] for b in bufs]
+            self.c_rows = self.dests[0]
+        else:
+            self.c_rows = torch.empty((self.hi - self.lo, N), dtype=torch.bfloat16, device=device)
+            self.c_full = None
+
+    def __call__(self, A_rows, scale_A_rows, B, scale_B) -> torch.Tensor:
+        """A_rows: this rank's [M/g, .] block of A.  Returns the rank's rows of C, or all of C with gather=True."""
+        if self.push:
+            from .gemm import dispatch_multi
+
+            dispatch_multi(A_rows, B, self.dests, 0, scale_A_rows, scale_B, self.fmt)
+            self.symm.barrier()
+            return self.c_full
+        dispatch_micro(A_rows, B, self.c_rows, scale_A_rows, scale_B, self.fmt)
+        return self.c_rows

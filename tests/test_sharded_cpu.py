@@ -77,3 +77,9 @@ def test_two_rank_gloo_gather_equals_single():
         ret = mgr.dict()
         mp.spawn(_worker, args=(world, _free_port(), 64, 256, 256, ret), nprocs=world, join=True)
         assert dict(ret) == {0: True, 1: True}
+
+
+def test_row_parallel_single_process_bounds():
+    # without a process group the wrapper owns all rows; only the partition arithmetic is exercised here
+    rp = sharded.RowParallelGemm(64, 32, 128, device="cpu")
+    assert (rp.lo, rp.hi) == (0, 64) and tuple(rp.c_rows.shape) == (64, 32) and rp.c_full is None

@@ -31,6 +31,13 @@ for mode in ("nccl", "fused"):
         C = op(pa, sa, shard_rows(pb, world, rank), shard_rows(sb, world, rank))
         torch.cuda.synchronize()
         ok = ok and bool(torch.equal(C.view(torch.int16), want.view(torch.int16)))
+from hipkittensp_b200.sharded import RowParallelGemm
+for g in (False, True):
+    rp = RowParallelGemm(M, N, K, device=dev, gather=g)
+    out = rp(shard_rows(pa, world, rank), shard_rows(sa, world, rank), pb, sb)
+    torch.cuda.synchronize()
+    exp = want if g else want[rp.lo:rp.hi]
+    ok = ok and bool(torch.equal(out.view(torch.int16), exp.contiguous().view(torch.int16)))
 assert hk.device_status() == 0
 flag = torch.tensor([1 if ok else 0], device=dev)
 dist.all_reduce(flag, op=dist.ReduceOp.MIN)
