@@ -58,8 +58,6 @@ struct GemmParams {
     unsigned long long wait_cycles;  // budget of one wait in clock cycles
     int group_p;               // pair kernel: P-tiles per rasterisation group
     int early_p;               // swapped form: P (the weights) may be read before the preceding kernel has finished
-    unsigned long long* dbg_times;   // debug builds: per-CTA time stamps
-    int dbg;                   // experiment switches, honoured only by builds with MXFP6_DEBUG_KNOBS
 };
 
 template <int BN_, bool SWAP_, bool STREAMK_>
@@ -198,18 +196,6 @@ __device__ __forceinline__ bool wait_bar_warp(uint32_t bar, uint32_t parity, vol
     return __all_sync(0xffffffffu, wait_bar(bar, parity, abort_flag, P, code));
 }
 
-#ifdef MXFP6_DEBUG_KNOBS
-__device__ __forceinline__ void dbg_stamp(const GemmParams& P, int slot) {
-    if (P.dbg_times) {
-        unsigned long long t;
-        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-        P.dbg_times[blockIdx.x * 8 + slot] = t;
-    }
-}
-#define MXFP6_STAMP(slot) dbg_stamp(P, slot)
-#else
-#define MXFP6_STAMP(slot)
-#endif
 
 template <class Cfg>
 __global__ void __launch_bounds__(Cfg::THREADS, 1)
@@ -242,7 +228,6 @@ mxfp6_gemm_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constan
     volatile int* ticket_slot = reinterpret_cast<volatile int*>(smem_gen + misc_off + 8);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    if (threadIdx.x == 0) MXFP6_STAMP(0);
     pdl_launch_dependents();     // the next kernel may set itself up on SMs this grid has left
 
     if (threadIdx.x == 0) {
@@ -271,7 +256,6 @@ mxfp6_gemm_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constan
     // ahead and requests the first stages of P (weights that the preceding kernel does not write) before it waits.
     const bool early = Cfg::SWAP && P.early_p != 0;
     if (!(early && warp == 0)) pdl_wait();
-    if (threadIdx.x == 0) MXFP6_STAMP(1);
 
     // =========================================================== warp 0: TMA producer
     if (warp == 0) {
@@ -340,19 +324,6 @@ mxfp6_gemm_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constan
                     for (int j = 0; j < nb; ++j) {
                         const int s = (n_stage + j) % Cfg::STAGES;
                         const uint32_t dst = stage_base + s * Cfg::STAGE_BYTES;
-#ifdef MXFP6_DEBUG_KNOBS
-                        if ((P.dbg & 4) && n_stage + j >= (uint32_t)Cfg::STAGES) continue;
-                        if (P.dbg & 128) {        // P loads only
-                            mbar_arrive_expect_tx(bar_full(s), 128u * 96u);
-                            tma_load_2d(dst, &tm_p, bar_full(s), (kb + j) * Cfg::BK, sg.p0);
-                            continue;
-                        }
-                        if (P.dbg & 256) {        // Q loads only
-                            mbar_arrive_expect_tx(bar_full(s), (uint32_t)P.stage_tx_bytes - 128u * 96u);
-                            tma_load_2d(dst + Cfg::P_BYTES, &tm_q, bar_full(s), (kb + j) * Cfg::BK, sg.q0);
-                            continue;
-                        }
-#endif
                         if (n_stage + j >= pre_stage) {
                             mbar_arrive_expect_tx(bar_full(s), (uint32_t)P.stage_tx_bytes);
                             tma_load_2d(dst, &tm_p, bar_full(s), (kb + j) * Cfg::BK, sg.p0);
@@ -388,22 +359,13 @@ mxfp6_gemm_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constan
                 // the scale atoms arrive per group of 4 K-blocks (one raw slab)
                 if (kb == sg.k0 || (kb & 3) == 0)
                     ok = wait_bar_warp(bar_atom_full(g), (n_grp / Cfg::ATOM_GROUPS) & 1, abort_flag, P, kStatusTimeoutMma);
-#ifdef MXFP6_DEBUG_KNOBS
-                if (!((P.dbg & 4) && n_kb >= (uint32_t)Cfg::STAGES))
-#endif
                 ok = ok && wait_bar_warp(bar_full(s), (n_kb / Cfg::STAGES) & 1, abort_flag, P, kStatusTimeoutMma);
                 if (!ok) break;
-#ifdef MXFP6_DEBUG_KNOBS
-                if (n_kb == 0 && lane == 0) MXFP6_STAMP(2);
-#endif
                 const bool group_done = (kb & 3) == 3 || kb == sg.k1 - 1;
                 if (elect_one_sync()) {
                     const uint32_t sfa = tmem_base + Cfg::SF_COL + (n_kb & 1) * 16;
                     const uint32_t sfb = sfa + 4;
                     const uint32_t atom = atom_base + g * Cfg::GROUP_BYTES + (kb & 3) * Cfg::ATOM_BYTES;
-#ifdef MXFP6_DEBUG_KNOBS
-                    if (!(P.dbg & 1) || kb == sg.k0)
-#endif
                     {
                     tc_cp_32x128b_warpx4(sfa, smem_desc_sf(atom));
 #pragma unroll
@@ -414,16 +376,9 @@ mxfp6_gemm_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constan
                     const uint64_t bdesc = smem_desc_sw128(sp + Cfg::P_BYTES);
 #pragma unroll
                     for (uint32_t k = 0; k < 4; ++k) {
-#ifdef MXFP6_DEBUG_KNOBS
-                        if ((P.dbg & 16) && k > 0) break;
-                        if (P.dbg & 512) break;
-#endif
                         mma_mxf8f6f4(acc, adesc + 2 * k, bdesc + 2 * k, idesc_with_sf(P.idesc, k),
                                      sfa | (k << 30), sfb | (k << 30), (kb > sg.k0 || k > 0) ? 1u : 0u);
                     }
-#ifdef MXFP6_DEBUG_KNOBS
-                    if (!(P.dbg & 1024))
-#endif
                     tc_commit(bar_empty(s));
                     if (group_done) tc_commit(bar_atom_empty(g));
                 }
@@ -434,7 +389,6 @@ mxfp6_gemm_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constan
             if (!ok) break;
             if (elect_one_sync()) tc_commit(bar_acc_full(b));
             __syncwarp();
-            if (lane == 0) MXFP6_STAMP(3);
             ++n_seg;
         }
     }
@@ -640,7 +594,6 @@ mxfp6_gemm_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constan
                     if (etid == 0) P.ws_counter[sg.tile] = 0u;
                 }
             }
-            if (etid == 0) MXFP6_STAMP(4);
             ++n_seg;
         }
     }
@@ -655,7 +608,6 @@ mxfp6_gemm_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constan
     __syncthreads();
     tc_fence_after();
     if (warp == 1) tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
-    if (threadIdx.x == 32) MXFP6_STAMP(5);
 }
 
 }  // namespace mxfp6

@@ -158,9 +158,6 @@ mxfp6_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_co
             pair_coords(P, tile, p0, q0);
             const int my_p = p0 + 128 * (int)rank, my_q = q0 + 128 * (int)rank;
             for (int kb = 0; kb < P.kblocks && ok; ++kb) {
-#ifdef MXFP6_DEBUG_KNOBS
-                if ((kb & 3) == 0 && (P.dbg & 64) && n_raw >= (uint32_t)Cfg::ATOM_GROUPS) { ++n_raw; } else
-#endif
                 if ((kb & 3) == 0) {
                     const int r = n_raw % Cfg::RAW_SLOTS;
                     ok = wait_bar_warp(bar_raw_empty(r), ((n_raw / Cfg::RAW_SLOTS) & 1) ^ 1, abort_flag, P, kStatusTimeoutProducer);
@@ -174,9 +171,6 @@ mxfp6_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_co
                     ++n_raw;
                 }
                 const int s = n_stage % Cfg::STAGES;
-#ifdef MXFP6_DEBUG_KNOBS
-                if ((P.dbg & 4) && n_stage >= (uint32_t)Cfg::STAGES) { ++n_stage; continue; }
-#endif
                 ok = wait_bar_warp(bar_empty(s), ((n_stage / Cfg::STAGES) & 1) ^ 1, abort_flag, P, kStatusTimeoutProducer);
                 if (!ok) break;
                 if (elect_one_sync()) {
@@ -207,27 +201,15 @@ mxfp6_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_co
                 for (int kb = 0; kb < P.kblocks; ++kb) {
                     const int s = n_kb % Cfg::STAGES;
                     const int g = n_grp % Cfg::ATOM_GROUPS;
-#ifdef MXFP6_DEBUG_KNOBS
-                    if ((kb & 3) == 0 && !((P.dbg & 64) && n_grp >= (uint32_t)Cfg::ATOM_GROUPS))
-#else
                     if ((kb & 3) == 0)
-#endif
                         ok = wait_bar_cluster_warp(bar_atom_full(g), (n_grp / Cfg::ATOM_GROUPS) & 1, abort_flag, P, kStatusTimeoutMma);
-#ifdef MXFP6_DEBUG_KNOBS
-                    const bool skip_full = (P.dbg & 4) && n_kb >= (uint32_t)Cfg::STAGES;
-                    ok = ok && (skip_full || wait_bar_warp(bar_full(s), (n_kb / Cfg::STAGES) & 1, abort_flag, P, kStatusTimeoutMma));
-#else
                     ok = ok && wait_bar_warp(bar_full(s), (n_kb / Cfg::STAGES) & 1, abort_flag, P, kStatusTimeoutMma);
-#endif
                     if (!ok) break;
                     const bool group_done = (kb & 3) == 3 || kb == P.kblocks - 1;
                     if (elect_one_sync()) {
                         const uint32_t sfa = tmem_base + Cfg::SF_COL + (n_kb & 1) * 16;
                         const uint32_t sfb = sfa + 4;
                         const uint32_t atom = atom_base + g * Cfg::GROUP_BYTES + (kb & 3) * Cfg::ATOM_BYTES;
-#ifdef MXFP6_DEBUG_KNOBS
-                        if (!(P.dbg & 1) || kb == 0)
-#endif
                         {
                         tc_cp_32x128b_warpx4_pair(sfa, smem_desc_sf(atom));
                         tc_cp_32x128b_warpx4_pair(sfb, smem_desc_sf(atom + 512));
@@ -238,19 +220,11 @@ mxfp6_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_co
                         const uint64_t bdesc = smem_desc_sw128(sp + Cfg::P_BYTES);
 #pragma unroll
                         for (uint32_t k = 0; k < 4; ++k) {
-#ifdef MXFP6_DEBUG_KNOBS
-                            if ((P.dbg & 16) && k > 0) break;
-#endif
                             mma_mxf8f6f4_pair(acc, adesc + 2 * k, bdesc + 2 * k, idesc_with_sf(P.idesc, k),
                                               sfa | (k << 30), sfb | (k << 30), (kb > 0 || k > 0) ? 1u : 0u);
                         }
-#ifdef MXFP6_DEBUG_KNOBS
-                        if (!((P.dbg & 32) && (P.dbg & 4) && n_kb >= (uint32_t)Cfg::STAGES)) tc_commit_pair(bar_empty(s), 3);
-                        if (group_done && !(P.dbg & 64)) tc_commit_pair(bar_atom_empty(g), 3);
-#else
                         tc_commit_pair(bar_empty(s), 3);
                         if (group_done) tc_commit_pair(bar_atom_empty(g), 3);
-#endif
                     }
                     __syncwarp();
                     ++n_kb;
@@ -273,9 +247,6 @@ mxfp6_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_co
         for (int tile = cluster_id; tile < num_tiles && ok; tile += n_clusters) {
             for (int kb = 0; kb < P.kblocks && ok; kb += 4, ++n_grp) {
                 if ((int)(n_grp & 1) != warp - 2) continue;
-#ifdef MXFP6_DEBUG_KNOBS
-                if ((P.dbg & 64) && n_grp >= (uint32_t)Cfg::ATOM_GROUPS) continue;
-#endif
                 uint32_t rp[4][4], rq[8][4];
                 const int r = n_grp % Cfg::RAW_SLOTS;
                 ok = wait_bar_warp(bar_raw_full(r), (n_grp / Cfg::RAW_SLOTS) & 1, abort_flag, P, kStatusTimeoutScale);
@@ -337,9 +308,6 @@ mxfp6_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_co
                 tmem_ld_x32(tacc + piece * 64 + 32, reinterpret_cast<uint32_t(&)[32]>(v[32]));
                 tmem_ld_wait();
                 if (ci == 0) { tc_fence_before(); mbar_arrive_cluster(ovl0); }
-#ifdef MXFP6_DEBUG_KNOBS
-                if (P.dbg & 8) { ++n_out; continue; }
-#endif
                 if (P.q_fmt >= 0) {
                     // the result leaves as an MX operand of the next layer: 64 columns = two blocks of 32
                     const int row = my_p0 + prow;

@@ -354,12 +354,6 @@ static int gemm_impl(const void* a, const void* sfa, const void* b, const void* 
     P.ws_slots = pl.ws_slots;
     P.status = d.status;
     P.wait_cycles = d.wait_cycles;
-    P.dbg = env_int("MXFP6_DBG", 0);
-#ifdef MXFP6_DEBUG_KNOBS
-    P.dbg_times = (unsigned long long*)(uintptr_t)strtoull(getenv("MXFP6_DBG_TIMES") ? getenv("MXFP6_DBG_TIMES") : "0", nullptr, 0);
-#else
-    P.dbg_times = nullptr;
-#endif
     // B is the P operand of the swapped (skinny-M) form; with programmatic dependent launch its first stages may be
     // requested while the preceding kernel is still draining
     P.early_p = (pl.swap && (flags & MXFP6_FLAG_B_STATIC) && env_int("MXFP6_PDL", 1)) ? 1 : 0;
