@@ -364,10 +364,14 @@ def run_reference(args):
     R.gemm_cpu_path(ta[:64], tsa[:64], tb[:512], tsb[:512])      # warm the thread pool
     t0 = time.perf_counter()
     R.gemm_cpu_path(ta[:256], tsa[:256], tb, tsb)
-    probe = time.perf_counter() - t0
+    probe = time.perf_counter() - t0                              # 256 rows of A against all sampled rows of B
     rows = rows_a
     while rows > 256 and probe * rows / 256 > budget:
         rows //= 2
+    # many steps: shrink the B side of the sample too (its dequantisation is the floor of a step)
+    while rows_b > 512 and probe * (rows / 256) * (rows_b / tb.shape[0]) > budget:
+        rows_b //= 2
+    tb, tsb = tb[:rows_b], tsb[:rows_b]
     for _ in range(W):
         R.gemm_cpu_path(ta[:rows], tsa[:rows], tb, tsb)
     t0 = time.perf_counter()
