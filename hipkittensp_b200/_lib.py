@@ -20,7 +20,7 @@ OK, ERR_BAD_ARG, ERR_CUDA, ERR_DEVICE_WAIT, ERR_UNSUPPORTED = 0, 1, 2, 3, 4
 # every symbol include/mxfp6.h declares
 SYMBOLS = ("mxfp6_version", "mxfp6_last_error", "mxfp6_gemm", "mxfp6_gemm_workspace_bytes", "mxfp6_gemm_ws",
            "mxfp6_gemm_noalloc", "mxfp6_gemm_multi", "mxfp6_gemm_ex", "mxfp6_gemm_requant",
-           "mxfp6_quantize", "mxfp6_dequantize", "mxfp6_device_status", "mxfp6_debug_tma_dump")
+           "mxfp6_quantize", "mxfp6_dequantize", "mxfp6_device_status", "mxfp6_debug_tma_dump", "mxfp6_debug_wait_timeout")
 
 
 class Mxfp6Error(RuntimeError):
@@ -63,6 +63,8 @@ def _load() -> ctypes.CDLL:
     lib.mxfp6_dequantize.argtypes = [vp, vp, i64, i64, ci, vp, vp]
     lib.mxfp6_device_status.restype = ci
     lib.mxfp6_device_status.argtypes = [ctypes.POINTER(ci)]
+    lib.mxfp6_debug_wait_timeout.restype = ci
+    lib.mxfp6_debug_wait_timeout.argtypes = [ci, vp]
     lib.mxfp6_debug_tma_dump.restype = ci
     lib.mxfp6_debug_tma_dump.argtypes = [vp, i64, i64, i64, i64, vp, vp]
     return lib

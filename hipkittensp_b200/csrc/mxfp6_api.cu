@@ -537,6 +537,16 @@ __global__ void tma_dump_kernel(const __grid_constant__ CUtensorMap tm, int x, i
     for (int i = threadIdx.x; i < 16384; i += blockDim.x) out[i] = gen[i];
 }
 
+// One warp waits on an mbarrier that nothing ever arrives on, with the same bounded wait the GEMM kernels use:
+// the wait must run out, record its status word and return.
+__global__ void wait_probe_kernel(GemmParams P) {
+    __shared__ uint64_t bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) { mbar_init(smem_u32(&bar), 1); abort_flag = 0; fence_barrier_init(); }
+    __syncthreads();
+    wait_bar_warp(smem_u32(&bar), 0, &abort_flag, P, 9);
+}
+
 }  // namespace mxfp6
 
 // ====================================================================================== C ABI
@@ -718,6 +728,20 @@ extern "C" int mxfp6_device_status(int* status_out) {
         if (d->ws) CUDA_TRY(cudaMemset(d->ws, 0, d->ws_bytes));
         return fail(MXFP6_ERR_DEVICE_WAIT, "a bounded wait ran out on the device: role %d, CTA %d", h[0] & 0xff, h[0] >> 8);
     }
+    return MXFP6_OK;
+}
+
+extern "C" int mxfp6_debug_wait_timeout(int budget_us, void* stream) {
+    if (budget_us < 1 || budget_us > 100000) return fail(MXFP6_ERR_BAD_ARG, "wait_timeout: budget must be 1..100000 us");
+    DeviceState* d = nullptr;
+    int rc = get_device_state(&d);
+    if (rc) return rc;
+    GemmParams P{};
+    P.status = d->status;
+    P.wait_cycles = d->wait_cycles / 2000000ull * (unsigned long long)budget_us;   // wait_cycles covers 2 s by default
+    if (P.wait_cycles < 1000) P.wait_cycles = 1000;
+    wait_probe_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(P);
+    CUDA_TRY(cudaGetLastError());
     return MXFP6_OK;
 }
 

@@ -15,6 +15,8 @@
  *     asynchronous on that stream and do not synchronise;
  *   - the return value is 0 on success, a MXFP6_ERR_* code otherwise; mxfp6_last_error() gives
  *     the message of the calling thread's last failure;
+ *   - the first call on a device (and the first call of a kernel variant) does one-time set-up (attribute
+ *     calls, a memset, for split shapes a cudaMalloc): make it before any stream capture;
  *   - preconditions: K % 128 == 0; packed operand pointers 32-byte aligned; C 2-byte aligned
  *     (16-byte aligned C with N % 8 == 0 takes the vector store path); M, N >= 0.
  *
@@ -151,6 +153,15 @@ int mxfp6_dequantize(const void* packed, const void* scales, int64_t rows, int64
  * (256_256_64_32_with16x32.cpp:385 leaves `ret` unused); this is the checked alternative.
  */
 int mxfp6_device_status(int* status_out);
+
+/*
+ * Diagnostic: launches one warp that waits, with the kernels' bounded wait and a budget of budget_us
+ * microseconds, on an mbarrier that nothing arrives on.  The wait runs out, the kernel returns, and the next
+ * mxfp6_device_status() reports MXFP6_ERR_DEVICE_WAIT with role 9: the failure path of the GEMM kernels,
+ * exercised without a fault, trap or hang.  (No counterpart in the reference, whose kernels have no waits
+ * that can be bounded.)
+ */
+int mxfp6_debug_wait_timeout(int budget_us, void* stream);
 
 /*
  * Diagnostic: TMA-loads one 128-row x 128-element box of a packed operand (rows row0.., elements

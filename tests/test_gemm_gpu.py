@@ -295,3 +295,19 @@ def test_requant_epilogue_random_inputs_within_one_step():
     ref2 = got.astype(np.float64) @ R.dequantize(pw, sw, R.E4M3).astype(np.float64).T
     absdot2 = np.abs(got).astype(np.float64) @ np.abs(R.dequantize(pw, sw, R.E4M3)).astype(np.float64).T
     check(C2.float().cpu().numpy(), ref2, absdot2)
+
+
+def test_bounded_wait_reports_and_context_survives():
+    """Failure path without a fault: a wait that nothing satisfies runs out after its budget (1 ms here), the
+    kernel returns, the status word names the waiter, and the GPU keeps working."""
+    import time
+    assert hk.device_status() == 0
+    t0 = time.perf_counter()
+    _lib_check = hk._lib.check
+    _lib_check(hk.lib.mxfp6_debug_wait_timeout(1000, None))
+    with pytest.raises(hk.Mxfp6Error) as ei:
+        hk.device_status()
+    assert time.perf_counter() - t0 < 2.0
+    assert ei.value.code == hk._lib.ERR_DEVICE_WAIT and "role 9" in str(ei.value)
+    assert hk.device_status() == 0                      # the status word was cleared
+    _case("normal", 256, 256, 512)                      # and the context is still usable
