@@ -1,0 +1,94 @@
+"""Parity at the full benchmark sizes.  The CPU oracle cannot produce a whole 8192 x 8192 result in seconds, so
+each configuration is checked on a seeded sample of complete rows of C against the fp64 oracle (every column of
+those rows, hence every tile column and every K-block of the kernel's schedule), and, where two different
+kernels can compute the same problem, on agreement between them over the whole matrix."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import hipkittensp_b200 as hk
+from oracle import mxfp6_ref as R
+from tests.gpu_util import ROW_REL_TOL, ULP_TOL
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(autouse=True)
+def _clean_env():
+    yield
+    os.environ.pop("MXFP6_FORCE_CFG", None)
+
+
+def _quantized(config, M, N, K, fmt, seed):
+    A, B = R.make_inputs(config, M, N, K, seed)
+    pa, sa = R.c_quantize(A, fmt)
+    pb, sb = R.c_quantize(B, fmt)
+    return pa, sa, pb, sb
+
+
+def _check_rows(C, pa, sa, pb, sb, fmt, rows):
+    """Rows `rows` of the GPU result against the fp64 oracle (tolerances of the parity tests)."""
+    Bd = torch.from_numpy(R.c_dequantize(pb, sb, fmt)).double()
+    Ad = torch.from_numpy(R.c_dequantize(pa[rows], sa[rows], fmt)).double()
+    ref = (Ad @ Bd.t()).numpy()
+    absdot = (Ad.abs() @ Bd.abs().t()).numpy()
+    got = C[torch.as_tensor(rows, device=C.device)].float().cpu().numpy()
+    assert not np.isnan(got).any()
+    rep = R.error_report(got, ref, absdot)
+    assert rep["row_rel"] <= ROW_REL_TOL and rep["max_ulp"] <= ULP_TOL, rep
+    return rep
+
+
+def _gpu(pa, sa, pb, sb, fmt):
+    t = [torch.from_numpy(x).cuda() for x in (pa, sa, pb, sb)]
+    C = hk.gemm(t[0], t[1], t[2], t[3], fmt)
+    assert hk.device_status() == 0
+    return C
+
+
+def test_config_8192_cubed_lognormal():
+    M = N = K = 8192
+    pa, sa, pb, sb = _quantized("lognormal", M, N, K, R.E2M3, seed=0)
+    C = _gpu(pa, sa, pb, sb, R.E2M3)
+    rows = np.sort(np.random.default_rng(0).choice(M, 48, replace=False))
+    rows[:4] = [0, 127, 128, M - 1]                        # tile edges
+    _check_rows(C, pa, sa, pb, sb, R.E2M3, np.sort(rows))
+    # the single-CTA kernel computes the same matrix
+    os.environ["MXFP6_FORCE_CFG"] = "256,0,0,0"
+    C1 = _gpu(pa, sa, pb, sb, R.E2M3)
+    diff = (C.float() - C1.float()).abs()
+    assert float((diff / C1.float().abs().clamp_min(1e-30)).max()) <= 2 ** -7, "pair and single-CTA kernels disagree by more than 1 bf16 ulp"
+    assert float((C != C1).float().mean()) < 1e-3
+
+
+def test_config_ffn_e3m2_with_outlier_channels():
+    M, N, K = 4096, 14336, 8192
+    pa, sa, pb, sb = _quantized("ffn", M, N, K, R.E3M2, seed=0)
+    C = _gpu(pa, sa, pb, sb, R.E3M2)
+    rows = np.sort(np.random.default_rng(1).choice(M, 24, replace=False))
+    _check_rows(C, pa, sa, pb, sb, R.E3M2, rows)
+
+
+@pytest.mark.parametrize("M", [1, 16, 64])
+def test_config_decode_full(M):
+    N, K = 28672, 8192
+    pa, sa, pb, sb = _quantized("decode", M, N, K, R.E2M3, seed=M)
+    C = _gpu(pa, sa, pb, sb, R.E2M3)
+    rows = np.arange(M) if M <= 16 else np.sort(np.random.default_rng(2).choice(M, 16, replace=False))
+    _check_rows(C, pa, sa, pb, sb, R.E2M3, rows)
+    # whole-tile kernel (no K split) gives the same result up to the summation order of split tiles
+    os.environ["MXFP6_FORCE_CFG"] = "%d,1,0" % (16 if M <= 16 else 64)
+    C1 = _gpu(pa, sa, pb, sb, R.E2M3)
+    assert float(((C.float() - C1.float()).abs() / C1.float().abs().clamp_min(1e-30)).median()) == 0.0
+    assert float((C != C1).float().mean()) < 2e-2
+
+
+def test_config_sharded_one_shard():
+    """One g=8 shard of the column-parallel configuration: A [16384, K] against 7168 rows of B."""
+    M, N, K = 16384, 7168, 8192
+    pa, sa, pb, sb = _quantized("normal", M, N, K, R.E2M3, seed=3)
+    C = _gpu(pa, sa, pb, sb, R.E2M3)
+    rows = np.sort(np.random.default_rng(3).choice(M, 32, replace=False))
+    _check_rows(C, pa, sa, pb, sb, R.E2M3, rows)
