@@ -30,6 +30,10 @@ sys.path.insert(0, ROOT)
 
 METRIC = "mxfp6_gemm_tflops"
 UNIT = "TFLOP/s"
+# The reference's own published figure for this metric: HipKittens FP6 GEMM at 8192^3 on an AMD MI355X
+# (analysis/fp6_gemm/mi355x_fp6_gemm.json:2-6); the same file set records 3038.77 for NVIDIA's CUTLASS on a B200.
+PUBLISHED_TFLOPS_8192 = 2861.52
+
 HEADLINE = dict(M=8192, N=8192, K=8192, fmt="e2m3", dist="lognormal(0,1.5) block amplitudes")
 SHARDED = dict(M=16384, N=57344, K=8192, fmt="e2m3", dist="N(0,1)")
 
@@ -279,7 +283,9 @@ def run_native(args):
         line = {
             "metric": METRIC, "value": round(value, 2), "unit": UNIT, "n_gpus": world, "steps": K_steps, "warmup": W,
             "ms_per_step": round(ms_step, 5), "higher_is_better": True,
-            "scaling": "weak" if world == 1 else "strong", "vs_baseline": None, "dtype": "fp6_e2m3xfp6_e2m3->f32->bf16",
+            "scaling": "weak" if world == 1 else "strong",
+            "vs_baseline": round(value / PUBLISHED_TFLOPS_8192, 4) if (world == 1 and not args.small and not args.shape) else None,
+            "dtype": "fp6_e2m3xfp6_e2m3->f32->bf16",
             "data": "synthetic",
             "config": {"workload": workload, "M": M, "N": N, "K": K, "format": "e2m3", "scale": "e8m0 per 32 along K",
                        "l2": "operand sets rotate and A+B+C exceed L2" if world == 1 else "A+B shard+C exceed L2",
