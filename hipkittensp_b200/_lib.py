@@ -19,7 +19,7 @@ OK, ERR_BAD_ARG, ERR_CUDA, ERR_DEVICE_WAIT, ERR_UNSUPPORTED = 0, 1, 2, 3, 4
 
 # every symbol include/mxfp6.h declares
 SYMBOLS = ("mxfp6_version", "mxfp6_last_error", "mxfp6_gemm", "mxfp6_gemm_workspace_bytes", "mxfp6_gemm_ws",
-           "mxfp6_gemm_noalloc", "mxfp6_gemm_multi", "mxfp6_gemm_ex", "mxfp6_gemm_requant",
+           "mxfp6_gemm_noalloc", "mxfp6_gemm_multi", "mxfp6_gemm_ex", "mxfp6_gemm_requant", "mxfp6_gemm_scaled",
            "mxfp6_quantize", "mxfp6_dequantize", "mxfp6_device_status", "mxfp6_debug_tma_dump", "mxfp6_debug_wait_timeout")
 
 
@@ -51,6 +51,8 @@ def _load() -> ctypes.CDLL:
     lib.mxfp6_gemm_ex.argtypes = [vp, vp, vp, vp, vp, i64, i64, i64, ci, ci, ctypes.c_uint, vp]
     lib.mxfp6_gemm_requant.restype = ci
     lib.mxfp6_gemm_requant.argtypes = [vp, vp, vp, vp, vp, vp, i64, i64, i64, ci, ci, ci, vp]
+    lib.mxfp6_gemm_scaled.restype = ci
+    lib.mxfp6_gemm_scaled.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, i64, i64, i64, ci, ci, vp]
     lib.mxfp6_gemm_multi.restype = ci
     lib.mxfp6_gemm_multi.argtypes = [vp, vp, vp, vp, ctypes.POINTER(vp), ci, i64, i64, i64, i64, ci, ci, vp]
     lib.mxfp6_gemm_workspace_bytes.restype = sz

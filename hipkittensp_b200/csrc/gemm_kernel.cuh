@@ -58,7 +58,68 @@ struct GemmParams {
     unsigned long long wait_cycles;  // budget of one wait in clock cycles
     int group_p;               // pair kernel: P-tiles per rasterisation group
     int early_p;               // swapped form: P (the weights) may be read before the preceding kernel has finished
+    // optional fp32 epilogue, applied to the finished sum before it is rounded (null = absent):
+    // C[m,n] = (acc * scale_n[n]) * scale_m[m] + bias_n[n]
+    const float* scale_m;      // [M]
+    const float* scale_n;      // [N]
+    const float* bias_n;       // [N]
 };
+
+// The epilogue arithmetic for one element.  D[p,q] is C[p,q], or C[q,p] in the swapped form.  Three separate
+// roundings (no fused multiply-add), in the order column scale, row scale, bias.
+template <bool SWAP>
+__device__ __forceinline__ float affine_one(const GemmParams& P, float x, int p, int q) {
+    const int m = SWAP ? q : p, n = SWAP ? p : q;
+    const float sn = (P.scale_n && n < P.c_cols) ? __ldg(P.scale_n + n) : 1.f;
+    const float sm = (P.scale_m && m < P.c_rows) ? __ldg(P.scale_m + m) : 1.f;
+    const float bn = (P.bias_n && n < P.c_cols) ? __ldg(P.bias_n + n) : 0.f;
+    return __fadd_rn(__fmul_rn(__fmul_rn(x, sn), sm), bn);
+}
+
+__device__ __forceinline__ bool has_affine(const GemmParams& P) {
+    return P.scale_m != nullptr || P.scale_n != nullptr || P.bias_n != nullptr;
+}
+
+// The same for the CW consecutive columns q0.. of row p that one epilogue thread holds.
+template <bool SWAP, int CW>
+__device__ __forceinline__ void affine_chunk(const GemmParams& P, uint32_t (&v)[CW], int p, int q0) {
+    if (SWAP) {
+        // p is the column of C: one scale and one bias for the whole chunk; the row scale varies along it
+        const bool in = p < P.c_cols;
+        const float sn = (P.scale_n && in) ? __ldg(P.scale_n + p) : 1.f;
+        const float bn = (P.bias_n && in) ? __ldg(P.bias_n + p) : 0.f;
+#pragma unroll
+        for (int i = 0; i < CW; ++i) {
+            const float sm = (P.scale_m && q0 + i < P.c_rows) ? __ldg(P.scale_m + q0 + i) : 1.f;
+            v[i] = __float_as_uint(__fadd_rn(__fmul_rn(__fmul_rn(__uint_as_float(v[i]), sn), sm), bn));
+        }
+    } else {
+        const float sm = (P.scale_m && p < P.c_rows) ? __ldg(P.scale_m + p) : 1.f;
+        const bool whole = q0 + CW <= P.c_cols;     // q0 is a multiple of 16 and the vectors are 16-byte aligned
+#pragma unroll
+        for (int i = 0; i < CW; i += 4) {
+            float4 sn = make_float4(1.f, 1.f, 1.f, 1.f), bn = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (whole) {
+                if (P.scale_n) sn = __ldg(reinterpret_cast<const float4*>(P.scale_n + q0 + i));
+                if (P.bias_n) bn = __ldg(reinterpret_cast<const float4*>(P.bias_n + q0 + i));
+            } else {
+                float* s4 = reinterpret_cast<float*>(&sn);
+                float* b4 = reinterpret_cast<float*>(&bn);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    if (q0 + i + e < P.c_cols) {
+                        if (P.scale_n) s4[e] = __ldg(P.scale_n + q0 + i + e);
+                        if (P.bias_n) b4[e] = __ldg(P.bias_n + q0 + i + e);
+                    }
+                }
+            }
+            v[i + 0] = __float_as_uint(__fadd_rn(__fmul_rn(__fmul_rn(__uint_as_float(v[i + 0]), sn.x), sm), bn.x));
+            v[i + 1] = __float_as_uint(__fadd_rn(__fmul_rn(__fmul_rn(__uint_as_float(v[i + 1]), sn.y), sm), bn.y));
+            v[i + 2] = __float_as_uint(__fadd_rn(__fmul_rn(__fmul_rn(__uint_as_float(v[i + 2]), sn.z), sm), bn.z));
+            v[i + 3] = __float_as_uint(__fadd_rn(__fmul_rn(__fmul_rn(__uint_as_float(v[i + 3]), sn.w), sm), bn.w));
+        }
+    }
+}
 
 template <int BN_, bool SWAP_, bool STREAMK_>
 struct GemmCfg {
@@ -491,6 +552,7 @@ mxfp6_gemm_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constan
             float* slot = nullptr;
             if (partial) slot = P.ws_partial + ((size_t)sg.tile * P.ws_slots + sg.segidx) * (size_t)(BN * 128);
             const int p = sg.p0 + prow;
+            const bool affine = has_affine(P);
 #pragma unroll 1
             for (int ci = 0; ci < NCH; ++ci) {
                 // with overlapping accumulators the 32 shared columns are drained first
@@ -502,6 +564,7 @@ mxfp6_gemm_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constan
                 if (Cfg::OVERLAP && ci == 0) { tc_fence_before(); mbar_arrive(bar_ovl); }
                 if (!Cfg::OVERLAP && ci == NCH - 1) { tc_fence_before(); mbar_arrive(bar_acc_empty(b)); }
                 const int qc = sg.q0 + ch * CW;              // first D column of this chunk
+                if (!partial && affine) affine_chunk<Cfg::SWAP, CW>(P, v, p, qc);
                 if (partial) {
 #pragma unroll
                     for (int i = 0; i < CW; ++i) slot[(size_t)(ch * CW + i) * 128 + prow] = __uint_as_float(v[i]);
@@ -584,6 +647,7 @@ mxfp6_gemm_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constan
 #pragma unroll
                         for (int j = 0; j < FC; ++j) {
                             const int q = sg.q0 + col0 + j;
+                            if (affine) acc[j] = affine_one<Cfg::SWAP>(P, acc[j], p, q);
                             if (Cfg::SWAP) {
                                 if (p < P.c_cols && q < P.c_rows) P.c[(size_t)q * P.ldc + p] = __float2bfloat16_rn(acc[j]);
                             } else {

@@ -31,19 +31,25 @@ struct PairCfg {
     static constexpr int P_BYTES = BM * BK;               // 16 KB
     static constexpr int Q_BYTES = (BN / 2) * BK;         // 16 KB: this CTA's half of B
     static constexpr int STAGE_BYTES = P_BYTES + Q_BYTES;
-    static constexpr int STAGES = 5;
-    static constexpr int OUT_COLS = 64;                   // columns of one output staging buffer (128 bytes of bf16)
-    static constexpr int OUT_BYTES = BM * OUT_COLS * 2;   // 16 KB, two of them
+#ifndef MXFP6_PAIR_STAGES
+#define MXFP6_PAIR_STAGES 5
+#endif
+    static constexpr int STAGES = MXFP6_PAIR_STAGES;
+    // output staging: with 5 stages two buffers of 128 rows x 64 columns (128-byte swizzle); with 6 stages one
+    // buffer of 128 x 32 columns (64-byte swizzle) is what still fits
+    static constexpr int OUT_COLS = STAGES >= 6 ? 32 : 64;
+    static constexpr int OUT_BUFS = STAGES >= 6 ? 1 : 2;
+    static constexpr int OUT_BYTES = BM * OUT_COLS * 2;
     static constexpr int RAW_SLOTS = 2;
     static constexpr int RAW_BYTES = (BM + BN) * 16;      // own P rows + all 256 Q rows, 16 scale bytes each
     static constexpr int ATOM_BYTES = 512 * 3;            // P atom + two Q atoms of one K-block
     static constexpr int GROUP_BYTES = 4 * ATOM_BYTES;    // the 4 K-blocks one raw slab covers
-    static constexpr int ATOM_GROUPS = 3;
+    static constexpr int ATOM_GROUPS = STAGES >= 6 ? 2 : 3;
     static constexpr int ACC_COL1 = 224;
     static constexpr int SF_COL = 480;
     static constexpr int TMEM_COLS = 512;
     static constexpr int NUM_BARS = 2 * STAGES + 2 * RAW_SLOTS + 2 * ATOM_GROUPS + 3;
-    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 2 * OUT_BYTES + RAW_SLOTS * RAW_BYTES +
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + OUT_BUFS * OUT_BYTES + RAW_SLOTS * RAW_BYTES +
                                       ATOM_GROUPS * GROUP_BYTES + NUM_BARS * 8 + 64;
     static constexpr int SMEM_ALLOC = SMEM_BYTES + 1024;
     static constexpr int THREADS = 256;
@@ -99,7 +105,7 @@ mxfp6_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_co
 
     const uint32_t stage_base = smem_base;
     const uint32_t out_base = stage_base + Cfg::STAGES * Cfg::STAGE_BYTES;      // 1024-byte aligned
-    const uint32_t raw_base = out_base + 2 * Cfg::OUT_BYTES;
+    const uint32_t raw_base = out_base + Cfg::OUT_BUFS * Cfg::OUT_BYTES;
     const uint32_t atom_base = raw_base + Cfg::RAW_SLOTS * Cfg::RAW_BYTES;
     const uint32_t bar_base = atom_base + Cfg::ATOM_GROUPS * Cfg::GROUP_BYTES;
     auto bar_full = [&](int s) { return bar_base + 8u * s; };
@@ -297,24 +303,28 @@ mxfp6_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_co
             tc_fence_after();
             const uint32_t tacc = tmem_base + ((uint32_t)(quad * 32) << 16) + (b ? Cfg::ACC_COL1 : 0);
             const int my_p0 = p0 + 128 * (int)rank;
+            constexpr int OC = Cfg::OUT_COLS;                 // columns per piece
+            const bool affine = has_affine(P);
+            constexpr int NP = 256 / OC;
 #pragma unroll 1
-            for (int ci = 0; ci < 4; ++ci) {
-                // 64 columns per step; the piece that holds the 32 columns shared by the two accumulators goes first
-                const int piece = b == 0 ? (ci + 3) % 4 : ci;
-                const uint32_t buf = out_base + (n_out & 1) * Cfg::OUT_BYTES;
+            for (int ci = 0; ci < NP; ++ci) {
+                // the piece that holds the 32 columns shared by the two accumulators goes first
+                const int piece = b == 0 ? (ci + NP - 1) % NP : ci;
+                const uint32_t buf = out_base + (n_out % Cfg::OUT_BUFS) * Cfg::OUT_BYTES;
                 // accumulator columns first: the shared columns are released to the next tile's MMA as early as possible
-                uint32_t v[64];
-                tmem_ld_x32(tacc + piece * 64, reinterpret_cast<uint32_t(&)[32]>(v[0]));
-                tmem_ld_x32(tacc + piece * 64 + 32, reinterpret_cast<uint32_t(&)[32]>(v[32]));
+                uint32_t v[OC];
+#pragma unroll
+                for (int h = 0; h < OC / 32; ++h) tmem_ld_x32(tacc + piece * OC + 32 * h, reinterpret_cast<uint32_t(&)[32]>(v[32 * h]));
                 tmem_ld_wait();
                 if (ci == 0) { tc_fence_before(); mbar_arrive_cluster(ovl0); }
+                if (affine) affine_chunk<false, OC>(P, v, my_p0 + prow, q0 + piece * OC);
                 if (P.q_fmt >= 0) {
-                    // the result leaves as an MX operand of the next layer: 64 columns = two blocks of 32
+                    // the result leaves as an MX operand of the next layer, in blocks of 32 columns
                     const int row = my_p0 + prow;
                     if (row < P.c_rows) {
 #pragma unroll
-                        for (int hb = 0; hb < 2; ++hb) {
-                            const int col = q0 + piece * 64 + 32 * hb;
+                        for (int hb = 0; hb < OC / 32; ++hb) {
+                            const int col = q0 + piece * OC + 32 * hb;
                             if (col < P.c_cols)
                                 quant_store32(v + 32 * hb, P.q_fmt, P.q_out, (size_t)P.q_ld, P.q_scales, P.c_cols, row, col);
                         }
@@ -322,24 +332,26 @@ mxfp6_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_co
                     ++n_out;
                     continue;
                 }
-                // the stores issued two steps ago have finished reading this staging buffer
-                if (etid == 0) bulk_wait_group_read<1>();
+                // the stores that last used this staging buffer have finished reading it
+                if (etid == 0) bulk_wait_group_read<Cfg::OUT_BUFS - 1>();
                 asm volatile("bar.sync 1, 128;" ::: "memory");
-                // row prow of the 128x64 bf16 piece = 128 bytes = eight 16-byte chunks, chunk c stored at c ^ (row % 8)
-                const uint32_t rowaddr = buf + prow * 128;
+                // row prow of the piece = OC*2 bytes in 16-byte chunks; chunk c is stored at c ^ (row % 8) (128-byte
+                // swizzle, 64 columns) or c ^ ((row / 2) % 4) (64-byte swizzle, 32 columns), as the TMA store expects
+                const uint32_t rowaddr = buf + prow * (OC * 2);
+                const uint32_t sw = OC == 64 ? (uint32_t)(prow & 7) : (uint32_t)((prow >> 1) & 3);
 #pragma unroll
-                for (int c = 0; c < 8; ++c) {
+                for (int c = 0; c < OC / 8; ++c) {
                     const uint32_t x0 = pack_bf16x2(__uint_as_float(v[8 * c + 0]), __uint_as_float(v[8 * c + 1]));
                     const uint32_t x1 = pack_bf16x2(__uint_as_float(v[8 * c + 2]), __uint_as_float(v[8 * c + 3]));
                     const uint32_t x2 = pack_bf16x2(__uint_as_float(v[8 * c + 4]), __uint_as_float(v[8 * c + 5]));
                     const uint32_t x3 = pack_bf16x2(__uint_as_float(v[8 * c + 6]), __uint_as_float(v[8 * c + 7]));
                     asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};"
-                                 ::"r"(rowaddr + ((c ^ (prow & 7)) << 4)), "r"(x0), "r"(x1), "r"(x2), "r"(x3) : "memory");
+                                 ::"r"(rowaddr + ((c ^ sw) << 4)), "r"(x0), "r"(x1), "r"(x2), "r"(x3) : "memory");
                 }
                 fence_proxy_async_smem();
                 asm volatile("bar.sync 1, 128;" ::: "memory");
                 if (etid == 0) {
-                    for (int d = 0; d < P.ndst; ++d) tma_store_2d(&cmaps.m[d], buf, q0 + piece * 64, my_p0);
+                    for (int d = 0; d < P.ndst; ++d) tma_store_2d(&cmaps.m[d], buf, q0 + piece * OC, my_p0);
                     bulk_commit_group();
                 }
                 ++n_out;

@@ -109,6 +109,7 @@ static std::map<MapKey, CUtensorMap> g_maps;
 // kind 1: scale bytes [rows, K/32] (inner = K/32 bytes), box 16 x box_rows, no swizzle
 // kind 3: fp8 operand [rows, K] (inner = K bytes), box 128 x box_rows, 128-byte swizzle
 // kind 2: bf16 output block [rows, inner] with a row stride of stride_bytes, box 64 x box_rows, 128-byte swizzle
+// kind 4: the same with box 32 x box_rows and the 64-byte swizzle
 static int make_map(const void* ptr, int64_t rows, int64_t inner, int box_rows, int kind, CUtensorMap* out,
                     int64_t stride_bytes = 0) {
     MapKey key{ptr, rows, inner, stride_bytes, box_rows, kind};
@@ -120,14 +121,14 @@ static int make_map(const void* ptr, int64_t rows, int64_t inner, int box_rows, 
     int rc = get_encode_fn();
     if (rc) return rc;
     cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)rows};
-    cuuint64_t strides[1] = {(cuuint64_t)(kind == 0 ? inner * 3 / 4 : kind == 2 ? stride_bytes : inner)};
-    cuuint32_t box[2] = {(cuuint32_t)(kind == 1 ? 16 : kind == 2 ? 64 : 128), (cuuint32_t)box_rows};
+    cuuint64_t strides[1] = {(cuuint64_t)(kind == 0 ? inner * 3 / 4 : (kind == 2 || kind == 4) ? stride_bytes : inner)};
+    cuuint32_t box[2] = {(cuuint32_t)(kind == 1 ? 16 : kind == 2 ? 64 : kind == 4 ? 32 : 128), (cuuint32_t)box_rows};
     cuuint32_t estr[2] = {1, 1};
     const CUtensorMapDataType dt = kind == 0 ? CU_TENSOR_MAP_DATA_TYPE_16U6_ALIGN16B
-                                 : kind == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+                                 : (kind == 2 || kind == 4) ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
     CUresult r = g_encode(out, dt, 2,
                           const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                          kind == 1 ? CU_TENSOR_MAP_SWIZZLE_NONE : CU_TENSOR_MAP_SWIZZLE_128B,
+                          kind == 1 ? CU_TENSOR_MAP_SWIZZLE_NONE : kind == 4 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B,
                           CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS)
         return fail(MXFP6_ERR_CUDA, "cuTensorMapEncodeTiled(kind=%d rows=%lld inner=%lld box_rows=%d) failed with %d",
@@ -261,9 +262,17 @@ struct Dest {
     int64_t ldc;
 };
 
+// optional fp32 epilogue vectors (null = absent)
+struct Affine {
+    const float* scale_m = nullptr;   // [M]
+    const float* scale_n = nullptr;   // [N]
+    const float* bias_n = nullptr;    // [N]
+};
+
 static int gemm_impl(const void* a, const void* sfa, const void* b, const void* sfb, const Dest& dst, int64_t M, int64_t N,
                      int64_t K, int fmt_a, int fmt_b, void* ws, size_t ws_bytes, bool own_ws, void* stream,
-                     unsigned flags = 0, void* q_out = nullptr, void* q_scales = nullptr, int q_fmt = -1) {
+                     unsigned flags = 0, void* q_out = nullptr, void* q_scales = nullptr, int q_fmt = -1,
+                     const Affine& aff = Affine{}) {
     void* c = dst.c[0];
     if (M < 0 || N < 0 || K < 0) return fail(MXFP6_ERR_BAD_ARG, "negative dimension (M=%lld N=%lld K=%lld)", (long long)M, (long long)N, (long long)K);
     if (K % 128 != 0) return fail(MXFP6_ERR_BAD_ARG, "K=%lld must be a multiple of 128", (long long)K);
@@ -359,8 +368,9 @@ static int gemm_impl(const void* a, const void* sfa, const void* b, const void* 
     P.early_p = (pl.swap && (flags & MXFP6_FLAG_B_STATIC) && env_int("MXFP6_PDL", 1)) ? 1 : 0;
     P.group_p = env_int("MXFP6_GROUP_P", 16);   // 16 pair-tiles (4096 rows of A) share each tile of B
     if (P.group_p < 1) P.group_p = 1;
+    P.scale_m = aff.scale_m; P.scale_n = aff.scale_n; P.bias_n = aff.bias_n;
 
- if (pl.pair) {
+    if (pl.pair) {
         auto kern = mxfp6_gemm_pair_kernel;
         {
             std::lock_guard<std::mutex> lk(g_mu);
@@ -371,7 +381,7 @@ static int gemm_impl(const void* a, const void* sfa, const void* b, const void* 
         }
         CMaps cm;
         for (int i = 0; i < 8; ++i)
-            if ((rc = make_map(dst.c[i < dst.n ? i : 0], M, N, 128, 2, &cm.m[i], dst.ldc * 2))) return rc;
+            if ((rc = make_map(dst.c[i < dst.n ? i : 0], M, N, 128, PairCfg::OUT_COLS == 64 ? 2 : 4, &cm.m[i], dst.ldc * 2))) return rc;
         cudaLaunchConfig_t lc = launch_config(pl.grid, PairCfg::THREADS, PairCfg::SMEM_ALLOC, st);
         CUDA_TRY(cudaLaunchKernelEx(&lc, kern, tp, tq, tsp, tsq, cm, P));
         return MXFP6_OK;
@@ -591,6 +601,31 @@ extern "C" int mxfp6_gemm_requant(const void* a, const void* sfa, const void* b,
         return MXFP6_OK;
     }
     return gemm_impl(a, sfa, b, sfb, Dest{{out}, 1, N}, M, N, K, fmt_a, fmt_b, nullptr, 0, true, stream, 0, out, out_scales, out_fmt);
+}
+
+// C = bias broadcast along rows: what the scaled GEMM yields for K = 0
+__global__ void bias_fill_kernel(__nv_bfloat16* c, const float* bias, int64_t M, int64_t N) {
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < M * N; i += (int64_t)gridDim.x * blockDim.x)
+        c[i] = __float2bfloat16_rn(__fadd_rn(0.f, bias[i % N]));
+}
+
+extern "C" int mxfp6_gemm_scaled(const void* a, const void* sfa, const void* b, const void* sfb, void* c,
+                                 const float* scale_a, const float* scale_b, const float* bias,
+                                 int64_t M, int64_t N, int64_t K, int fmt_a, int fmt_b, void* stream) {
+    if (((uintptr_t)scale_a & 3) || ((uintptr_t)scale_b & 15) || ((uintptr_t)bias & 15))
+        return fail(MXFP6_ERR_BAD_ARG, "scaled: scale_a must be 4-byte aligned, scale_b and bias 16-byte aligned");
+    if (K == 0 && bias && M > 0 && N > 0) {
+        if (!c) return fail(MXFP6_ERR_BAD_ARG, "null C");
+        DeviceState* dp = nullptr;
+        int rc = get_device_state(&dp);
+        if (rc) return rc;
+        bias_fill_kernel<<<dp->sm_count * 4, 256, 0, (cudaStream_t)stream>>>((__nv_bfloat16*)c, bias, M, N);
+        CUDA_TRY(cudaGetLastError());
+        return MXFP6_OK;
+    }
+    Affine aff;
+    aff.scale_m = scale_a; aff.scale_n = scale_b; aff.bias_n = bias;
+    return gemm_impl(a, sfa, b, sfb, Dest{{c}, 1, N}, M, N, K, fmt_a, fmt_b, nullptr, 0, true, stream, 0, nullptr, nullptr, -1, aff);
 }
 
 extern "C" int mxfp6_gemm_multi(const void* a, const void* sfa, const void* b, const void* sfb, void* const* c_dst,

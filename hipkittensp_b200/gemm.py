@@ -121,6 +121,39 @@ def gemm_requant(A, scale_A, B, scale_B, fmt: int = E2M3, fmt_b: int | None = No
     return out, scales
 
 
+def gemm_scaled(A, scale_A, B, scale_B, row_scale=None, col_scale=None, bias=None, fmt: int = E2M3,
+                fmt_b: int | None = None, out=None):
+    """C[m,n] = bf16((acc[m,n] * col_scale[n]) * row_scale[m] + bias[n]) with fp32 vectors row_scale [M], col_scale [N],
+    bias [N] (any may be None), applied in the GEMM epilogue: the per-row / per-column scaling of the reference's
+    scaled_matmul (kernels/torch_scaled/scaled_matmul.cu:253-265) on top of the MX block scales."""
+    _accept(A, "A", torch.uint8)
+    _accept(B, "B", torch.uint8)
+    _accept(scale_A, "scale_A", torch.uint8)
+    _accept(scale_B, "scale_B", torch.uint8)
+    fb = fmt if fmt_b is None else fmt_b
+    M, N, K = A.shape[0], B.shape[0], _k_of(A, fmt, "A")
+    if _k_of(B, fb, "B") != K:
+        raise RuntimeError("A and B disagree on K")
+    for name, v, n in (("row_scale", row_scale, M), ("col_scale", col_scale, N), ("bias", bias, N)):
+        if v is not None:
+            if not isinstance(v, torch.Tensor) or v.dtype != torch.float32 or not v.is_contiguous():
+                raise RuntimeError(f"{name} must be a contiguous fp32 tensor")
+            if v.device != A.device:
+                raise RuntimeError("Tensor must be on CUDA device")
+            if v.numel() != n:
+                raise RuntimeError(f"{name} must have {n} elements, has {v.numel()}")
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.bfloat16, device=A.device)
+    _accept(out, "C", torch.bfloat16)
+    if tuple(out.shape) != (M, N):
+        raise RuntimeError(f"C must be [{M}, {N}]")
+    ptr = lambda v: 0 if v is None else v.data_ptr()
+    with torch.cuda.device(A.device):
+        check(lib.mxfp6_gemm_scaled(A.data_ptr(), scale_A.data_ptr(), B.data_ptr(), scale_B.data_ptr(), out.data_ptr(),
+                                    ptr(row_scale), ptr(col_scale), ptr(bias), M, N, K, fmt, fb, _stream_ptr()))
+    return out
+
+
 def gemm(A, scale_A, B, scale_B, fmt: int = E2M3, fmt_b: int | None = None, out=None):
     """Allocating convenience wrapper around dispatch_micro; returns C."""
     M, N = A.shape[0], B.shape[0]

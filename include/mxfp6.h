@@ -90,6 +90,20 @@ int mxfp6_gemm_ex(const void* a, const void* sfa, const void* b, const void* sfb
 int mxfp6_gemm_requant(const void* a, const void* sfa, const void* b, const void* sfb, void* out, void* out_scales,
                        int64_t M, int64_t N, int64_t K, int fmt_a, int fmt_b, int out_fmt, void* stream);
 
+/*
+ * The GEMM with the per-row / per-column fp32 scaling of the reference's scale-taking kernel and an optional bias,
+ * applied to the finished fp32 sum before the single rounding to bf16:
+ *     C[m,n] = bf16( (acc[m,n] * scale_b[n]) * scale_a[m] + bias[n] )
+ * three separate fp32 roundings in this order (no fused multiply-add).  scale_a [M], scale_b [N] and bias [N] are
+ * fp32 device vectors; any of them may be NULL (factor 1 / addend 0); scale_b and bias 16-byte aligned.  These
+ * per-tensor-row factors come on top of the MX block scales, which act inside the MMA.  Stands in for the
+ * epilogue of kernels/torch_scaled/scaled_matmul.cu:253-265 (mul_col by scale_b, then mul_row by scale_a; argument
+ * order of :17-18); the bias has no counterpart there.
+ */
+int mxfp6_gemm_scaled(const void* a, const void* sfa, const void* b, const void* sfb, void* c,
+                      const float* scale_a, const float* scale_b, const float* bias,
+                      int64_t M, int64_t N, int64_t K, int fmt_a, int fmt_b, void* stream);
+
 /* Scratch bytes mxfp6_gemm_ws needs for this shape on the current device (0 if none). */
 size_t mxfp6_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K);
 

@@ -311,3 +311,54 @@ def test_bounded_wait_reports_and_context_survives():
     assert ei.value.code == hk._lib.ERR_DEVICE_WAIT and "role 9" in str(ei.value)
     assert hk.device_status() == 0                      # the status word was cleared
     _case("normal", 256, 256, 512)                      # and the context is still usable
+
+
+# ------------------------------------------------------------------------------- scaled / biased epilogue
+@pytest.mark.parametrize("shape,force", [((256, 384, 512), None), ((512, 768, 1024), "256,0,0,1"), ((130, 200, 256), None),
+                                         ((16, 1024, 2048), None), ((64, 520, 1024), None), ((256, 512, 512), "256,0,0")])
+@pytest.mark.parametrize("which", ["all", "row", "col", "bias"])
+def test_scaled_epilogue_bit_exact_on_exact_sums(shape, force, which):
+    """(acc * scale_b[n]) * scale_a[m] + bias[n], three fp32 roundings then bf16: with operands whose sums are exact
+    in every order the result must equal the same arithmetic done on the CPU, bit for bit."""
+    M, N, K = shape
+    if force:
+        os.environ["MXFP6_FORCE_CFG"] = force
+    A, B = _exact_inputs(M, N, K, seed=7 * M + N)
+    pa, sa = R.quantize(A, R.E2M3)
+    pb, sb = R.quantize(B, R.E2M3)
+    acc = (R.dequantize(pa, sa, R.E2M3).astype(np.float64) @ R.dequantize(pb, sb, R.E2M3).astype(np.float64).T).astype(np.float32)
+    rng = np.random.default_rng(M + N)
+    row = rng.lognormal(0, 1, M).astype(np.float32) if which in ("all", "row") else None
+    col = rng.lognormal(0, 1, N).astype(np.float32) if which in ("all", "col") else None
+    bias = rng.normal(0, 30, N).astype(np.float32) if which in ("all", "bias") else None
+    want = acc
+    if col is not None:
+        want = want * col[None, :]
+    if row is not None:
+        want = want * row[:, None]
+    if bias is not None:
+        want = want + bias[None, :]
+    assert want.dtype == np.float32
+    want = torch.from_numpy(want).to(torch.bfloat16).float().numpy()
+    t = [torch.from_numpy(x).cuda() for x in (pa, sa, pb, sb)]
+    dev = lambda v: None if v is None else torch.from_numpy(v).cuda()
+    C = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+    hk.gemm_scaled(t[0], t[1], t[2], t[3], dev(row), dev(col), dev(bias), R.E2M3, out=C)
+    assert hk.device_status() == 0
+    np.testing.assert_array_equal(C.float().cpu().numpy(), want)
+
+
+def test_scaled_epilogue_k_zero_gives_bias():
+    bias = torch.arange(64, dtype=torch.float32, device="cuda") - 7.25
+    e = torch.empty((8, 0), dtype=torch.uint8, device="cuda")
+    f = torch.empty((64, 0), dtype=torch.uint8, device="cuda")
+    C = hk.gemm_scaled(e, e.clone(), f, f.clone(), None, None, bias, R.E2M3)
+    torch.testing.assert_close(C.float(), bias.to(torch.bfloat16).float().expand(8, 64), rtol=0, atol=0)
+
+
+def test_scaled_epilogue_argument_checks():
+    pa, sa, pb, sb = [torch.from_numpy(x).cuda() for x in quantized_inputs("normal", 128, 128, 256)]
+    with pytest.raises(RuntimeError, match="128 elements"):
+        hk.gemm_scaled(pa, sa, pb, sb, torch.ones(64, device="cuda"))
+    with pytest.raises(RuntimeError, match="fp32"):
+        hk.gemm_scaled(pa, sa, pb, sb, None, torch.ones(128, device="cuda", dtype=torch.bfloat16))
