@@ -20,6 +20,7 @@ CSRC = os.path.join(PKG, "csrc")
 LIB = os.path.join(PKG, "libmxfp6.so")
 EXT = os.path.join(PKG, "tk_kernel" + (sysconfig.get_config_var("EXT_SUFFIX") or ".so"))
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
+CUDA_HOME = os.path.dirname(os.path.dirname(NVCC))
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-lineinfo",
               "-Xcompiler", "-fPIC", "-cudart", "shared", "-Xlinker", "-rpath,/usr/local/cuda/lib64"]
@@ -62,7 +63,8 @@ def build_ext(force: bool = False) -> str:
         return EXT
     cmd = ["g++", "-O2", "-std=c++17", "-shared", "-fPIC", "-fvisibility=hidden",
            "-I", pybind11.get_include(), "-I", sysconfig.get_paths()["include"], "-I", os.path.join(ROOT, "include"),
-           src, "-o", EXT, "-L", PKG, "-lmxfp6", "-Wl,-rpath,$ORIGIN"]
+           "-I", os.path.join(CUDA_HOME, "include"), src, "-o", EXT, "-L", PKG, "-lmxfp6",
+           "-L", os.path.join(CUDA_HOME, "lib64"), "-lcudart", "-Wl,-rpath,$ORIGIN"]
     res = subprocess.run(cmd, capture_output=True, text=True)
     if res.returncode != 0:
         raise RuntimeError("g++ failed:\n" + res.stdout + res.stderr)

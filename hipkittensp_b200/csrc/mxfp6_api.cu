@@ -65,6 +65,7 @@ static int get_device_state(DeviceState** out) {
     CUDA_TRY(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64) return fail(MXFP6_ERR_BAD_ARG, "device index %d out of range", dev);
     DeviceState& d = g_dev[dev];
+    std::lock_guard<std::mutex> lk(g_mu);      // two threads may make their first call on a device together
     if (!d.init) {
         int khz = 0;
         CUDA_TRY(cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, dev));
@@ -224,16 +225,15 @@ static Plan make_plan(int64_t M, int64_t N, int64_t K, int sm_count, bool allow_
 // Launch configuration shared by the GEMM kernels.  Programmatic stream serialisation lets the next kernel of
 // the stream begin its set-up (barriers, TMEM, descriptor prefetch) before this one has drained; the kernels
 // call griddepcontrol.wait before their first global access.  MXFP6_PDL=0 turns it off.
-static cudaLaunchAttribute g_pdl_attr;
-static cudaLaunchConfig_t launch_config(int grid, int threads, int smem, cudaStream_t st) {
+static cudaLaunchConfig_t launch_config(int grid, int threads, int smem, cudaStream_t st, cudaLaunchAttribute* attr) {
     cudaLaunchConfig_t lc{};
     lc.gridDim = dim3((unsigned)grid, 1, 1);
     lc.blockDim = dim3((unsigned)threads, 1, 1);
     lc.dynamicSmemBytes = (size_t)smem;
     lc.stream = st;
-    g_pdl_attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    g_pdl_attr.val.programmaticStreamSerializationAllowed = 1;
-    lc.attrs = &g_pdl_attr;
+    attr->id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr->val.programmaticStreamSerializationAllowed = 1;
+    lc.attrs = attr;
     lc.numAttrs = env_int("MXFP6_PDL", 1) ? 1 : 0;
     return lc;
 }
@@ -249,7 +249,8 @@ static int launch_cfg(DeviceState& d, const Plan& pl, const CUtensorMap& tp, con
             d.smem_attr_set[(const void*)kern] = true;
         }
     }
-    cudaLaunchConfig_t lc = launch_config(pl.grid, Cfg::THREADS, Cfg::SMEM_ALLOC, st);
+    cudaLaunchAttribute attr{};
+    cudaLaunchConfig_t lc = launch_config(pl.grid, Cfg::THREADS, Cfg::SMEM_ALLOC, st, &attr);
     CUDA_TRY(cudaLaunchKernelEx(&lc, kern, tp, tq, tsp, tsq, P));
     return MXFP6_OK;
 }
@@ -380,9 +381,12 @@ static int gemm_impl(const void* a, const void* sfa, const void* b, const void* 
             }
         }
         CMaps cm;
-        for (int i = 0; i < 8; ++i)
-            if ((rc = make_map(dst.c[i < dst.n ? i : 0], M, N, 128, PairCfg::OUT_COLS == 64 ? 2 : 4, &cm.m[i], dst.ldc * 2))) return rc;
-        cudaLaunchConfig_t lc = launch_config(pl.grid, PairCfg::THREADS, PairCfg::SMEM_ALLOC, st);
+        for (int i = 0; i < 8; ++i) {
+            if (i >= dst.n) { cm.m[i] = cm.m[0]; continue; }     // unused slots hold a valid map all the same
+            if ((rc = make_map(dst.c[i], M, N, 128, PairCfg::OUT_COLS == 64 ? 2 : 4, &cm.m[i], dst.ldc * 2))) return rc;
+        }
+        cudaLaunchAttribute attr{};
+        cudaLaunchConfig_t lc = launch_config(pl.grid, PairCfg::THREADS, PairCfg::SMEM_ALLOC, st, &attr);
         CUDA_TRY(cudaLaunchKernelEx(&lc, kern, tp, tq, tsp, tsq, cm, P));
         return MXFP6_OK;
     }

@@ -1,11 +1,13 @@
 // Python extension `tk_kernel` with one function `dispatch_micro`, the module and function names the
 // reference's harness imports (kernels/gemm/bf16fp32/256_256_64_32_with16x32.cpp:389-393, bench.py:34).
 // Like the reference's binding (include/pyutils/pyutils.cuh:15-47) it duck-types torch tensors --
-// class name, is_contiguous(), device.type, shape, data_ptr() -- and does not link against torch.
+// class name, is_contiguous(), is_cuda, shape, data_ptr() -- and does not link against torch.
 // It adds the dtype / shape cross-checks the reference leaves out and forwards to the C ABI.
+#include <cuda_runtime_api.h>
 #include <pybind11/pybind11.h>
 
 #include <array>
+#include <cstring>
 #include <cstdint>
 #include <stdexcept>
 #include <string>
@@ -16,18 +18,40 @@ namespace py = pybind11;
 
 namespace {
 
+enum class DType { U8, BF16, Other };
+
 struct TensorView {
     uint64_t ptr;
     std::array<int64_t, 4> shape;   // left-padded with 1s, as the reference's gl<> descriptors are
-    std::string dtype;
+    DType dtype;
     int device;
 };
 
+// Objects looked up once: the two dtypes the operator accepts and torch's accessor of the current stream handle.
+struct TorchHandles {
+    py::object u8, bf16, raw_stream, cuda;
+    TorchHandles() {
+        py::module_ torch = py::module_::import("torch");
+        u8 = torch.attr("uint8");
+        bf16 = torch.attr("bfloat16");
+        cuda = torch.attr("cuda");
+        py::object c = torch.attr("_C");
+        if (py::hasattr(c, "_cuda_getCurrentRawStream")) raw_stream = c.attr("_cuda_getCurrentRawStream");
+    }
+    uint64_t current_stream(int device) const {
+        if (raw_stream) return raw_stream(device).cast<uint64_t>();
+        return cuda.attr("current_stream")(device).attr("cuda_stream").cast<uint64_t>();
+    }
+};
+const TorchHandles& handles() {
+    static TorchHandles* h = new TorchHandles();   // never destroyed: outlives interpreter shutdown order problems
+    return *h;
+}
+
 TensorView view_of(const py::object& obj) {
-    if (!(py::hasattr(obj, "__class__") && obj.attr("__class__").attr("__name__").cast<std::string>() == "Tensor"))
-        throw std::runtime_error("Expected a torch.Tensor");
+    if (std::strcmp(Py_TYPE(obj.ptr())->tp_name, "Tensor") != 0) throw std::runtime_error("Expected a torch.Tensor");
     if (!obj.attr("is_contiguous")().cast<bool>()) throw std::runtime_error("Tensor must be contiguous");
-    if (obj.attr("device").attr("type").cast<std::string>() == "cpu") throw std::runtime_error("Tensor must be on CUDA device");
+    if (!obj.attr("is_cuda").cast<bool>()) throw std::runtime_error("Tensor must be on CUDA device");
     TensorView v{};
     v.shape = {1, 1, 1, 1};
     auto shp = obj.attr("shape").cast<py::tuple>();
@@ -35,17 +59,31 @@ TensorView view_of(const py::object& obj) {
     if (dims > 4) throw std::runtime_error("Expected Tensor.ndim <= 4");
     for (size_t i = 0; i < dims; ++i) v.shape[4 - dims + i] = py::cast<int64_t>(shp[i]);
     v.ptr = obj.attr("data_ptr")().cast<uint64_t>();
-    v.dtype = py::str(obj.attr("dtype")).cast<std::string>();
-    py::object idx = obj.attr("device").attr("index");
-    v.device = idx.is_none() ? 0 : idx.cast<int>();
+    const TorchHandles& h = handles();
+    py::object dt = obj.attr("dtype");
+    v.dtype = dt.is(h.u8) ? DType::U8 : dt.is(h.bf16) ? DType::BF16 : DType::Other;
+    v.device = obj.attr("get_device")().cast<int>();
     return v;
 }
 
+// Makes `device` current for the lifetime of the object and restores the previous one.
+struct DeviceGuard {
+    int prev = -1, changed = 0;
+    explicit DeviceGuard(int device) {
+        if (cudaGetDevice(&prev) != cudaSuccess) throw std::runtime_error("cudaGetDevice failed");
+        if (prev != device) {
+            if (cudaSetDevice(device) != cudaSuccess) throw std::runtime_error("cudaSetDevice failed");
+            changed = 1;
+        }
+    }
+    ~DeviceGuard() { if (changed) cudaSetDevice(prev); }
+};
+
 void dispatch_micro(py::object A, py::object B, py::object C, py::object scale_A, py::object scale_B, int fmt) {
     const TensorView a = view_of(A), b = view_of(B), c = view_of(C), sa = view_of(scale_A), sb = view_of(scale_B);
-    if (a.dtype != "torch.uint8" || b.dtype != "torch.uint8") throw std::runtime_error("A and B must be packed fp6 as torch.uint8");
-    if (sa.dtype != "torch.uint8" || sb.dtype != "torch.uint8") throw std::runtime_error("scales must be E8M0 bytes as torch.uint8");
-    if (c.dtype != "torch.bfloat16") throw std::runtime_error("C must be torch.bfloat16");
+    if (a.dtype != DType::U8 || b.dtype != DType::U8) throw std::runtime_error("A and B must be packed fp6 as torch.uint8");
+    if (sa.dtype != DType::U8 || sb.dtype != DType::U8) throw std::runtime_error("scales must be E8M0 bytes as torch.uint8");
+    if (c.dtype != DType::BF16) throw std::runtime_error("C must be torch.bfloat16");
     for (const TensorView* t : {&a, &b, &c, &sa, &sb})
         if (t->shape[0] != 1 || t->shape[1] != 1) throw std::runtime_error("Expected 2-D tensors");
     // M from A, N from C, K from A -- the reference's rule (256_256_64_32_with16x32.cpp:52-54)
@@ -63,20 +101,14 @@ void dispatch_micro(py::object A, py::object B, py::object C, py::object scale_A
     if (fmt < 0 || fmt > 3) throw std::runtime_error("fmt must be 0 (E2M3), 1 (E3M2), 2 (fp8 E4M3) or 3 (fp8 E5M2)");
 
     // launch on torch's current stream of the tensors' device, with that device current
-    py::module_ cuda = py::module_::import("torch").attr("cuda");
-    py::object guard = cuda.attr("device")(a.device);
-    guard.attr("__enter__")();
     int rc;
-    try {
-        const uint64_t stream = cuda.attr("current_stream")().attr("cuda_stream").cast<uint64_t>();
+    {
+        DeviceGuard guard(a.device);
+        const uint64_t stream = handles().current_stream(a.device);
         rc = mxfp6_gemm(reinterpret_cast<const void*>(a.ptr), reinterpret_cast<const void*>(sa.ptr),
                         reinterpret_cast<const void*>(b.ptr), reinterpret_cast<const void*>(sb.ptr),
                         reinterpret_cast<void*>(c.ptr), M, N, K, fmt, fmt, reinterpret_cast<void*>(stream));
-    } catch (...) {
-        guard.attr("__exit__")(py::none(), py::none(), py::none());
-        throw;
     }
-    guard.attr("__exit__")(py::none(), py::none(), py::none());
     if (rc != MXFP6_OK) throw std::runtime_error(std::string("mxfp6_gemm failed: ") + mxfp6_last_error());
 }
 

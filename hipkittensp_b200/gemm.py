@@ -38,8 +38,32 @@ def _k_of(t, fmt: int, name: str) -> int:
     return t.shape[1] // 3 * 4
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream_ptr() -> int:
+    """Handle of torch's current stream on the current device."""
+    if _raw_stream is not None:
+        return _raw_stream(torch.cuda.current_device())
     return torch.cuda.current_stream().cuda_stream
+
+
+class _NoGuard:
+    def __enter__(self):
+        return None
+
+    def __exit__(self, *exc):
+        return False
+
+
+_NO_GUARD = _NoGuard()
+
+
+def _on_device_of(t):
+    """Context that makes t's device current; free when it already is (the common case)."""
+    if t.device.index == torch.cuda.current_device():
+        return _NO_GUARD
+    return torch.cuda.device(t.device)
 
 
 def dispatch_micro(A, B, C, scale_A, scale_B, fmt: int = E2M3, fmt_b: int | None = None, b_static: bool = False) -> None:
@@ -68,7 +92,7 @@ def dispatch_micro(A, B, C, scale_A, scale_B, fmt: int = E2M3, fmt_b: int | None
         raise RuntimeError("scales must be [rows, K/32]")
     if len({t.device for t in (A, B, C, scale_A, scale_B)}) != 1:
         raise RuntimeError("all tensors must be on the same device")
-    with torch.cuda.device(A.device):
+    with _on_device_of(A):
         check(lib.mxfp6_gemm_ex(A.data_ptr(), scale_A.data_ptr(), B.data_ptr(), scale_B.data_ptr(), C.data_ptr(),
                                 M, N, K, fmt, fb, _lib.FLAG_B_STATIC if b_static else 0, _stream_ptr()))
 
@@ -95,7 +119,7 @@ def dispatch_multi(A, B, dests, col_offset: int, scale_A, scale_B, fmt: int = E2
         if col_offset < 0 or col_offset + N > d.shape[1]:
             raise RuntimeError("column window outside the destination")
     ptrs = (ctypes.c_void_p * len(dests))(*[d.data_ptr() + 2 * col_offset for d in dests])
-    with torch.cuda.device(A.device):
+    with _on_device_of(A):
         check(lib.mxfp6_gemm_multi(A.data_ptr(), scale_A.data_ptr(), B.data_ptr(), scale_B.data_ptr(), ptrs, len(dests),
                                    ldc, M, N, K, fmt, fmt, _stream_ptr()))
 
@@ -115,7 +139,7 @@ def gemm_requant(A, scale_A, B, scale_B, fmt: int = E2M3, fmt_b: int | None = No
         raise RuntimeError("N must be a multiple of 64")
     out = torch.empty((M, N if out_fmt in (E4M3, E5M2) else N * 3 // 4), dtype=torch.uint8, device=A.device)
     scales = torch.empty((M, N // 32), dtype=torch.uint8, device=A.device)
-    with torch.cuda.device(A.device):
+    with _on_device_of(A):
         check(lib.mxfp6_gemm_requant(A.data_ptr(), scale_A.data_ptr(), B.data_ptr(), scale_B.data_ptr(), out.data_ptr(),
                                      scales.data_ptr(), M, N, K, fmt, fb, out_fmt, _stream_ptr()))
     return out, scales
@@ -148,7 +172,7 @@ def gemm_scaled(A, scale_A, B, scale_B, row_scale=None, col_scale=None, bias=Non
     if tuple(out.shape) != (M, N):
         raise RuntimeError(f"C must be [{M}, {N}]")
     ptr = lambda v: 0 if v is None else v.data_ptr()
-    with torch.cuda.device(A.device):
+    with _on_device_of(A):
         check(lib.mxfp6_gemm_scaled(A.data_ptr(), scale_A.data_ptr(), B.data_ptr(), scale_B.data_ptr(), out.data_ptr(),
                                     ptr(row_scale), ptr(col_scale), ptr(bias), M, N, K, fmt, fb, _stream_ptr()))
     return out
@@ -174,7 +198,7 @@ def quantize(x: torch.Tensor, fmt: int = E2M3):
         raise RuntimeError("K must be a multiple of 32")
     packed = torch.empty((rows, K if fmt in (E4M3, E5M2) else K * 3 // 4), dtype=torch.uint8, device=x.device)
     scales = torch.empty((rows, K // 32), dtype=torch.uint8, device=x.device)
-    with torch.cuda.device(x.device):
+    with _on_device_of(x):
         check(lib.mxfp6_quantize(x.data_ptr(), 0 if x.dtype == torch.float32 else 1, rows, K, fmt,
                                  packed.data_ptr(), scales.data_ptr(), _stream_ptr()))
     return packed, scales
@@ -186,7 +210,7 @@ def dequantize(packed: torch.Tensor, scales: torch.Tensor, fmt: int = E2M3) -> t
     _accept(scales, "scales", torch.uint8)
     rows, K = packed.shape[0], _k_of(packed, fmt, "packed")
     out = torch.empty((rows, K), dtype=torch.float32, device=packed.device)
-    with torch.cuda.device(packed.device):
+    with _on_device_of(packed):
         check(lib.mxfp6_dequantize(packed.data_ptr(), scales.data_ptr(), rows, K, fmt, out.data_ptr(), _stream_ptr()))
     return out
 
@@ -204,6 +228,6 @@ def tma_dump(packed: torch.Tensor, row0: int = 0, k0: int = 0) -> torch.Tensor:
     """Diagnostic: the 16 KiB shared-memory image of one 128x128 operand box as the GEMM loads it."""
     rows, K = packed.shape[0], packed.shape[1] // 3 * 4
     out = torch.empty(16384, dtype=torch.uint8, device=packed.device)
-    with torch.cuda.device(packed.device):
+    with _on_device_of(packed):
         check(lib.mxfp6_debug_tma_dump(packed.data_ptr(), rows, K, row0, k0, out.data_ptr(), _stream_ptr()))
     return out

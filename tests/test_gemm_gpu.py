@@ -362,3 +362,13 @@ def test_scaled_epilogue_argument_checks():
         hk.gemm_scaled(pa, sa, pb, sb, torch.ones(64, device="cuda"))
     with pytest.raises(RuntimeError, match="fp32"):
         hk.gemm_scaled(pa, sa, pb, sb, None, torch.ones(128, device="cuda", dtype=torch.bfloat16))
+
+
+# ------------------------------------------------------------------------------- reference-style harness
+def test_reference_style_harness_runs_and_checks(capsys):
+    from hipkittensp_b200 import harness
+    harness.check_gemm((256, 384, 512))
+    harness.check_gemm((16, 1024, 1024), fmt=R.E3M2)
+    tf = harness.bench_gemm({"shape": (512, 512, 512)}, None, num_warmup=3, num_iter=3)
+    assert tf > 0
+    assert "m=512,n=512,k=512:" in capsys.readouterr().out
