@@ -617,41 +617,68 @@ mxfp6_gemm_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constan
                 asm volatile("bar.sync 1, 128;" ::: "memory");
                 if (last) {
                     __threadfence();
-                    const float* base = P.ws_partial + (size_t)sg.tile * P.ws_slots * (size_t)(BN * 128) + prow;
-                    // FC columns at a time: the loads of a chunk are independent and in flight together; each
-                    // element is still summed in slot order
-                    constexpr int FC = BN >= 16 ? 16 : BN;
+                    // Each thread sums 4 consecutive rows (one 16-byte load per slot) of every fourth column: JB columns
+                    // at a time, their loads independent and in flight together; each element is still summed in slot
+                    // order starting from zero, so the result does not depend on which CTA does the summing.
+                    const int r4 = 4 * lane;                         // first of this thread's 4 rows
+                    const float* base = P.ws_partial + (size_t)sg.tile * P.ws_slots * (size_t)(BN * 128) + r4;
+                    constexpr int NJ = BN / 4;                       // columns per thread: quad + 4 * j
+                    constexpr int JB = NJ >= 8 ? 8 : NJ;
+                    const int pr = sg.p0 + r4;
 #pragma unroll 1
-                    for (int col0 = 0; col0 < BN; col0 += FC) {
-                        float acc[FC];
-#pragma unroll
-                        for (int j = 0; j < FC; ++j) acc[j] = 0.f;
+                    for (int j0 = 0; j0 < NJ; j0 += JB) {
+                        float4 acc[JB];
                         if (sg.nseg == 2) {                       // the common case: both slots fetched at once
-                            float t0[FC], t1[FC];
+                            float4 t0[JB], t1[JB];
 #pragma unroll
-                            for (int j = 0; j < FC; ++j) {
-                                t0[j] = __ldcg(base + (size_t)(col0 + j) * 128);
-                                t1[j] = __ldcg(base + (size_t)(BN * 128) + (size_t)(col0 + j) * 128);
+                            for (int j = 0; j < JB; ++j) {
+                                const float* src = base + (size_t)(quad + 4 * (j0 + j)) * 128;
+                                t0[j] = __ldcg(reinterpret_cast<const float4*>(src));
+                                t1[j] = __ldcg(reinterpret_cast<const float4*>(src + (size_t)(BN * 128)));
                             }
 #pragma unroll
-                            for (int j = 0; j < FC; ++j) acc[j] = (0.f + t0[j]) + t1[j];
+                            for (int j = 0; j < JB; ++j)
+                                acc[j] = make_float4((0.f + t0[j].x) + t1[j].x, (0.f + t0[j].y) + t1[j].y,
+                                                     (0.f + t0[j].z) + t1[j].z, (0.f + t0[j].w) + t1[j].w);
                         } else {
+#pragma unroll
+                            for (int j = 0; j < JB; ++j) acc[j] = make_float4(0.f, 0.f, 0.f, 0.f);
                             for (int sgi = 0; sgi < sg.nseg; ++sgi) {
-                                float t[FC];
+                                float4 t[JB];
 #pragma unroll
-                                for (int j = 0; j < FC; ++j) t[j] = __ldcg(base + (size_t)sgi * (BN * 128) + (size_t)(col0 + j) * 128);
+                                for (int j = 0; j < JB; ++j)
+                                    t[j] = __ldcg(reinterpret_cast<const float4*>(base + (size_t)sgi * (BN * 128) + (size_t)(quad + 4 * (j0 + j)) * 128));
 #pragma unroll
-                                for (int j = 0; j < FC; ++j) acc[j] += t[j];
+                                for (int j = 0; j < JB; ++j) { acc[j].x += t[j].x; acc[j].y += t[j].y; acc[j].z += t[j].z; acc[j].w += t[j].w; }
                             }
                         }
 #pragma unroll
-                        for (int j = 0; j < FC; ++j) {
-                            const int q = sg.q0 + col0 + j;
-                            if (affine) acc[j] = affine_one<Cfg::SWAP>(P, acc[j], p, q);
+                        for (int j = 0; j < JB; ++j) {
+                            const int q = sg.q0 + quad + 4 * (j0 + j);
+                            float x[4] = {acc[j].x, acc[j].y, acc[j].z, acc[j].w};
+                            if (affine) {
+#pragma unroll
+                                for (int e = 0; e < 4; ++e) x[e] = affine_one<Cfg::SWAP>(P, x[e], pr + e, q);
+                            }
                             if (Cfg::SWAP) {
-                                if (p < P.c_cols && q < P.c_rows) P.c[(size_t)q * P.ldc + p] = __float2bfloat16_rn(acc[j]);
-                            } else {
-                                if (p < P.c_rows && q < P.c_cols) P.c[(size_t)p * P.ldc + q] = __float2bfloat16_rn(acc[j]);
+                                // D[p,q] -> C[q,p]: the 4 rows are 4 consecutive bf16 of C's row q
+                                if (q < P.c_rows) {
+                                    __nv_bfloat16* dst = P.c + (size_t)q * P.ldc + pr;
+                                    if (pr + 3 < P.c_cols && (reinterpret_cast<uintptr_t>(dst) & 7) == 0) {
+                                        uint2 o;
+                                        o.x = pack_bf16x2(x[0], x[1]);
+                                        o.y = pack_bf16x2(x[2], x[3]);
+                                        *reinterpret_cast<uint2*>(dst) = o;
+                                    } else {
+#pragma unroll
+                                        for (int e = 0; e < 4; ++e)
+                                            if (pr + e < P.c_cols) dst[e] = __float2bfloat16_rn(x[e]);
+                                    }
+                                }
+                            } else if (q < P.c_cols) {
+#pragma unroll
+                                for (int e = 0; e < 4; ++e)
+                                    if (pr + e < P.c_rows) P.c[(size_t)(pr + e) * P.ldc + q] = __float2bfloat16_rn(x[e]);
                             }
                         }
                     }

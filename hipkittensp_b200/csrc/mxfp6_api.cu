@@ -172,9 +172,8 @@ static Plan make_plan(int64_t M, int64_t N, int64_t K, int sm_count, bool allow_
     if (M <= 128 && N > M && !plain) {      // plain: whole tiles, C stored untransposed (several destinations)
         p.swap = true;
         p.bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : 128;
-        // K-split work units balance the SMs; with 128-wide accumulators the fix-up of split tiles costs more
-        // than the imbalance it removes
-        p.streamk = p.bn <= 64 && (int64_t)ceil_div(N, 128) <= kMaxSplitTiles;
+        // K-split work units balance the SMs
+        p.streamk = (int64_t)ceil_div(N, 128) <= kMaxSplitTiles;
     } else {
         p.swap = false; p.streamk = false;
         const int64_t t256 = (int64_t)ceil_div(M, 128) * ceil_div(N, 256);
