@@ -31,20 +31,17 @@ struct PairCfg {
     static constexpr int P_BYTES = BM * BK;               // 16 KB
     static constexpr int Q_BYTES = (BN / 2) * BK;         // 16 KB: this CTA's half of B
     static constexpr int STAGE_BYTES = P_BYTES + Q_BYTES;
-#ifndef MXFP6_PAIR_STAGES
-#define MXFP6_PAIR_STAGES 5
-#endif
-    static constexpr int STAGES = MXFP6_PAIR_STAGES;
-    // output staging: with 5 stages two buffers of 128 rows x 64 columns (128-byte swizzle); with 6 stages one
-    // buffer of 128 x 32 columns (64-byte swizzle) is what still fits
-    static constexpr int OUT_COLS = STAGES >= 6 ? 32 : 64;
-    static constexpr int OUT_BUFS = STAGES >= 6 ? 1 : 2;
+    // 5 stages of 32 KB; a sixth (paid for with a single 8 KB staging buffer and two scale-atom groups) measured
+    // no faster: throughput rises from 3 to 4 to 5 stages and is flat beyond
+    static constexpr int STAGES = 5;
+    static constexpr int OUT_COLS = 64;                   // output staging: two buffers of 128 rows x 64 columns
+    static constexpr int OUT_BUFS = 2;
     static constexpr int OUT_BYTES = BM * OUT_COLS * 2;
     static constexpr int RAW_SLOTS = 2;
     static constexpr int RAW_BYTES = (BM + BN) * 16;      // own P rows + all 256 Q rows, 16 scale bytes each
     static constexpr int ATOM_BYTES = 512 * 3;            // P atom + two Q atoms of one K-block
     static constexpr int GROUP_BYTES = 4 * ATOM_BYTES;    // the 4 K-blocks one raw slab covers
-    static constexpr int ATOM_GROUPS = STAGES >= 6 ? 2 : 3;
+    static constexpr int ATOM_GROUPS = 3;
     static constexpr int ACC_COL1 = 224;
     static constexpr int SF_COL = 480;
     static constexpr int TMEM_COLS = 512;
@@ -335,10 +332,11 @@ mxfp6_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_co
                 // the stores that last used this staging buffer have finished reading it
                 if (etid == 0) bulk_wait_group_read<Cfg::OUT_BUFS - 1>();
                 asm volatile("bar.sync 1, 128;" ::: "memory");
-                // row prow of the piece = OC*2 bytes in 16-byte chunks; chunk c is stored at c ^ (row % 8) (128-byte
-                // swizzle, 64 columns) or c ^ ((row / 2) % 4) (64-byte swizzle, 32 columns), as the TMA store expects
+                // row prow of the piece = 128 bytes in 16-byte chunks; chunk c is stored at c ^ (row % 8), the
+                // 128-byte swizzle the TMA store expects
+                static_assert(OC == 64, "the staging layout below is the 128-byte swizzle of 64 bf16 columns");
                 const uint32_t rowaddr = buf + prow * (OC * 2);
-                const uint32_t sw = OC == 64 ? (uint32_t)(prow & 7) : (uint32_t)((prow >> 1) & 3);
+                const uint32_t sw = (uint32_t)(prow & 7);
 #pragma unroll
                 for (int c = 0; c < OC / 8; ++c) {
                     const uint32_t x0 = pack_bf16x2(__uint_as_float(v[8 * c + 0]), __uint_as_float(v[8 * c + 1]));

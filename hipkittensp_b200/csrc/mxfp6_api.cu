@@ -110,7 +110,6 @@ static std::map<MapKey, CUtensorMap> g_maps;
 // kind 1: scale bytes [rows, K/32] (inner = K/32 bytes), box 16 x box_rows, no swizzle
 // kind 3: fp8 operand [rows, K] (inner = K bytes), box 128 x box_rows, 128-byte swizzle
 // kind 2: bf16 output block [rows, inner] with a row stride of stride_bytes, box 64 x box_rows, 128-byte swizzle
-// kind 4: the same with box 32 x box_rows and the 64-byte swizzle
 static int make_map(const void* ptr, int64_t rows, int64_t inner, int box_rows, int kind, CUtensorMap* out,
                     int64_t stride_bytes = 0) {
     MapKey key{ptr, rows, inner, stride_bytes, box_rows, kind};
@@ -122,14 +121,14 @@ static int make_map(const void* ptr, int64_t rows, int64_t inner, int box_rows, 
     int rc = get_encode_fn();
     if (rc) return rc;
     cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)rows};
-    cuuint64_t strides[1] = {(cuuint64_t)(kind == 0 ? inner * 3 / 4 : (kind == 2 || kind == 4) ? stride_bytes : inner)};
-    cuuint32_t box[2] = {(cuuint32_t)(kind == 1 ? 16 : kind == 2 ? 64 : kind == 4 ? 32 : 128), (cuuint32_t)box_rows};
+    cuuint64_t strides[1] = {(cuuint64_t)(kind == 0 ? inner * 3 / 4 : kind == 2 ? stride_bytes : inner)};
+    cuuint32_t box[2] = {(cuuint32_t)(kind == 1 ? 16 : kind == 2 ? 64 : 128), (cuuint32_t)box_rows};
     cuuint32_t estr[2] = {1, 1};
     const CUtensorMapDataType dt = kind == 0 ? CU_TENSOR_MAP_DATA_TYPE_16U6_ALIGN16B
-                                 : (kind == 2 || kind == 4) ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+                                 : kind == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
     CUresult r = g_encode(out, dt, 2,
                           const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                          kind == 1 ? CU_TENSOR_MAP_SWIZZLE_NONE : kind == 4 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B,
+                          kind == 1 ? CU_TENSOR_MAP_SWIZZLE_NONE : CU_TENSOR_MAP_SWIZZLE_128B,
                           CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS)
         return fail(MXFP6_ERR_CUDA, "cuTensorMapEncodeTiled(kind=%d rows=%lld inner=%lld box_rows=%d) failed with %d",
@@ -382,7 +381,7 @@ static int gemm_impl(const void* a, const void* sfa, const void* b, const void* 
         CMaps cm;
         for (int i = 0; i < 8; ++i) {
             if (i >= dst.n) { cm.m[i] = cm.m[0]; continue; }     // unused slots hold a valid map all the same
-            if ((rc = make_map(dst.c[i], M, N, 128, PairCfg::OUT_COLS == 64 ? 2 : 4, &cm.m[i], dst.ldc * 2))) return rc;
+            if ((rc = make_map(dst.c[i], M, N, 128, 2, &cm.m[i], dst.ldc * 2))) return rc;
         }
         cudaLaunchAttribute attr{};
         cudaLaunchConfig_t lc = launch_config(pl.grid, PairCfg::THREADS, PairCfg::SMEM_ALLOC, st, &attr);
