@@ -372,3 +372,29 @@ def test_reference_style_harness_runs_and_checks(capsys):
     tf = harness.bench_gemm({"shape": (512, 512, 512)}, None, num_warmup=3, num_iter=3)
     assert tf > 0
     assert "m=512,n=512,k=512:" in capsys.readouterr().out
+
+
+# ------------------------------------------------------------------------------- CUDA graph capture
+@pytest.mark.parametrize("shape", [(256, 512, 512), (16, 2048, 2048), (512, 768, 1024)])
+def test_calls_can_be_captured_in_a_cuda_graph(shape):
+    """After one eager call (one-time set-up: attributes, scratch), the launch is plain stream work: capture it,
+    replay it on new operand contents, and compare with an eager call."""
+    M, N, K = shape
+    pa, sa, pb, sb = [torch.from_numpy(x).cuda() for x in quantized_inputs("normal", M, N, K, seed=5)]
+    C = torch.empty((M, N), dtype=torch.bfloat16, device="cuda")
+    hk.dispatch_micro(pa, pb, C, sa, sb, R.E2M3)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        hk.dispatch_micro(pa, pb, C, sa, sb, R.E2M3)
+    # new contents in the same buffers
+    qa, ta, qb, tb = [torch.from_numpy(x).cuda() for x in quantized_inputs("normal", M, N, K, seed=6)]
+    pa.copy_(qa); sa.copy_(ta); pb.copy_(qb); sb.copy_(tb)
+    C.fill_(float("nan"))
+    g.replay()
+    g.replay()
+    torch.cuda.synchronize()
+    want = torch.empty_like(C)
+    hk.dispatch_micro(pa, pb, want, sa, sb, R.E2M3)
+    assert hk.device_status() == 0
+    assert torch.equal(C, want)
