@@ -92,3 +92,49 @@ def test_config_sharded_one_shard():
     C = _gpu(pa, sa, pb, sb, R.E2M3)
     rows = np.sort(np.random.default_rng(3).choice(M, 32, replace=False))
     _check_rows(C, pa, sa, pb, sb, R.E2M3, rows)
+
+
+# ------------------------------------------------------------------------------- size-independent properties
+def _flip_signs_fp6(packed: torch.Tensor) -> torch.Tensor:
+    """Negates every element of a packed fp6 operand: the sign is bit 5 of each 6-bit code, i.e. bits 5, 11, 17, 23
+    of every 3-byte group."""
+    mask = torch.tensor([0x20, 0x08, 0x82], dtype=torch.uint8, device=packed.device).repeat(packed.shape[1] // 3)
+    return packed ^ mask
+
+
+def test_full_size_exact_properties_8192_cubed():
+    """Properties that hold bit for bit whatever the size, checked on the whole 8192 x 8192 result:
+    a scale byte + 1 on every block of A doubles C exactly; negating A negates C; permuting the rows of A permutes
+    the rows of C; a block of B's rows gives the matching block of C's columns."""
+    M = N = K = 8192
+    pa, sa, pb, sb = (torch.from_numpy(x).cuda() for x in _quantized("lognormal", M, N, K, R.E2M3, seed=1))
+    C = hk.gemm(pa, sa, pb, sb, R.E2M3)
+    assert hk.device_status() == 0
+    assert int(sa.max()) < 254
+    C2 = hk.gemm(pa, sa + 1, pb, sb, R.E2M3)
+    assert torch.equal(C2.float(), 2.0 * C.float())
+    Cn = hk.gemm(_flip_signs_fp6(pa), sa, pb, sb, R.E2M3)
+    assert torch.equal(Cn.float(), -C.float())
+    perm = torch.randperm(M, device="cuda", generator=torch.Generator(device="cuda").manual_seed(3))
+    Cp = hk.gemm(pa[perm].contiguous(), sa[perm].contiguous(), pb, sb, R.E2M3)
+    assert torch.equal(Cp, C[perm])
+    lo, hi = 2048, 6144
+    Cb = hk.gemm(pa, sa, pb[lo:hi].contiguous(), sb[lo:hi].contiguous(), R.E2M3)
+    assert torch.equal(Cb, C[:, lo:hi])
+    assert hk.device_status() == 0
+
+
+def test_full_size_exact_properties_decode():
+    """The same properties on the K-split kernel (M=16, N=28672, K=8192), whose split tiles are summed in a fixed order."""
+    M, N, K = 16, 28672, 8192
+    pa, sa, pb, sb = (torch.from_numpy(x).cuda() for x in _quantized("decode", M, N, K, R.E2M3, seed=2))
+    C = hk.gemm(pa, sa, pb, sb, R.E2M3)
+    assert int(sb.max()) < 254
+    C2 = hk.gemm(pa, sa, pb, sb + 1, R.E2M3)
+    assert torch.equal(C2.float(), 2.0 * C.float())
+    Cn = hk.gemm(pa, sa, _flip_signs_fp6(pb), sb, R.E2M3)
+    assert torch.equal(Cn.float(), -C.float())
+    perm = torch.randperm(M, device="cuda", generator=torch.Generator(device="cuda").manual_seed(4))
+    Cp = hk.gemm(pa[perm].contiguous(), sa[perm].contiguous(), pb, sb, R.E2M3)
+    assert torch.equal(Cp, C[perm])
+    assert hk.device_status() == 0
