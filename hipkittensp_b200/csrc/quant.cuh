@@ -28,8 +28,11 @@ __device__ __forceinline__ uint32_t cvt_pair(float x0, float x1) {
 template <int FMT>
 __device__ __forceinline__ uint32_t cvt_quad(float x0, float x1, float x2, float x3) {
     const uint32_t lo = cvt_pair<FMT>(x0, x1), hi = cvt_pair<FMT>(x2, x3);
-    if constexpr (FMT == kE4M3 || FMT == kE5M2) return lo | (hi << 16);
-    else return (lo & 63u) | ((lo >> 8) << 6) | ((hi & 63u) << 12) | ((hi >> 8) << 18);
+    const uint32_t t = lo | (hi << 16);                   // one code per byte
+    if constexpr (FMT == kE4M3 || FMT == kE5M2) return t;
+    // four 6-bit fields at bit 0, 8, 16, 24 -> bit 0, 6, 12, 18: first within each half, then the halves
+    const uint32_t u = (t & 0x003f003fu) | ((t >> 2) & 0x0fc00fc0u);
+    return (u & 0xfffu) | ((u >> 4) & 0xfff000u);
 }
 
 // E8M0 byte of a block whose largest magnitude is amax
@@ -52,17 +55,18 @@ __device__ __forceinline__ int quant_block32(const float* v, uint32_t* out) {
     for (int i = 0; i < 32; ++i) amax = fmaxf(amax, fabsf(v[i]));
     const int sb = quant_scale_byte(amax, FMT);
     const int e = sb - 127;
-    const int h = (-e) / 2;          // 2^-e applied in two exact steps that stay inside fp32
-    const float f1 = __uint_as_float((uint32_t)(h + 127) << 23), f2 = __uint_as_float((uint32_t)(-e - h + 127) << 23);
+    // 2^-e, -127 <= -e <= 127, is an fp32 value (2^-127 a subnormal one) and the product with an element of the
+    // block is exact: |x| * 2^-e < 2^(emax+1)
+    const float f = e == 127 ? __uint_as_float(0x00400000u) : __uint_as_float((uint32_t)(127 - e) << 23);
     if constexpr (FMT == kE4M3 || FMT == kE5M2) {
 #pragma unroll
         for (int g = 0; g < 8; ++g)
-            out[g] = cvt_quad<FMT>(v[4 * g] * f1 * f2, v[4 * g + 1] * f1 * f2, v[4 * g + 2] * f1 * f2, v[4 * g + 3] * f1 * f2);
+            out[g] = cvt_quad<FMT>(v[4 * g] * f, v[4 * g + 1] * f, v[4 * g + 2] * f, v[4 * g + 3] * f);
     } else {
         uint32_t w24[8];
 #pragma unroll
         for (int g = 0; g < 8; ++g)
-            w24[g] = cvt_quad<FMT>(v[4 * g] * f1 * f2, v[4 * g + 1] * f1 * f2, v[4 * g + 2] * f1 * f2, v[4 * g + 3] * f1 * f2);
+            w24[g] = cvt_quad<FMT>(v[4 * g] * f, v[4 * g + 1] * f, v[4 * g + 2] * f, v[4 * g + 3] * f);
 #pragma unroll
         for (int h4 = 0; h4 < 2; ++h4) {      // 4 x 24 bits -> 3 words, twice
             const uint32_t* q = w24 + 4 * h4;

@@ -11,6 +11,7 @@ with the CPU oracle).
 
     python -m hipkittensp_b200.harness                 # the reference's shape list, E2M3
     python -m hipkittensp_b200.harness --check         # asserting run on a few shapes
+    python -m hipkittensp_b200.harness --quantize      # GB/s of the block quantiser
 """
 from __future__ import annotations
 
@@ -95,15 +96,44 @@ def check_gemm(shape, fmt: int = F.E2M3, device="cuda:0", rel_tol: float = 1e-2)
     return err
 
 
+def bench_quantize(rows: int = 8192, K: int = 8192, fmt: int = F.E2M3, device="cuda:0", iters: int = 20) -> dict:
+    """GB/s of the block quantiser (the step in front of the GEMM) for fp32 and bf16 sources: algorithmic bytes
+    (source read once, codes and scale bytes written once) over the mean time of `iters` back-to-back launches."""
+    out = {}
+    for name, dtype in (("fp32", torch.float32), ("bf16", torch.bfloat16)):
+        x = torch.randn((rows, K), dtype=torch.float32, device=device).to(dtype)
+        for _ in range(3):
+            p, s = quantize(x, fmt)
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        start.record()
+        for _ in range(iters):
+            p, s = quantize(x, fmt)
+        end.record()
+        torch.cuda.synchronize()
+        us = start.elapsed_time(end) / iters * 1e3
+        nbytes = x.numel() * x.element_size() + p.numel() + s.numel()
+        out[name] = nbytes / us / 1e3
+        print(f"quantize {name} [{rows},{K}] -> fmt {fmt}: {us:.1f} us, {out[name]:.0f} GB/s")
+    if device_status() != 0:
+        raise RuntimeError("a kernel reported a device-side wait that ran out")
+    return out
+
+
 def main(argv=None) -> None:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--check", action="store_true", help="asserting run instead of the timing sweep")
+    ap.add_argument("--quantize", action="store_true", help="time the block quantiser instead of the GEMM")
     ap.add_argument("--fmt", choices=["e2m3", "e3m2", "e4m3", "e5m2"], default="e2m3")
     ap.add_argument("--warmup", type=int, default=500)
     ap.add_argument("--iters", type=int, default=500)
     args = ap.parse_args(argv)
     fmt = {"e2m3": F.E2M3, "e3m2": F.E3M2, "e4m3": F.E4M3, "e5m2": F.E5M2}[args.fmt]
     torch.manual_seed(0)
+    if args.quantize:
+        print_title(f"MX {args.fmt} block quantiser (B200)")
+        bench_quantize(fmt=fmt, iters=args.iters if args.iters != 500 else 20)
+        return
     if args.check:
         print_title(f"MX {args.fmt} GEMM check")
         for shape in [(1024, 1024, 1024), (130, 200, 256), (16, 4096, 2048), (2048, 2048, 2048)]:

@@ -6,7 +6,32 @@ import torch
 import hipkittensp_b200 as hk
 from oracle import mxfp6_ref as R
 
+import os
+
 pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(autouse=True, params=["stream", "quad"])
+def _quantiser_path(request):
+    """Every test runs on both quantiser kernels: the TMA-fed streaming kernel (default) and the plain-load kernel."""
+    if request.param == "quad":
+        os.environ["MXFP6_QUANT_PATH"] = "quad"
+    yield
+    os.environ.pop("MXFP6_QUANT_PATH", None)
+
+
+@pytest.mark.parametrize("fmt", [R.E2M3, R.E4M3])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("rows,K", [(1, 32), (5, 96), (3, 32 * 43), (129, 32), (2048, 4096), (1000, 2464)])
+def test_quantize_ragged_and_many_tiles(fmt, dtype, rows, K):
+    """Block counts that are not multiples of the 128-block tile (the tail takes plain stores), a single block, and
+    more tiles than resident CTAs (each CTA loops over its ring of stages several times)."""
+    x = torch.randn(rows, K, generator=torch.Generator().manual_seed(rows + K)).to(dtype)
+    pa, sa = R.c_quantize(np.ascontiguousarray(x.float().numpy()), fmt)
+    gp, gs = hk.quantize(x.cuda(), fmt)
+    assert hk.device_status() == 0
+    np.testing.assert_array_equal(gs.cpu().numpy(), sa)
+    np.testing.assert_array_equal(gp.cpu().numpy(), pa)
 
 
 @pytest.mark.parametrize("fmt", [R.E2M3, R.E3M2])
