@@ -710,8 +710,9 @@ extern "C" int mxfp6_quantize(const void* src, int src_dtype, int64_t rows, int6
                     d->smem_attr_set[(const void*)kern] = true;                                                      \
                 }                                                                                                    \
             }                                                                                                        \
-            kern<<<grid, QuantCfg<T, F>::THREADS, QuantCfg<T, F>::SMEM_ALLOC, st>>>(tm, (long long)nblk, (uint8_t*)packed, \
-                                                                                   (uint8_t*)scales, d->status, d->wait_cycles); \
+            cudaLaunchAttribute attr{};                                                                              \
+            cudaLaunchConfig_t lc = launch_config((int)grid, QuantCfg<T, F>::THREADS, QuantCfg<T, F>::SMEM_ALLOC, st, &attr); \
+            CUDA_TRY(cudaLaunchKernelEx(&lc, kern, tm, (long long)nblk, (uint8_t*)packed, (uint8_t*)scales, d->status, d->wait_cycles)); \
         } while (0)
         if (src_dtype == 0) {
             if (fmt == MXFP6_E2M3) QT(float, MXFP6_E2M3); else if (fmt == MXFP6_E3M2) QT(float, MXFP6_E3M2);

@@ -47,12 +47,27 @@ __device__ __forceinline__ int quant_scale_byte(float amax, int fmt) {
     return sb;
 }
 
-// v[0..31] (fp32) -> out[0..5] (fp6: 24 bytes) or out[0..7] (fp8: 32 bytes); returns the scale byte
-template <int FMT>
-__device__ __forceinline__ int quant_block32(const float* v, uint32_t* out) {
-    float amax = 0.f;
+// max(|a|, |b|, |c|) in one instruction (three-input max of sm_100)
+__device__ __forceinline__ float amax3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(fabsf(a)), "f"(fabsf(b)), "f"(fabsf(c)));
+    return d;
+}
+
+// largest magnitude of v[0..31]
+__device__ __forceinline__ float amax32(const float* v) {
+    float m[11];
 #pragma unroll
-    for (int i = 0; i < 32; ++i) amax = fmaxf(amax, fabsf(v[i]));
+    for (int i = 0; i < 10; ++i) m[i] = amax3(v[3 * i], v[3 * i + 1], v[3 * i + 2]);
+    m[10] = fmaxf(fabsf(v[30]), fabsf(v[31]));
+    const float a = amax3(m[0], m[1], m[2]), b = amax3(m[3], m[4], m[5]), c = amax3(m[6], m[7], m[8]);
+    return amax3(amax3(a, b, c), m[9], m[10]);
+}
+
+// v[0..31] (fp32) with largest magnitude amax -> out[0..5] (fp6: 24 bytes) or out[0..7] (fp8: 32 bytes); returns
+// the scale byte
+template <int FMT>
+__device__ __forceinline__ int quant_block32_amax(const float* v, float amax, uint32_t* out) {
     const int sb = quant_scale_byte(amax, FMT);
     const int e = sb - 127;
     // 2^-e, -127 <= -e <= 127, is an fp32 value (2^-127 a subnormal one) and the product with an element of the
@@ -76,6 +91,11 @@ __device__ __forceinline__ int quant_block32(const float* v, uint32_t* out) {
         }
     }
     return sb;
+}
+
+template <int FMT>
+__device__ __forceinline__ int quant_block32(const float* v, uint32_t* out) {
+    return quant_block32_amax<FMT>(v, amax32(v), out);
 }
 
 // Quantise 32 consecutive columns [col, col+32) of row `row` and store codes + scale.

@@ -88,6 +88,11 @@ quantize_tma_kernel(const __grid_constant__ CUtensorMap tm_src, long long n_bloc
         tma_prefetch_desc(&tm_src);
     }
     __syncthreads();
+    // launched with programmatic stream serialisation: everything above overlapped the end of the preceding kernel,
+    // nothing of global memory is touched before it has completed; the kernel after this one may likewise set
+    // itself up as soon as SMs become free (it waits for this grid's completion before its own first access)
+    pdl_launch_dependents();
+    pdl_wait();
 
     const long long n_tiles = (n_blocks + Cfg::TILE_BLOCKS - 1) / Cfg::TILE_BLOCKS;
     if (warp == 0) {
@@ -112,13 +117,13 @@ quantize_tma_kernel(const __grid_constant__ CUtensorMap tm_src, long long n_bloc
         // 768 / 1024 code bytes with one bulk copy from its own slice of the staging buffers.
         const int t = threadIdx.x - 32;
         const int cw = t >> 5;                               // consumer warp 0..3
-        uint32_t n = 0;
-        for (long long tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++n) {
-            const int s = n % Cfg::STAGES;
-            if (!__all_sync(0xffffffffu, quant_wait(bar_full(s), (n / Cfg::STAGES) & 1, abort_flag, status, wait_cycles,
+        uint32_t n = 0, s = 0, phase = 0;
+        for (long long tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++n, phase ^= (s + 1 == Cfg::STAGES), s = (s + 1 == Cfg::STAGES) ? 0 : s + 1) {
+            if (!__all_sync(0xffffffffu, quant_wait(bar_full(s), phase, abort_flag, status, wait_cycles,
                                                     kStatusTimeoutQuantData)))
                 break;
             float v[32];
+            float amax;
             const uint8_t* row = smem_gen + s * Cfg::IN_BYTES + t * Cfg::IN_ROW;
             if constexpr (sizeof(T) == 4) {
                 // 128-byte rows, 128-byte swizzle: 16-byte chunk c of row t sits at chunk c ^ (t % 8)
@@ -127,8 +132,10 @@ quantize_tma_kernel(const __grid_constant__ CUtensorMap tm_src, long long n_bloc
                     const float4 x = *reinterpret_cast<const float4*>(row + ((c ^ (t & 7)) << 4));
                     v[4 * c] = x.x; v[4 * c + 1] = x.y; v[4 * c + 2] = x.z; v[4 * c + 3] = x.w;
                 }
+                amax = amax32(v);
             } else {
                 // 64-byte rows, 64-byte swizzle: chunk c of row t sits at chunk c ^ ((t / 2) % 4)
+                __nv_bfloat162 m2;
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
                     const uint4 x = *reinterpret_cast<const uint4*>(row + ((c ^ ((t >> 1) & 3)) << 4));
@@ -137,14 +144,18 @@ quantize_tma_kernel(const __grid_constant__ CUtensorMap tm_src, long long n_bloc
                     for (int e = 0; e < 4; ++e) {
                         v[8 * c + 2 * e] = __uint_as_float(w[e] << 16);
                         v[8 * c + 2 * e + 1] = __uint_as_float(w[e] & 0xffff0000u);
+                        // the largest magnitude is found on the packed pairs (half-precision pipe, not the ALU)
+                        const __nv_bfloat162 a2 = __habs2(*reinterpret_cast<const __nv_bfloat162*>(&w[e]));
+                        m2 = (c == 0 && e == 0) ? a2 : __hmax2(m2, a2);
                     }
                 }
+                amax = fmaxf(__low2float(m2), __high2float(m2));
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_empty(s));       // this warp's part of the stage is in registers
 
             uint32_t w[8];
-            const int sb = quant_block32<FMT>(v, w);
+            const int sb = quant_block32_amax<FMT>(v, amax, w);
             const long long blk = tile * Cfg::TILE_BLOCKS + t;
             const bool whole = (tile + 1) * Cfg::TILE_BLOCKS <= n_blocks;
             if (blk < n_blocks) scales[blk] = (uint8_t)sb;   // 32 consecutive bytes per warp
