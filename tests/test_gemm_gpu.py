@@ -398,3 +398,19 @@ def test_calls_can_be_captured_in_a_cuda_graph(shape):
     hk.dispatch_micro(pa, pb, want, sa, sb, R.E2M3)
     assert hk.device_status() == 0
     assert torch.equal(C, want)
+
+
+# ------------------------------------------------------------------------------- empty dimensions
+def test_empty_dimensions():
+    """M = 0 or N = 0: nothing to do, success.  K = 0: an empty sum, C is written as zeros."""
+    dev = "cuda"
+    u8 = lambda r, c: torch.empty((r, c), dtype=torch.uint8, device=dev)
+    C = torch.full((8, 64), float("nan"), dtype=torch.bfloat16, device=dev)
+    hk.dispatch_micro(u8(8, 0), u8(64, 0), C, u8(8, 0), u8(64, 0), R.E2M3)          # K = 0
+    assert hk.device_status() == 0
+    assert torch.equal(C.float(), torch.zeros(8, 64, device=dev))
+    hk.dispatch_micro(u8(0, 96), u8(64, 96), torch.empty((0, 64), dtype=torch.bfloat16, device=dev), u8(0, 4), u8(64, 4), R.E2M3)   # M = 0
+    hk.dispatch_micro(u8(8, 96), u8(0, 96), torch.empty((8, 0), dtype=torch.bfloat16, device=dev), u8(8, 4), u8(0, 4), R.E2M3)     # N = 0
+    p, s = hk.quantize(torch.empty((0, 64), dtype=torch.float32, device=dev), R.E2M3)
+    assert p.shape == (0, 48) and s.shape == (0, 2)
+    assert hk.device_status() == 0
