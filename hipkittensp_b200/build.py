@@ -1,4 +1,5 @@
-"""In-tree build of the native parts: libmxfp6.so (CUDA kernels + C ABI, sm_100a) and the
+"""In-tree build of the native parts: libmxfp6.so (CUDA kernels + C ABI, sm_100a), the stand-alone C++ harness
+matmul_host, and the
 tk_kernel Python extension (pybind11, same module/function names as the reference's binding,
 include/pyutils/pyutils.cuh:55-72 and kernels/gemm/bf16fp32/Makefile:41,51-52).
 
@@ -71,8 +72,25 @@ def build_ext(force: bool = False) -> str:
     return EXT
 
 
+HOST = os.path.join(PKG, "matmul_host")
+
+
+def build_host(force: bool = False) -> str:
+    """The stand-alone C++ harness over the C ABI (counterpart of the reference's `matmul_host` programs)."""
+    src = os.path.join(CSRC, "matmul_host.cpp")
+    if not force and _newer(HOST, [src, LIB, os.path.join(ROOT, "include", "mxfp6.h")]):
+        return HOST
+    cuda_lib = os.path.join(CUDA_HOME, "lib64")
+    cmd = ["g++", "-O2", "-std=c++17", "-fopenmp", "-I", os.path.join(ROOT, "include"), "-I", os.path.join(CUDA_HOME, "include"),
+           src, "-o", HOST, "-L", PKG, "-lmxfp6", "-L", cuda_lib, "-lcudart", "-Wl,-rpath,$ORIGIN", "-Wl,-rpath," + cuda_lib]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if res.returncode != 0:
+        raise RuntimeError("g++ failed:\n" + res.stdout + res.stderr)
+    return HOST
+
+
 def build_all(force: bool = False, verbose: bool = False):
-    return build_lib(force, verbose), build_ext(force)
+    return build_lib(force, verbose), build_ext(force), build_host(force)
 
 
 if __name__ == "__main__":

@@ -75,3 +75,13 @@ def test_tk_kernel_module_matches_reference_names():
         tk_kernel.dispatch_micro(A.t(), A, C, S, S)
     with pytest.raises(RuntimeError, match="Expected a torch.Tensor"):
         tk_kernel.dispatch_micro(3, A, C, S, S)
+
+
+def test_cpp_host_harness_is_built_and_rejects_bad_arguments():
+    import subprocess
+
+    import hipkittensp_b200 as hk
+    exe = os.path.join(os.path.dirname(hk.__file__), "matmul_host")
+    assert os.path.exists(exe), "build it with `python hipkittensp_b200/build.py`"
+    res = subprocess.run([exe, "128", "128", "100"], capture_output=True, text=True, timeout=60)   # K not a multiple of 128
+    assert res.returncode == 2 and "usage" in res.stderr

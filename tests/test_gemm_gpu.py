@@ -414,3 +414,14 @@ def test_empty_dimensions():
     p, s = hk.quantize(torch.empty((0, 64), dtype=torch.float32, device=dev), R.E2M3)
     assert p.shape == (0, 48) and s.shape == (0, 2)
     assert hk.device_status() == 0
+
+
+# ------------------------------------------------------------------------------- C++ host harness over the C ABI
+@pytest.mark.parametrize("args", [["512", "768", "1024", "0", "5", "10", "8"], ["16", "2048", "1024", "1", "3", "5", "16"],
+                                  ["256", "256", "512", "2", "3", "5", "4"]])
+def test_cpp_host_harness(args):
+    import subprocess
+    exe = os.path.join(os.path.dirname(hk.__file__), "matmul_host")
+    res = subprocess.run([exe] + args, capture_output=True, text=True, timeout=300)
+    assert res.returncode == 0, res.stdout + res.stderr
+    assert "TFLOP/s" in res.stdout and res.stdout.strip().endswith("OK")
