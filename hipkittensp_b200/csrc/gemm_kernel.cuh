@@ -296,7 +296,7 @@ mxfp6_gemm_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constan
         for (int s = 0; s < Cfg::RAW_SLOTS; ++s) { mbar_init(bar_raw_full(s), 1); mbar_init(bar_raw_empty(s), 32); }
         for (int s = 0; s < Cfg::ATOM_GROUPS; ++s) { mbar_init(bar_atom_full(s), 32); mbar_init(bar_atom_empty(s), 1); }
         for (int b = 0; b < 2; ++b) { mbar_init(bar_acc_full(b), 1); mbar_init(bar_acc_empty(b), 128); }
-        mbar_init(bar_ovl, 128);
+        mbar_init(bar_ovl, 4);
         *abort_flag = 0;
         *ticket_slot = 0;
         fence_barrier_init();
@@ -561,7 +561,7 @@ mxfp6_gemm_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constan
                 if constexpr (CW == 32) tmem_ld_x32(tacc + ch * CW, reinterpret_cast<uint32_t(&)[32]>(v));
                 else tmem_ld_x16(tacc + ch * CW, reinterpret_cast<uint32_t(&)[16]>(v));
                 tmem_ld_wait();
-                if (Cfg::OVERLAP && ci == 0) { tc_fence_before(); mbar_arrive(bar_ovl); }
+                if (Cfg::OVERLAP && ci == 0) { tc_fence_before(); __syncwarp(); if (lane == 0) mbar_arrive(bar_ovl); }
                 if (!Cfg::OVERLAP && ci == NCH - 1) { tc_fence_before(); mbar_arrive(bar_acc_empty(b)); }
                 const int qc = sg.q0 + ch * CW;              // first D column of this chunk
                 if (!partial && affine) affine_chunk<Cfg::SWAP, CW>(P, v, p, qc);

@@ -15,10 +15,10 @@
 //   full[s]      even CTA   1 arrival (+ bytes of both CTAs' TMA loads)        waited by the MMA thread
 //   empty[s]     each CTA   1 arrival by multicast tcgen05.commit               waited by that CTA's producer
 //   raw_full/raw_empty[r]  each CTA, local scale-slab ring
-//   atom_full[g] even CTA   64 arrivals (scale warp lanes of both CTAs), one per group of 4 K-blocks
+//   atom_full[g] even CTA   2 arrivals (the scale warp of each CTA), one per group of 4 K-blocks
 //   atom_empty[g] each CTA  1 arrival by multicast commit
 //   acc_full[b]  each CTA   1 arrival by multicast commit                       waited by that CTA's epilogue
-//   ovl          even CTA   256 arrivals (epilogue threads of both CTAs)        waited by the MMA thread
+//   ovl          even CTA   8 arrivals (epilogue warps of both CTAs)             waited by the MMA thread
 #pragma once
 #include "gemm_kernel.cuh"
 
@@ -129,9 +129,9 @@ mxfp6_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_co
     if (threadIdx.x == 0) {
         for (int s = 0; s < Cfg::STAGES; ++s) { mbar_init(bar_full(s), 1); mbar_init(bar_empty(s), 1); }
         for (int s = 0; s < Cfg::RAW_SLOTS; ++s) { mbar_init(bar_raw_full(s), 1); mbar_init(bar_raw_empty(s), 32); }
-        for (int s = 0; s < Cfg::ATOM_GROUPS; ++s) { mbar_init(bar_atom_full(s), 64); mbar_init(bar_atom_empty(s), 1); }
+        for (int s = 0; s < Cfg::ATOM_GROUPS; ++s) { mbar_init(bar_atom_full(s), 2); mbar_init(bar_atom_empty(s), 1); }
         for (int b = 0; b < 2; ++b) mbar_init(bar_acc_full(b), 1);
-        mbar_init(bar_ovl, 256);
+        mbar_init(bar_ovl, 8);
         *abort_flag = 0;
         fence_barrier_init();
     }
@@ -278,7 +278,8 @@ mxfp6_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_co
                     *reinterpret_cast<uint4*>(atom + 1024 + lane * 16) = make_uint4(rq[4][jj], rq[5][jj], rq[6][jj], rq[7][jj]);
                 }
                 fence_proxy_async_smem();
-                mbar_arrive_cluster(mapa_shared(bar_atom_full(g), 0));
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(mapa_shared(bar_atom_full(g), 0));
             }
         }
         if (!ok && lane == 0) signal_abort_to_peer();
@@ -313,7 +314,12 @@ mxfp6_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_co
 #pragma unroll
                 for (int h = 0; h < OC / 32; ++h) tmem_ld_x32(tacc + piece * OC + 32 * h, reinterpret_cast<uint32_t(&)[32]>(v[32 * h]));
                 tmem_ld_wait();
-                if (ci == 0) { tc_fence_before(); mbar_arrive_cluster(ovl0); }
+                if (ci == 0) {
+                    // one arrival per warp: every lane's loads are complete (wait::ld above) before the warp meets
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive_cluster(ovl0);
+                }
                 if (affine) affine_chunk<false, OC>(P, v, my_p0 + prow, q0 + piece * OC);
                 if (P.q_fmt >= 0) {
                     // the result leaves as an MX operand of the next layer, in blocks of 32 columns
