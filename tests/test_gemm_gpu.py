@@ -425,3 +425,28 @@ def test_cpp_host_harness(args):
     res = subprocess.run([exe] + args, capture_output=True, text=True, timeout=300)
     assert res.returncode == 0, res.stdout + res.stderr
     assert "TFLOP/s" in res.stdout and res.stdout.strip().endswith("OK")
+
+
+# ------------------------------------------------------------------------------- seeded random shapes
+def _random_shapes(n, seed):
+    rng = np.random.default_rng(seed)
+    shapes = []
+    for _ in range(n):
+        M = int(rng.choice([1, 7, 16, 33, 64, 100, 128, 129, 255, 256, 300, 512, 777, 1024, 1500, 2304]))
+        N = int(rng.choice([8, 16, 72, 128, 200, 256, 264, 512, 1000, 1024, 2048, 2312, 4096]))
+        K = int(rng.choice([128, 256, 384, 512, 640, 1024, 1536, 2048]))
+        shapes.append((M, N, K))
+    return shapes
+
+
+@pytest.mark.parametrize("shape", _random_shapes(40, seed=2024), ids=lambda s: "x".join(map(str, s)))
+def test_random_shapes_against_oracle(shape):
+    """Shapes on both sides of every kernel-choice boundary (M <= 128 swap, pair-kernel threshold, TMA-able scale
+    rows, vector-store alignment), mixed formats by seed, all against the fp64 oracle."""
+    M, N, K = shape
+    fmts = [(R.E2M3, R.E2M3), (R.E3M2, R.E3M2), (R.E2M3, R.E3M2), (R.E4M3, R.E2M3)]
+    fa, fb = fmts[(M + N + K) % 4]
+    pa, sa, pb, sb = quantized_inputs("lognormal" if (M * N) % 3 == 0 else "normal", M, N, K, fa, seed=M + 3 * N + K, fmt_b=fb)
+    c = run_gpu(pa, sa, pb, sb, fa, fb)
+    ref, absdot = oracle_f64(pa, sa, pb, sb, fa, fb)
+    check(c, ref, absdot)
