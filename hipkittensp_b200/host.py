@@ -10,7 +10,7 @@ from __future__ import annotations
 
 import torch
 
-from ._lib import E2M3
+from ._lib import E2M3, E4M3, E5M2
 from .gemm import dispatch_micro
 
 
@@ -19,11 +19,12 @@ class HostGemm:
         self.M, self.N, self.K, self.fmt, self.depth = M, N, K, fmt, depth
         self.device = torch.device(device)
         u8 = dict(dtype=torch.uint8, device=self.device)
+        row_bytes = K if fmt in (E4M3, E5M2) else K * 3 // 4      # one byte per fp8 element, 3 bytes per 4 fp6 elements
         self.slots = []
         for _ in range(depth):
             self.slots.append(dict(
-                a=torch.empty((M, K * 3 // 4), **u8), sa=torch.empty((M, K // 32), **u8),
-                b=torch.empty((N, K * 3 // 4), **u8), sb=torch.empty((N, K // 32), **u8),
+                a=torch.empty((M, row_bytes), **u8), sa=torch.empty((M, K // 32), **u8),
+                b=torch.empty((N, row_bytes), **u8), sb=torch.empty((N, K // 32), **u8),
                 c=torch.empty((M, N), dtype=torch.bfloat16, device=self.device),
                 loaded=torch.cuda.Event(), computed=torch.cuda.Event(), drained=torch.cuda.Event()))
         self.s_in = torch.cuda.Stream(self.device)

@@ -188,14 +188,15 @@ def test_multi_destination_column_window(shape, force):
     assert torch.equal(dests[0][:, off:off + N], dests[2][:, off:off + N])
 
 
-def test_host_gemm_pipeline_matches_direct_calls():
+@pytest.mark.parametrize("fmt", [R.E2M3, R.E4M3])
+def test_host_gemm_pipeline_matches_direct_calls(fmt):
     """HostGemm: operands and results in pinned host memory, consecutive calls overlapped on three streams."""
     M, N, K = 256, 512, 1024
     sets = []
     for seed in range(3):
-        pa, sa, pb, sb = quantized_inputs("lognormal", M, N, K, seed=seed)
+        pa, sa, pb, sb = quantized_inputs("lognormal", M, N, K, fmt, seed=seed)
         sets.append([torch.from_numpy(x).pin_memory() for x in (pa, sa, pb, sb)])
-    pipe = hk.HostGemm(M, N, K)
+    pipe = hk.HostGemm(M, N, K, fmt=fmt)
     outs = [torch.empty((M, N), dtype=torch.bfloat16).pin_memory() for _ in range(6)]
     for i in range(6):
         h = sets[i % 3]
@@ -204,7 +205,7 @@ def test_host_gemm_pipeline_matches_direct_calls():
     assert hk.device_status() == 0
     for i in range(6):
         h = [t.cuda() for t in sets[i % 3]]
-        want = hk.gemm(h[0], h[1], h[2], h[3]).cpu()
+        want = hk.gemm(h[0], h[1], h[2], h[3], fmt).cpu()
         assert torch.equal(outs[i].view(torch.int16), want.view(torch.int16))
 
 
