@@ -1,5 +1,5 @@
 """Host logic of the column-parallel wrapper on CPU: partition arithmetic, gather layout, and a
-world_size-2 gloo run in which the per-rank GEMM is replaced by the oracle (no GPU)."""
+world_size-2 and -4 gloo runs in which the per-rank GEMM is replaced by the oracle (no GPU)."""
 import os
 import socket
 
@@ -71,12 +71,12 @@ def _worker(rank, world, port, M, N, K, ret):
         dist.destroy_process_group()
 
 
-def test_two_rank_gloo_gather_equals_single():
-    world = 2
+@pytest.mark.parametrize("world", [2, 4])
+def test_gloo_ranks_gather_equals_single(world):
     with mp.Manager() as mgr:
         ret = mgr.dict()
         mp.spawn(_worker, args=(world, _free_port(), 64, 256, 256, ret), nprocs=world, join=True)
-        assert dict(ret) == {0: True, 1: True}
+        assert dict(ret) == {r: True for r in range(world)}
 
 
 def test_row_parallel_single_process_bounds():
