@@ -568,6 +568,12 @@ mxfp6_gemm_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constan
                 if (partial) {
 #pragma unroll
                     for (int i = 0; i < CW; ++i) slot[(size_t)(ch * CW + i) * 128 + prow] = __uint_as_float(v[i]);
+                } else if (Cfg::SWAP && P.q_fmt >= 0) {
+                    // the result leaves as an MX operand: the warp's 32 rows p are one 32-column block of C row q
+#pragma unroll
+                    for (int i = 0; i < CW; ++i)
+                        quant_store_lanes(__uint_as_float(v[i]), P.q_fmt, P.q_out, (size_t)P.q_ld, P.q_scales, P.c_cols,
+                                          qc + i, sg.p0 + quad * 32, qc + i < P.c_rows && sg.p0 + quad * 32 < P.c_cols);
                 } else if (Cfg::SWAP) {
                     // D[p,q] -> C[q,p]: consecutive lanes write consecutive bf16 of one C row
                     if (p < P.c_cols) {
@@ -660,7 +666,12 @@ mxfp6_gemm_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constan
 #pragma unroll
                                 for (int e = 0; e < 4; ++e) x[e] = affine_one<Cfg::SWAP>(P, x[e], pr + e, q);
                             }
-                            if (Cfg::SWAP) {
+                            if (Cfg::SWAP && P.q_fmt >= 0) {
+                                // 8 lanes x 4 rows are one 32-column block of C row q
+                                // (every lane takes part in the shuffles; blocks past the edge only skip their stores)
+                                quant_store_lanes4(x, P.q_fmt, P.q_out, (size_t)P.q_ld, P.q_scales, P.c_cols, q,
+                                                   sg.p0 + (r4 & ~31), q < P.c_rows && sg.p0 + (r4 & ~31) < P.c_cols);
+                            } else if (Cfg::SWAP) {
                                 // D[p,q] -> C[q,p]: the 4 rows are 4 consecutive bf16 of C's row q
                                 if (q < P.c_rows) {
                                     __nv_bfloat16* dst = P.c + (size_t)q * P.ldc + pr;

@@ -316,7 +316,9 @@ static int gemm_impl(const void* a, const void* sfa, const void* b, const void* 
     // the pair kernel stores C by TMA: 16-byte aligned destinations and row stride
     bool c_tma_ok = (dst.ldc % 8) == 0;
     for (int i = 0; i < dst.n; ++i) c_tma_ok = c_tma_ok && !((uintptr_t)dst.c[i] & 15);
-    Plan pl = make_plan(M, N, K, d.sm_count, sf_tma_ok && c_tma_ok, dst.n > 1 || q_fmt >= 0);
+    // several destinations are written untransposed from whole tiles; a re-quantised result may take the swapped,
+    // K-split form (its blocks of 32 along N are then 32 rows of D: one per lane)
+    Plan pl = make_plan(M, N, K, d.sm_count, sf_tma_ok && c_tma_ok, dst.n > 1);
 
     if (pl.ws_bytes) {
         if (own_ws) {

@@ -24,15 +24,20 @@ __device__ __forceinline__ uint32_t cvt_pair(float x0, float x1) {
     else asm("cvt.rn.satfinite.e5m2x2.f32 %0, %1, %2;" : "=h"(r) : "f"(x1), "f"(x0));
     return r;
 }
+__device__ __forceinline__ uint32_t mad_u32(uint32_t a, uint32_t b, uint32_t c) {
+    uint32_t d;
+    asm("mad.lo.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
 // four values -> 4 codes: fp8 one per byte (32 bits), fp6 6 bits each (24 bits)
 template <int FMT>
 __device__ __forceinline__ uint32_t cvt_quad(float x0, float x1, float x2, float x3) {
     const uint32_t lo = cvt_pair<FMT>(x0, x1), hi = cvt_pair<FMT>(x2, x3);
-    const uint32_t t = lo | (hi << 16);                   // one code per byte
-    if constexpr (FMT == kE4M3 || FMT == kE5M2) return t;
-    // four 6-bit fields at bit 0, 8, 16, 24 -> bit 0, 6, 12, 18: first within each half, then the halves
-    const uint32_t u = (t & 0x003f003fu) | ((t >> 2) & 0x0fc00fc0u);
-    return (u & 0xfffu) | ((u >> 4) & 0xfff000u);
+    if constexpr (FMT == kE4M3 || FMT == kE5M2) return lo | (hi << 16);          // one code per byte
+    // a pair is c0 + 256*c1; the 12-bit form c0 + 64*c1 is pair - 192*(pair >> 8), and two 12-bit forms join by
+    // one more multiply-add: integer multiply-adds run on the FMA pipe, which this code leaves idle, not on the ALU
+    const uint32_t lo12 = mad_u32(lo >> 8, 0xffffff40u, lo), hi12 = mad_u32(hi >> 8, 0xffffff40u, hi);
+    return mad_u32(hi12, 4096u, lo12);
 }
 
 // E8M0 byte of a block whose largest magnitude is amax
@@ -85,9 +90,9 @@ __device__ __forceinline__ int quant_block32_amax(const float* v, float amax, ui
 #pragma unroll
         for (int h4 = 0; h4 < 2; ++h4) {      // 4 x 24 bits -> 3 words, twice
             const uint32_t* q = w24 + 4 * h4;
-            out[3 * h4 + 0] = q[0] | (q[1] << 24);
-            out[3 * h4 + 1] = (q[1] >> 8) | (q[2] << 16);
-            out[3 * h4 + 2] = (q[2] >> 16) | (q[3] << 8);
+            out[3 * h4 + 0] = mad_u32(q[1], 1u << 24, q[0]);
+            out[3 * h4 + 1] = mad_u32(q[2], 1u << 16, q[1] >> 8);
+            out[3 * h4 + 2] = mad_u32(q[3], 1u << 8, q[2] >> 16);
         }
     }
     return sb;
@@ -96,6 +101,78 @@ __device__ __forceinline__ int quant_block32_amax(const float* v, float amax, ui
 template <int FMT>
 __device__ __forceinline__ int quant_block32(const float* v, uint32_t* out) {
     return quant_block32_amax<FMT>(v, amax32(v), out);
+}
+
+// One code (low byte) from one value: the pair conversion with a zero partner.
+__device__ __forceinline__ uint32_t cvt_one(float x, int fmt) {
+    uint32_t r;
+    if (fmt == kE2M3) r = cvt_pair<kE2M3>(x, 0.f);
+    else if (fmt == kE3M2) r = cvt_pair<kE3M2>(x, 0.f);
+    else if (fmt == kE4M3) r = cvt_pair<kE4M3>(x, 0.f);
+    else r = cvt_pair<kE5M2>(x, 0.f);
+    return r & 0xffu;
+}
+__device__ __forceinline__ uint32_t cvt_quad_rt(float x0, float x1, float x2, float x3, int fmt) {
+    if (fmt == kE2M3) return cvt_quad<kE2M3>(x0, x1, x2, x3);
+    if (fmt == kE3M2) return cvt_quad<kE3M2>(x0, x1, x2, x3);
+    if (fmt == kE4M3) return cvt_quad<kE4M3>(x0, x1, x2, x3);
+    return cvt_quad<kE5M2>(x0, x1, x2, x3);
+}
+__device__ __forceinline__ float quant_inv_scale(int sb) {          // 2^-(sb-127)
+    const int e = sb - 127;
+    return e == 127 ? __uint_as_float(0x00400000u) : __uint_as_float((uint32_t)(127 - e) << 23);
+}
+
+// A block of 32 consecutive columns of output row `row` whose elements sit one per lane of a warp (lane = column
+// within the block): scale from the warp-wide largest magnitude, one conversion per lane, and the codes leave as
+// 32 bytes (fp8) or, gathered by four lanes at a time, as six 32-bit words (fp6).  Whole warp, converged.
+__device__ __forceinline__ void quant_store_lanes(float x, int fmt, uint8_t* q_out, size_t q_ld, uint8_t* q_scales,
+                                                  int n_cols, int row, int col0, bool row_valid) {
+    const int lane = threadIdx.x & 31;
+    const float amax = __uint_as_float(__reduce_max_sync(0xffffffffu, __float_as_uint(fabsf(x))));
+    const int sb = quant_scale_byte(amax, fmt);
+    const uint32_t code = cvt_one(x * quant_inv_scale(sb), fmt);
+    const bool fp8 = fmt == kE4M3 || fmt == kE5M2;
+    if (fp8) {
+        if (row_valid) q_out[(size_t)row * q_ld + col0 + lane] = (uint8_t)code;
+    } else {
+        // lanes 4j: 24 bits of the four codes 4j..4j+3; then lanes 4j, 4j+1, 4j+2 of every 16 write one word each
+        uint32_t w = code | (__shfl_down_sync(0xffffffffu, code, 1) << 6) | (__shfl_down_sync(0xffffffffu, code, 2) << 12) |
+                     (__shfl_down_sync(0xffffffffu, code, 3) << 18);
+        const uint32_t w0 = __shfl_sync(0xffffffffu, w, (lane & ~15) + 0), w1 = __shfl_sync(0xffffffffu, w, (lane & ~15) + 4),
+                       w2 = __shfl_sync(0xffffffffu, w, (lane & ~15) + 8), w3 = __shfl_sync(0xffffffffu, w, (lane & ~15) + 12);
+        const int i = lane & 15;
+        if (row_valid && i < 3) {
+            const uint32_t word = i == 0 ? (w0 | (w1 << 24)) : i == 1 ? ((w1 >> 8) | (w2 << 16)) : ((w2 >> 16) | (w3 << 8));
+            reinterpret_cast<uint32_t*>(q_out + (size_t)row * q_ld + col0 / 4 * 3)[(lane >> 4) * 3 + i] = word;
+        }
+    }
+    if (row_valid && lane == 0) q_scales[(size_t)row * (n_cols / 32) + col0 / 32] = (uint8_t)sb;
+}
+
+// The same for a block whose 32 columns are held four per lane by 8 consecutive lanes (lane % 8 = column / 4).
+__device__ __forceinline__ void quant_store_lanes4(const float (&x)[4], int fmt, uint8_t* q_out, size_t q_ld, uint8_t* q_scales,
+                                                   int n_cols, int row, int col0, bool row_valid) {
+    const int lane = threadIdx.x & 31;
+    float amax = fmaxf(fmaxf(fabsf(x[0]), fabsf(x[1])), fmaxf(fabsf(x[2]), fabsf(x[3])));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
+    const int sb = quant_scale_byte(amax, fmt);
+    const float f = quant_inv_scale(sb);
+    const uint32_t w = cvt_quad_rt(x[0] * f, x[1] * f, x[2] * f, x[3] * f, fmt);
+    const bool fp8 = fmt == kE4M3 || fmt == kE5M2;
+    const int j = lane & 7;                                   // this lane's 4 columns: col0 + 4j ..
+    if (fp8) {
+        if (row_valid) reinterpret_cast<uint32_t*>(q_out + (size_t)row * q_ld + col0)[j] = w;
+    } else {
+        // lanes 4g..4g+3 hold 4 x 24 bits = three 32-bit words of the packed stream
+        const uint32_t wn = __shfl_down_sync(0xffffffffu, w, 1);
+        const int i4 = lane & 3;
+        if (row_valid && i4 < 3)
+            reinterpret_cast<uint32_t*>(q_out + (size_t)row * q_ld + col0 / 4 * 3)[(j >> 2) * 3 + i4] = (w >> (8 * i4)) | (wn << (24 - 8 * i4));
+    }
+    if (row_valid && j == 0) q_scales[(size_t)row * (n_cols / 32) + col0 / 32] = (uint8_t)sb;
 }
 
 // Quantise 32 consecutive columns [col, col+32) of row `row` and store codes + scale.

@@ -256,7 +256,9 @@ def _exact_inputs(M, N, K, seed):
 
 @pytest.mark.parametrize("out_fmt", [R.E2M3, R.E3M2, R.E4M3, R.E5M2])
 @pytest.mark.parametrize("shape,force", [((256, 512, 512), None), ((512, 768, 1024), "256,0,0,1"),
-                                         ((130, 192, 256), None), ((16, 256, 512), None)])
+                                         ((130, 192, 256), None), ((16, 256, 512), None), ((16, 4096, 2048), None),
+                                         ((64, 2048, 1024), None), ((100, 1024, 512), None), ((16, 512, 256), "16,1,0"),
+                                         ((33, 1024, 1024), "64,1,1")])
 def test_requant_epilogue_bit_exact_on_exact_sums(out_fmt, shape, force):
     M, N, K = shape
     if force:
