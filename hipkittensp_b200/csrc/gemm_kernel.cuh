@@ -566,8 +566,11 @@ mxfp6_gemm_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constan
                 const int qc = sg.q0 + ch * CW;              // first D column of this chunk
                 if (!partial && affine) affine_chunk<Cfg::SWAP, CW>(P, v, p, qc);
                 if (partial) {
+                    // rows past the end of P (a skinny unswapped A) are neither published nor summed
+                    if (p < P.p_rows) {
 #pragma unroll
-                    for (int i = 0; i < CW; ++i) slot[(size_t)(ch * CW + i) * 128 + prow] = __uint_as_float(v[i]);
+                        for (int i = 0; i < CW; ++i) slot[(size_t)(ch * CW + i) * 128 + prow] = __uint_as_float(v[i]);
+                    }
                 } else if (Cfg::SWAP && P.q_fmt >= 0) {
                     // the result leaves as an MX operand: the warp's 32 rows p are one 32-column block of C row q
 #pragma unroll
@@ -631,10 +634,16 @@ mxfp6_gemm_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constan
                     constexpr int NJ = BN / 4;                       // columns per thread: quad + 4 * j
                     constexpr int JB = NJ >= 8 ? 8 : NJ;
                     const int pr = sg.p0 + r4;
+                    // every lane owns 4 rows; lanes whose rows all lie past the end of P have
+                    // nothing to sum (their partials were never written) but stay in the loop for the warp-wide steps
+                    const bool rows_live = pr < P.p_rows;
 #pragma unroll 1
                     for (int j0 = 0; j0 < NJ; j0 += JB) {
                         float4 acc[JB];
-                        if (sg.nseg == 2) {                       // the common case: both slots fetched at once
+                        if (!rows_live) {
+#pragma unroll
+                            for (int j = 0; j < JB; ++j) acc[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+                        } else if (sg.nseg == 2) {                       // the common case: both slots fetched at once
                             float4 t0[JB], t1[JB];
 #pragma unroll
                             for (int j = 0; j < JB; ++j) {

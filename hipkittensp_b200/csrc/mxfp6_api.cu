@@ -178,7 +178,15 @@ static Plan make_plan(int64_t M, int64_t N, int64_t K, int sm_count, bool allow_
     const char* force = getenv("MXFP6_FORCE_CFG");   // "bn,swap,streamk[,pair]", for tests
     int fbn = 0, fswap = -1, fsk = -1, fpair = -1;
     if (force) sscanf(force, "%d,%d,%d,%d", &fbn, &fswap, &fsk, &fpair);
-    if (M <= 128 && N > M && !plain) {      // plain: whole tiles, C stored untransposed (several destinations)
+    // Skinny M: the weights are what is streamed.  Up to M = 32 the swapped form (weights on the 128-row side, K-split
+    // work units over all SMs) is fastest.  Above that, whole unswapped 128 x 256 tiles stream 256 weight rows per
+    // K-block and store C untransposed, which is faster as long as the tiles cover most SMs (measured at
+    // N = 28672, K = 8192: M = 64 / 96 / 128 in 41.8 / 42.3 / 43.3 us against 45.7 / 52.6 / 53.4 us swapped;
+    // M = 16 in 52.4 against 38.5 us).
+    const int64_t t256n = ceil_div(N, 256);
+    const double cover = (double)t256n / (double)((int64_t)ceil_div(t256n, sm_count) * sm_count);
+    const bool wide_rows = M > 32 && M <= 128 && cover >= 0.6;
+    if (M <= 128 && N > M && !plain && !wide_rows) {      // plain: whole tiles, C stored untransposed (several destinations)
         p.swap = true;
         p.bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : 128;
         // K-split work units balance the SMs
@@ -186,11 +194,11 @@ static Plan make_plan(int64_t M, int64_t N, int64_t K, int sm_count, bool allow_
     } else {
         p.swap = false; p.streamk = false;
         const int64_t t256 = (int64_t)ceil_div(M, 128) * ceil_div(N, 256);
-        p.bn = (N >= 256 && t256 >= sm_count) ? 256 : 128;
+        p.bn = (N >= 256 && (t256 >= sm_count || wide_rows)) ? 256 : 128;
     }
     // one 256x256 tile per CTA pair as soon as that occupies at least half of the pairs (measured: 2048^3 with
     // 64 pair tiles runs in 11.6 us against 17 us with 128x128 tiles)
-    p.pair = !p.swap && N >= 256 && (K / 32) % 16 == 0 &&
+    p.pair = !p.swap && !wide_rows && N >= 256 && (K / 32) % 16 == 0 &&
              (int64_t)ceil_div(M, 256) * ceil_div(N, 256) >= sm_count / 4;
     if (fbn) { p.bn = fbn; p.pair = false; }
     if (fpair >= 0) p.pair = fpair != 0;
