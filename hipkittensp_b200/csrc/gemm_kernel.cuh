@@ -146,8 +146,10 @@ struct GemmCfg {
     static constexpr int SF_COL = OVERLAP ? 480 : 2 * BN;
     static constexpr int TMEM_COLS = 512;
     static constexpr int NUM_BARS = 2 * STAGES + 2 * RAW_SLOTS + 2 * ATOM_GROUPS + 5;
+    // unswapped form: column scale and bias of the current tile for the fp32 epilogue (2 x BN floats, 16-byte aligned)
+    static constexpr int AFF_BYTES = SWAP ? 0 : 2 * BN * 4 + 16;
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + RAW_SLOTS * RAW_BYTES + ATOM_GROUPS * GROUP_BYTES +
-                                      NUM_BARS * 8 + 64;
+                                      NUM_BARS * 8 + 64 + AFF_BYTES;
     static constexpr int SMEM_ALLOC = SMEM_BYTES + 1024;  // slack for the 1024-byte alignment of the operand ring
     static constexpr int THREADS = 256;
     static constexpr int GROUP_P = 8;                     // tile rasterisation: groups of 8 P-tiles share Q-tiles
@@ -287,6 +289,8 @@ mxfp6_gemm_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constan
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_gen + misc_off);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + misc_off + 4);
     volatile int* ticket_slot = reinterpret_cast<volatile int*>(smem_gen + misc_off + 8);
+    float* aff_sn = reinterpret_cast<float*>(smem_gen + ((misc_off + 64 + 15) & ~15u));    // [BN] column scales, then [BN] biases
+    float* aff_bn = aff_sn + BN;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     pdl_launch_dependents();     // the next kernel may set itself up on SMs this grid has left
@@ -544,15 +548,36 @@ mxfp6_gemm_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constan
         constexpr int NCH = BN / CW;
         while (ok && it.next(sg)) {
             const int b = n_seg & 1;
+            const bool affine = has_affine(P);
+            // unswapped fp32 epilogue: this thread's row factor and up to two of the tile's column factors / biases are
+            // fetched while the accumulator is still being computed, then shared through shared memory
+            float row_scale = 1.f, cs[2] = {1.f, 1.f}, cb[2] = {0.f, 0.f};
+            if (!Cfg::SWAP && affine) {
+                if (P.scale_m && sg.p0 + prow < P.c_rows) row_scale = __ldg(P.scale_m + sg.p0 + prow);
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const int c = sg.q0 + etid + 128 * h;
+                    if (etid + 128 * h < BN && c < P.c_cols) {
+                        if (P.scale_n) cs[h] = __ldg(P.scale_n + c);
+                        if (P.bias_n) cb[h] = __ldg(P.bias_n + c);
+                    }
+                }
+            }
             ok = epilogue_all(wait_bar_warp(bar_acc_full(b), (n_seg >> 1) & 1, abort_flag, P, kStatusTimeoutEpilogue));
             if (!ok) break;
             tc_fence_after();
+            if (!Cfg::SWAP && affine) {
+                // (the agreement above was a barrier of these 128 threads: nobody still reads the previous tile's vectors)
+#pragma unroll
+                for (int h = 0; h < 2; ++h)
+                    if (etid + 128 * h < BN) { aff_sn[etid + 128 * h] = cs[h]; aff_bn[etid + 128 * h] = cb[h]; }
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+            }
             const uint32_t tacc = tmem_base + ((uint32_t)(quad * 32) << 16) + (b ? Cfg::ACC_COL1 : 0);
             const bool partial = Cfg::STREAMK && sg.nseg > 1;
             float* slot = nullptr;
             if (partial) slot = P.ws_partial + ((size_t)sg.tile * P.ws_slots + sg.segidx) * (size_t)(BN * 128);
             const int p = sg.p0 + prow;
-            const bool affine = has_affine(P);
 #pragma unroll 1
             for (int ci = 0; ci < NCH; ++ci) {
                 // with overlapping accumulators the 32 shared columns are drained first
@@ -564,7 +589,22 @@ mxfp6_gemm_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constan
                 if (Cfg::OVERLAP && ci == 0) { tc_fence_before(); __syncwarp(); if (lane == 0) mbar_arrive(bar_ovl); }
                 if (!Cfg::OVERLAP && ci == NCH - 1) { tc_fence_before(); mbar_arrive(bar_acc_empty(b)); }
                 const int qc = sg.q0 + ch * CW;              // first D column of this chunk
-                if (!partial && affine) affine_chunk<Cfg::SWAP, CW>(P, v, p, qc);
+                if (!partial && affine) {
+                    if constexpr (Cfg::SWAP) {
+                        affine_chunk<true, CW>(P, v, p, qc);
+                    } else {
+                        // (acc * column scale) * row scale + bias, three roundings; the vectors are broadcast reads
+#pragma unroll
+                        for (int c = 0; c < CW; c += 4) {
+                            const float4 sn = *reinterpret_cast<const float4*>(aff_sn + ch * CW + c);
+                            const float4 bn = *reinterpret_cast<const float4*>(aff_bn + ch * CW + c);
+                            v[c + 0] = __float_as_uint(__fadd_rn(__fmul_rn(__fmul_rn(__uint_as_float(v[c + 0]), sn.x), row_scale), bn.x));
+                            v[c + 1] = __float_as_uint(__fadd_rn(__fmul_rn(__fmul_rn(__uint_as_float(v[c + 1]), sn.y), row_scale), bn.y));
+                            v[c + 2] = __float_as_uint(__fadd_rn(__fmul_rn(__fmul_rn(__uint_as_float(v[c + 2]), sn.z), row_scale), bn.z));
+                            v[c + 3] = __float_as_uint(__fadd_rn(__fmul_rn(__fmul_rn(__uint_as_float(v[c + 3]), sn.w), row_scale), bn.w));
+                        }
+                    }
+                }
                 if (partial) {
                     // rows past the end of P (a skinny unswapped A) are neither published nor summed
                     if (p < P.p_rows) {

@@ -46,8 +46,9 @@ struct PairCfg {
     static constexpr int SF_COL = 480;
     static constexpr int TMEM_COLS = 512;
     static constexpr int NUM_BARS = 2 * STAGES + 2 * RAW_SLOTS + 2 * ATOM_GROUPS + 3;
+    static constexpr int AFF_BYTES = 2 * BN * 4;          // column scale and bias of the current tile (fp32 epilogue)
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + OUT_BUFS * OUT_BYTES + RAW_SLOTS * RAW_BYTES +
-                                      ATOM_GROUPS * GROUP_BYTES + NUM_BARS * 8 + 64;
+                                      ATOM_GROUPS * GROUP_BYTES + NUM_BARS * 8 + 64 + 16 + AFF_BYTES;
     static constexpr int SMEM_ALLOC = SMEM_BYTES + 1024;
     static constexpr int THREADS = 256;
     static_assert(SMEM_ALLOC <= 232448, "exceeds the shared memory of a CTA");
@@ -118,6 +119,8 @@ mxfp6_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_co
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_gen + misc_off);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + misc_off + 4);
     const uint32_t abort_addr = smem_base + misc_off + 4;
+    float* aff_sn = reinterpret_cast<float*>(smem_gen + ((misc_off + 64 + 15) & ~15u));   // [256] column scales, then [256] biases (16-byte aligned)
+    float* aff_bn = aff_sn + Cfg::BN;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     pdl_launch_dependents();     // the next kernel may set itself up on SMs this grid has left
@@ -296,13 +299,29 @@ mxfp6_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_co
             int p0, q0;
             pair_coords(P, tile, p0, q0);
             const int b = n_seg & 1;
+            const int my_p0 = p0 + 128 * (int)rank;
+            const bool affine = has_affine(P);
+            // fp32 epilogue: this thread's row factor and two of the tile's 256 column factors / biases are fetched
+            // while the accumulator is still being computed
+            float row_scale = 1.f;
+            float2 col_scale = make_float2(1.f, 1.f), col_bias = make_float2(0.f, 0.f);
+            if (affine) {
+                const int c = q0 + 2 * etid;
+                if (P.scale_m && my_p0 + prow < P.c_rows) row_scale = __ldg(P.scale_m + my_p0 + prow);
+                if (P.scale_n) { if (c < P.c_cols) col_scale.x = __ldg(P.scale_n + c); if (c + 1 < P.c_cols) col_scale.y = __ldg(P.scale_n + c + 1); }
+                if (P.bias_n) { if (c < P.c_cols) col_bias.x = __ldg(P.bias_n + c); if (c + 1 < P.c_cols) col_bias.y = __ldg(P.bias_n + c + 1); }
+            }
             ok = epilogue_all(wait_bar_warp(bar_acc_full(b), (n_seg >> 1) & 1, abort_flag, P, kStatusTimeoutEpilogue));
             if (!ok) break;
             tc_fence_after();
+            if (affine) {
+                // (the agreement above was a barrier of these 128 threads: nobody still reads the previous tile's vectors)
+                reinterpret_cast<float2*>(aff_sn)[etid] = col_scale;
+                reinterpret_cast<float2*>(aff_bn)[etid] = col_bias;
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+            }
             const uint32_t tacc = tmem_base + ((uint32_t)(quad * 32) << 16) + (b ? Cfg::ACC_COL1 : 0);
-            const int my_p0 = p0 + 128 * (int)rank;
             constexpr int OC = Cfg::OUT_COLS;                 // columns per piece
-            const bool affine = has_affine(P);
             constexpr int NP = 256 / OC;
 #pragma unroll 1
             for (int ci = 0; ci < NP; ++ci) {
@@ -320,27 +339,70 @@ mxfp6_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_co
                     __syncwarp();
                     if (lane == 0) mbar_arrive_cluster(ovl0);
                 }
-                if (affine) affine_chunk<false, OC>(P, v, my_p0 + prow, q0 + piece * OC);
-                if (P.q_fmt >= 0) {
-                    // the result leaves as an MX operand of the next layer, in blocks of 32 columns
-                    const int row = my_p0 + prow;
-                    if (row < P.c_rows) {
+                if (affine) {
+                    // (acc * column scale) * row scale + bias, three roundings; the vectors are broadcast reads
 #pragma unroll
-                        for (int hb = 0; hb < OC / 32; ++hb) {
-                            const int col = q0 + piece * OC + 32 * hb;
-                            if (col < P.c_cols)
-                                quant_store32(v + 32 * hb, P.q_fmt, P.q_out, (size_t)P.q_ld, P.q_scales, P.c_cols, row, col);
-                        }
+                    for (int c = 0; c < OC; c += 4) {
+                        const float4 sn = *reinterpret_cast<const float4*>(aff_sn + piece * OC + c);
+                        const float4 bn = *reinterpret_cast<const float4*>(aff_bn + piece * OC + c);
+                        v[c + 0] = __float_as_uint(__fadd_rn(__fmul_rn(__fmul_rn(__uint_as_float(v[c + 0]), sn.x), row_scale), bn.x));
+                        v[c + 1] = __float_as_uint(__fadd_rn(__fmul_rn(__fmul_rn(__uint_as_float(v[c + 1]), sn.y), row_scale), bn.y));
+                        v[c + 2] = __float_as_uint(__fadd_rn(__fmul_rn(__fmul_rn(__uint_as_float(v[c + 2]), sn.z), row_scale), bn.z));
+                        v[c + 3] = __float_as_uint(__fadd_rn(__fmul_rn(__fmul_rn(__uint_as_float(v[c + 3]), sn.w), row_scale), bn.w));
                     }
-                    ++n_out;
-                    continue;
                 }
                 // the stores that last used this staging buffer have finished reading it
                 if (etid == 0) bulk_wait_group_read<Cfg::OUT_BUFS - 1>();
                 asm volatile("bar.sync 1, 128;" ::: "memory");
+                static_assert(OC == 64, "the staging layouts below assume pieces of 64 columns");
+                if (P.q_fmt >= 0) {
+                    // The result leaves as an MX operand of the next layer: this thread's 64 columns are two blocks of
+                    // 32.  Their codes (2 x 24 or 2 x 32 bytes) are staged as one dense row of the piece and the piece
+                    // is stored by TMA like a bf16 piece (cmaps.m[0] then describes the code bytes of the output).
+                    const bool fp8 = P.q_fmt == kE4M3 || P.q_fmt == kE5M2;
+                    const int row = my_p0 + prow;
+                    uint32_t sbs = 0;
+#pragma unroll
+                    for (int hb = 0; hb < 2; ++hb) {
+                        float f[32];
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) f[i] = __uint_as_float(v[32 * hb + i]);
+                        uint32_t w[8];
+                        int sb;
+                        if (P.q_fmt == kE2M3) sb = quant_block32<kE2M3>(f, w);
+                        else if (P.q_fmt == kE3M2) sb = quant_block32<kE3M2>(f, w);
+                        else if (P.q_fmt == kE4M3) sb = quant_block32<kE4M3>(f, w);
+                        else sb = quant_block32<kE5M2>(f, w);
+                        sbs |= (uint32_t)sb << (8 * hb);
+                        if (fp8) {
+                            // 64-byte rows, 64-byte swizzle: 16-byte chunk c sits at c ^ ((row / 2) % 4)
+                            const uint32_t ra = buf + prow * 64, sw8 = (uint32_t)((prow >> 1) & 3);
+                            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};"
+                                         ::"r"(ra + (((2 * hb) ^ sw8) << 4)), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]) : "memory");
+                            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};"
+                                         ::"r"(ra + (((2 * hb + 1) ^ sw8) << 4)), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7]) : "memory");
+                        } else {
+                            // 48-byte rows, no swizzle
+                            const uint32_t ra = buf + prow * 48 + 24 * hb;
+                            asm volatile("st.shared.v2.b32 [%0], {%1, %2};" ::"r"(ra), "r"(w[0]), "r"(w[1]) : "memory");
+                            asm volatile("st.shared.v2.b32 [%0], {%1, %2};" ::"r"(ra + 8), "r"(w[2]), "r"(w[3]) : "memory");
+                            asm volatile("st.shared.v2.b32 [%0], {%1, %2};" ::"r"(ra + 16), "r"(w[4]), "r"(w[5]) : "memory");
+                        }
+                    }
+                    const int col = q0 + piece * OC;
+                    if (row < P.c_rows && col < P.c_cols)
+                        *reinterpret_cast<uint16_t*>(P.q_scales + (size_t)row * (P.c_cols / 32) + col / 32) = (uint16_t)sbs;
+                    fence_proxy_async_smem();
+                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                    if (etid == 0) {
+                        tma_store_2d(&cmaps.m[0], buf, (fp8 ? 64 : 48) * (col / 64), my_p0);
+                        bulk_commit_group();
+                    }
+                    ++n_out;
+                    continue;
+                }
                 // row prow of the piece = 128 bytes in 16-byte chunks; chunk c is stored at c ^ (row % 8), the
                 // 128-byte swizzle the TMA store expects
-                static_assert(OC == 64, "the staging layout below is the 128-byte swizzle of 64 bf16 columns");
                 const uint32_t rowaddr = buf + prow * (OC * 2);
                 const uint32_t sw = (uint32_t)(prow & 7);
 #pragma unroll

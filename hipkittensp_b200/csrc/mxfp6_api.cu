@@ -113,6 +113,8 @@ static std::map<MapKey, CUtensorMap> g_maps;
 // kind 2: bf16 output block [rows, inner] with a row stride of stride_bytes, box 64 x box_rows, 128-byte swizzle
 // kind 4: quantiser source, fp32 viewed as [blocks, 32] (128-byte rows), box 32 x box_rows, 128-byte swizzle
 // kind 5: quantiser source, bf16 viewed as [blocks, 32] (64-byte rows), box 32 x box_rows, 64-byte swizzle
+// kind 6: re-quantised fp6 output bytes [rows, 3N/4] (inner = bytes per row), box 48 x box_rows, no swizzle
+// kind 7: re-quantised fp8 output bytes [rows, N], box 64 x box_rows, 64-byte swizzle
 static int make_map(const void* ptr, int64_t rows, int64_t inner, int box_rows, int kind, CUtensorMap* out,
                     int64_t stride_bytes = 0) {
     MapKey key{ptr, rows, inner, stride_bytes, box_rows, kind};
@@ -136,6 +138,8 @@ static int make_map(const void* ptr, int64_t rows, int64_t inner, int box_rows, 
         case 3: strides[0] = (cuuint64_t)inner; break;
         case 4: strides[0] = 128; box[0] = 32; dt = CU_TENSOR_MAP_DATA_TYPE_FLOAT32; break;
         case 5: strides[0] = 64; box[0] = 32; dt = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16; sw = CU_TENSOR_MAP_SWIZZLE_64B; break;
+        case 6: strides[0] = (cuuint64_t)inner; box[0] = 48; sw = CU_TENSOR_MAP_SWIZZLE_NONE; break;
+        case 7: strides[0] = (cuuint64_t)inner; box[0] = 64; sw = CU_TENSOR_MAP_SWIZZLE_64B; break;
         default: return fail(MXFP6_ERR_BAD_ARG, "make_map: unknown kind %d", kind);
     }
     CUresult r = g_encode(out, dt, 2, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
@@ -401,7 +405,9 @@ static int gemm_impl(const void* a, const void* sfa, const void* b, const void* 
         CMaps cm;
         for (int i = 0; i < 8; ++i) {
             if (i >= dst.n) { cm.m[i] = cm.m[0]; continue; }     // unused slots hold a valid map all the same
-            if ((rc = make_map(dst.c[i], M, N, 128, 2, &cm.m[i], dst.ldc * 2))) return rc;
+            if (q_fmt >= 0) {       // the pieces of a re-quantised result are code bytes, not bf16
+                if ((rc = make_map(q_out, M, fmt_is_fp8(q_fmt) ? N : N * 3 / 4, 128, fmt_is_fp8(q_fmt) ? 7 : 6, &cm.m[i]))) return rc;
+            } else if ((rc = make_map(dst.c[i], M, N, 128, 2, &cm.m[i], dst.ldc * 2))) return rc;
         }
         cudaLaunchAttribute attr{};
         cudaLaunchConfig_t lc = launch_config(pl.grid, PairCfg::THREADS, PairCfg::SMEM_ALLOC, st, &attr);
