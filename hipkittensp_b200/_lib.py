@@ -20,7 +20,7 @@ OK, ERR_BAD_ARG, ERR_CUDA, ERR_DEVICE_WAIT, ERR_UNSUPPORTED = 0, 1, 2, 3, 4
 # every symbol include/mxfp6.h declares
 SYMBOLS = ("mxfp6_version", "mxfp6_last_error", "mxfp6_gemm", "mxfp6_gemm_workspace_bytes", "mxfp6_gemm_ws",
            "mxfp6_gemm_noalloc", "mxfp6_gemm_multi", "mxfp6_gemm_ex", "mxfp6_gemm_requant", "mxfp6_gemm_scaled",
-           "mxfp6_quantize", "mxfp6_dequantize", "mxfp6_device_status", "mxfp6_debug_tma_dump", "mxfp6_debug_wait_timeout")
+           "mxfp6_quantize", "mxfp6_dequantize", "mxfp6_device_status", "mxfp6_debug_tma_dump", "mxfp6_debug_wait_timeout", "mxfp6_debug_option")
 
 
 class Mxfp6Error(RuntimeError):
@@ -67,6 +67,8 @@ def _load() -> ctypes.CDLL:
     lib.mxfp6_device_status.argtypes = [ctypes.POINTER(ci)]
     lib.mxfp6_debug_wait_timeout.restype = ci
     lib.mxfp6_debug_wait_timeout.argtypes = [ci, vp]
+    lib.mxfp6_debug_option.restype = ci
+    lib.mxfp6_debug_option.argtypes = [ctypes.c_char_p, ctypes.c_char_p]
     lib.mxfp6_debug_tma_dump.restype = ci
     lib.mxfp6_debug_tma_dump.argtypes = [vp, i64, i64, i64, i64, vp, vp]
     return lib
@@ -78,3 +80,8 @@ lib = _load()
 def check(rc: int) -> None:
     if rc != OK:
         raise Mxfp6Error(rc, lib.mxfp6_last_error().decode())
+
+
+def debug_option(name: str, value: str | None) -> None:
+    """Test hook: set one of the library's switches (None restores the default); see mxfp6_debug_option."""
+    check(lib.mxfp6_debug_option(name.encode(), None if value is None else str(value).encode()))

@@ -58,6 +58,7 @@ struct GemmParams {
     unsigned long long wait_cycles;  // budget of one wait in clock cycles
     int group_p;               // pair kernel: P-tiles per rasterisation group
     int early_p;               // swapped form: P (the weights) may be read before the preceding kernel has finished
+    int l2_load, l2_store;     // L2 eviction policy of the operand loads / of the stores of C (0 normal, 1 evict_first, 2 evict_last)
     // optional fp32 epilogue, applied to the finished sum before it is rounded (null = absent):
     // C[m,n] = (acc * scale_n[n]) * scale_m[m] + bias_n[n]
     const float* scale_m;      // [M]

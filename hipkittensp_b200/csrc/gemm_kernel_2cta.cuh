@@ -159,6 +159,7 @@ mxfp6_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_co
     if (warp == 0) {
         uint32_t n_stage = 0, n_raw = 0;
         bool ok = true;
+        const uint64_t pol_ld = l2_policy(P.l2_load);
         for (int tile = cluster_id; tile < num_tiles && ok; tile += n_clusters) {
             int p0, q0;
             pair_coords(P, tile, p0, q0);
@@ -184,8 +185,8 @@ mxfp6_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_co
                     const uint32_t full0 = mapa_shared(bar_full(s), 0);
                     // the even CTA announces the bytes of both CTAs' loads for this stage
                     if (leader) mbar_arrive_expect_tx(bar_full(s), 2u * (uint32_t)P.stage_tx_bytes);
-                    tma_load_2d_pair(dst, &tm_p, full0, kb * Cfg::BK, my_p);
-                    tma_load_2d_pair(dst + Cfg::P_BYTES, &tm_q, full0, kb * Cfg::BK, my_q);
+                    tma_load_2d_pair_hint(dst, &tm_p, full0, kb * Cfg::BK, my_p, pol_ld);
+                    tma_load_2d_pair_hint(dst + Cfg::P_BYTES, &tm_q, full0, kb * Cfg::BK, my_q, pol_ld);
                 }
                 __syncwarp();
                 ++n_stage;
@@ -295,6 +296,7 @@ mxfp6_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_co
         uint32_t n_seg = 0, n_out = 0;
         bool ok = true;
         const uint32_t ovl0 = mapa_shared(bar_ovl, 0);
+        const uint64_t pol_st = l2_policy(P.l2_store);
         for (int tile = cluster_id; tile < num_tiles && ok; tile += n_clusters) {
             int p0, q0;
             pair_coords(P, tile, p0, q0);
@@ -395,7 +397,7 @@ mxfp6_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_co
                     fence_proxy_async_smem();
                     asm volatile("bar.sync 1, 128;" ::: "memory");
                     if (etid == 0) {
-                        tma_store_2d(&cmaps.m[0], buf, (fp8 ? 64 : 48) * (col / 64), my_p0);
+                        tma_store_2d_hint(&cmaps.m[0], buf, (fp8 ? 64 : 48) * (col / 64), my_p0, pol_st);
                         bulk_commit_group();
                     }
                     ++n_out;
@@ -417,7 +419,7 @@ mxfp6_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_co
                 fence_proxy_async_smem();
                 asm volatile("bar.sync 1, 128;" ::: "memory");
                 if (etid == 0) {
-                    for (int d = 0; d < P.ndst; ++d) tma_store_2d(&cmaps.m[d], buf, q0 + piece * OC, my_p0);
+                    for (int d = 0; d < P.ndst; ++d) tma_store_2d_hint(&cmaps.m[d], buf, q0 + piece * OC, my_p0, pol_st);
                     bulk_commit_group();
                 }
                 ++n_out;

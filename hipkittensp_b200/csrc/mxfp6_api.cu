@@ -11,11 +11,14 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstdlib>
+#include <atomic>
 #include <cstring>
 #include <map>
+#include <memory>
 #include <mutex>
 #include <string>
-#include <tuple>
+#include <utility>
+#include <vector>
 
 #include "gemm_kernel_2cta.cuh"
 #include "quantize_kernel.cuh"
@@ -39,6 +42,52 @@ static int fail(int code, const char* fmt, ...) {
         if (e_ != cudaSuccess) return fail(MXFP6_ERR_CUDA, "%s: %s", #expr, cudaGetErrorString(e_)); \
     } while (0)
 
+// ---------------------------------------------------------------------------------- options
+// Test hooks.  Their first values come from the environment when the library is first used; afterwards only
+// mxfp6_debug_option changes them, so no call path reads the environment.
+struct Options {
+    int force_bn = 0, force_swap = -1, force_sk = -1, force_pair = -1;   // MXFP6_FORCE_CFG = "bn,swap,streamk[,pair]"
+    int no_sf_tma = 0;       // MXFP6_NO_SF_TMA: scale arrays read with plain loads
+    int pdl = 1;             // MXFP6_PDL: programmatic dependent launch
+    int group_p = 16;        // MXFP6_GROUP_P: pair tiles per rasterisation group
+    int quant_quad = 0;      // MXFP6_QUANT_PATH=quad: the plain-load quantiser
+    int wait_ms = 2000;      // MXFP6_WAIT_MS: budget of one bounded wait (read when a device is first used)
+    int l2_load = 0, l2_store = 0;   // MXFP6_L2 = "load,store": eviction policy of the pair kernel's TMA traffic
+    int tail_split = 1;      // MXFP6_TAIL_SPLIT: the pair kernel splits the tiles of its last partial wave along K
+    int decode_rows = 1;     // MXFP6_DECODE_ROWS: skinny problems take the row-balanced kernel when they qualify
+};
+static Options g_opt;
+static std::once_flag g_opt_once;
+static std::atomic<unsigned> g_opt_epoch{1};      // bumped by every change: cached launch recipes carry the epoch they were built in
+
+static bool set_option(const char* name, const char* v) {
+    const Options d{};
+    if (!strcmp(name, "MXFP6_FORCE_CFG")) {
+        g_opt.force_bn = d.force_bn; g_opt.force_swap = d.force_swap; g_opt.force_sk = d.force_sk; g_opt.force_pair = d.force_pair;
+        if (v) sscanf(v, "%d,%d,%d,%d", &g_opt.force_bn, &g_opt.force_swap, &g_opt.force_sk, &g_opt.force_pair);
+    } else if (!strcmp(name, "MXFP6_NO_SF_TMA")) g_opt.no_sf_tma = v ? atoi(v) : d.no_sf_tma;
+    else if (!strcmp(name, "MXFP6_PDL")) g_opt.pdl = v ? atoi(v) : d.pdl;
+    else if (!strcmp(name, "MXFP6_GROUP_P")) { g_opt.group_p = v ? atoi(v) : d.group_p; if (g_opt.group_p < 1) g_opt.group_p = 1; }
+    else if (!strcmp(name, "MXFP6_QUANT_PATH")) g_opt.quant_quad = (v && !strcmp(v, "quad")) ? 1 : 0;
+    else if (!strcmp(name, "MXFP6_WAIT_MS")) g_opt.wait_ms = v ? atoi(v) : d.wait_ms;
+    else if (!strcmp(name, "MXFP6_L2")) {
+        g_opt.l2_load = d.l2_load; g_opt.l2_store = d.l2_store;
+        if (v) sscanf(v, "%d,%d", &g_opt.l2_load, &g_opt.l2_store);
+    } else if (!strcmp(name, "MXFP6_TAIL_SPLIT")) g_opt.tail_split = v ? atoi(v) : d.tail_split;
+    else if (!strcmp(name, "MXFP6_DECODE_ROWS")) g_opt.decode_rows = v ? atoi(v) : d.decode_rows;
+    else return false;
+    return true;
+}
+static const char* const kOptionNames[] = {"MXFP6_FORCE_CFG", "MXFP6_NO_SF_TMA", "MXFP6_PDL", "MXFP6_GROUP_P", "MXFP6_QUANT_PATH",
+                                           "MXFP6_WAIT_MS", "MXFP6_L2", "MXFP6_TAIL_SPLIT", "MXFP6_DECODE_ROWS"};
+static const Options& options() {
+    std::call_once(g_opt_once, [] {
+        for (const char* n : kOptionNames)
+            if (const char* v = getenv(n)) set_option(n, v);
+    });
+    return g_opt;
+}
+
 // ---------------------------------------------------------------------------------- device state
 // Device-side status word written by kernels whose bounded waits run out.
 static __device__ int g_status_word[4];
@@ -49,22 +98,19 @@ struct DeviceState {
     int cc_major = 0;
     unsigned long long wait_cycles = 0;
     int* status = nullptr;       // device address of g_status_word on this device
-    void* ws = nullptr;          // library-owned scratch for split tiles
+    void* ws = nullptr;          // library-owned scratch for split tiles (the newest and largest buffer)
     size_t ws_bytes = 0;
+    std::vector<std::pair<void*, size_t>> ws_all;   // every buffer ever handed out: none is freed, launches and graphs may hold them
     std::map<const void*, bool> smem_attr_set;
 };
 static std::mutex g_mu;
 static DeviceState g_dev[64];
 
-static int env_int(const char* name, int dflt) {
-    const char* v = getenv(name);
-    return v ? atoi(v) : dflt;
-}
-
-static int get_device_state(DeviceState** out) {
+static int get_device_state(DeviceState** out, int* dev_out = nullptr) {
     int dev = 0;
     CUDA_TRY(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64) return fail(MXFP6_ERR_BAD_ARG, "device index %d out of range", dev);
+    if (dev_out) *dev_out = dev;
     DeviceState& d = g_dev[dev];
     std::lock_guard<std::mutex> lk(g_mu);      // two threads may make their first call on a device together
     if (!d.init) {
@@ -73,8 +119,7 @@ static int get_device_state(DeviceState** out) {
         CUDA_TRY(cudaDeviceGetAttribute(&d.cc_major, cudaDevAttrComputeCapabilityMajor, dev));
         CUDA_TRY(cudaDeviceGetAttribute(&khz, cudaDevAttrClockRate, dev));
         if (d.cc_major != 10) return fail(MXFP6_ERR_UNSUPPORTED, "device %d is sm_%d0; this library is sm_100a only", dev, d.cc_major);
-        const int wait_ms = env_int("MXFP6_WAIT_MS", 2000);
-        d.wait_cycles = (unsigned long long)khz * (unsigned long long)wait_ms;
+        d.wait_cycles = (unsigned long long)khz * (unsigned long long)options().wait_ms;
         CUDA_TRY(cudaGetSymbolAddress((void**)&d.status, g_status_word));
         CUDA_TRY(cudaMemset(d.status, 0, sizeof(int) * 4));
         d.init = true;
@@ -83,29 +128,35 @@ static int get_device_state(DeviceState** out) {
     return MXFP6_OK;
 }
 
+// smem attribute of a kernel, once per device (callers hold no lock)
+static int ensure_smem_attr(DeviceState& d, const void* kern, int bytes) {
+    std::lock_guard<std::mutex> lk(g_mu);
+    if (!d.smem_attr_set[kern]) {
+        CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+        d.smem_attr_set[kern] = true;
+    }
+    return MXFP6_OK;
+}
+
 // ---------------------------------------------------------------------------------- tensor maps
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-static EncodeTiledFn g_encode = nullptr;
+static std::atomic<EncodeTiledFn> g_encode{nullptr};
 
-static int get_encode_fn() {
-    if (g_encode) return MXFP6_OK;
-    void* fn = nullptr;
-    cudaDriverEntryPointQueryResult qres;
-    CUDA_TRY(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres));
-    if (!fn || qres != cudaDriverEntryPointSuccess) return fail(MXFP6_ERR_CUDA, "cuTensorMapEncodeTiled not available from the driver");
-    g_encode = (EncodeTiledFn)fn;
+static int get_encode_fn(EncodeTiledFn* out) {
+    EncodeTiledFn f = g_encode.load(std::memory_order_acquire);
+    if (!f) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        CUDA_TRY(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres));
+        if (!fn || qres != cudaDriverEntryPointSuccess) return fail(MXFP6_ERR_CUDA, "cuTensorMapEncodeTiled not available from the driver");
+        f = (EncodeTiledFn)fn;
+        g_encode.store(f, std::memory_order_release);
+    }
+    *out = f;
     return MXFP6_OK;
 }
-
-struct MapKey {
-    const void* ptr; int64_t rows, inner, stride; int box_rows, kind;
-    bool operator<(const MapKey& o) const {
-        return std::tie(ptr, rows, inner, stride, box_rows, kind) < std::tie(o.ptr, o.rows, o.inner, o.stride, o.box_rows, o.kind);
-    }
-};
-static std::map<MapKey, CUtensorMap> g_maps;
 
 // kind 0: packed 6-bit operand [rows, K] (inner = K elements), box 128 x box_rows, 128-byte swizzle
 // kind 1: scale bytes [rows, K/32] (inner = K/32 bytes), box 16 x box_rows, no swizzle
@@ -115,15 +166,12 @@ static std::map<MapKey, CUtensorMap> g_maps;
 // kind 5: quantiser source, bf16 viewed as [blocks, 32] (64-byte rows), box 32 x box_rows, 64-byte swizzle
 // kind 6: re-quantised fp6 output bytes [rows, 3N/4] (inner = bytes per row), box 48 x box_rows, no swizzle
 // kind 7: re-quantised fp8 output bytes [rows, N], box 64 x box_rows, 64-byte swizzle
+// Encoding is pure host arithmetic (no driver state), so maps are built where they are needed and kept inside the
+// launch recipe of the call that uses them.
 static int make_map(const void* ptr, int64_t rows, int64_t inner, int box_rows, int kind, CUtensorMap* out,
                     int64_t stride_bytes = 0) {
-    MapKey key{ptr, rows, inner, stride_bytes, box_rows, kind};
-    {
-        std::lock_guard<std::mutex> lk(g_mu);
-        auto it = g_maps.find(key);
-        if (it != g_maps.end()) { *out = it->second; return MXFP6_OK; }
-    }
-    int rc = get_encode_fn();
+    EncodeTiledFn encode = nullptr;
+    int rc = get_encode_fn(&encode);
     if (rc) return rc;
     cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)rows};
     cuuint64_t strides[1];
@@ -142,14 +190,11 @@ static int make_map(const void* ptr, int64_t rows, int64_t inner, int box_rows, 
         case 7: strides[0] = (cuuint64_t)inner; box[0] = 64; sw = CU_TENSOR_MAP_SWIZZLE_64B; break;
         default: return fail(MXFP6_ERR_BAD_ARG, "make_map: unknown kind %d", kind);
     }
-    CUresult r = g_encode(out, dt, 2, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
-                          CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    CUresult r = encode(out, dt, 2, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS)
         return fail(MXFP6_ERR_CUDA, "cuTensorMapEncodeTiled(kind=%d rows=%lld inner=%lld box_rows=%d) failed with %d",
                     kind, (long long)rows, (long long)inner, box_rows, (int)r);
-    std::lock_guard<std::mutex> lk(g_mu);
-    if (g_maps.size() > 256) g_maps.clear();
-    g_maps[key] = *out;
     return MXFP6_OK;
 }
 
@@ -178,10 +223,9 @@ constexpr int64_t kMaxSplitTiles = 65536;
 
 static Plan make_plan(int64_t M, int64_t N, int64_t K, int sm_count, bool allow_pair = true, bool plain = false) {
     Plan p{};
+    const Options& o = options();
     const int kb = (int)(K / 128);
-    const char* force = getenv("MXFP6_FORCE_CFG");   // "bn,swap,streamk[,pair]", for tests
-    int fbn = 0, fswap = -1, fsk = -1, fpair = -1;
-    if (force) sscanf(force, "%d,%d,%d,%d", &fbn, &fswap, &fsk, &fpair);
+    const int fbn = o.force_bn, fswap = o.force_swap, fsk = o.force_sk, fpair = o.force_pair;
     // Skinny M: the weights are what is streamed.  Up to M = 32 the swapped form (weights on the 128-row side, K-split
     // work units over all SMs) is fastest.  Above that, whole unswapped 128 x 256 tiles stream 256 weight rows per
     // K-block and store C untransposed, which is faster as long as the tiles cover most SMs (measured at
@@ -242,39 +286,6 @@ static Plan make_plan(int64_t M, int64_t N, int64_t K, int sm_count, bool allow_
     return p;
 }
 
-// Launch configuration shared by the GEMM kernels.  Programmatic stream serialisation lets the next kernel of
-// the stream begin its set-up (barriers, TMEM, descriptor prefetch) before this one has drained; the kernels
-// call griddepcontrol.wait before their first global access.  MXFP6_PDL=0 turns it off.
-static cudaLaunchConfig_t launch_config(int grid, int threads, int smem, cudaStream_t st, cudaLaunchAttribute* attr) {
-    cudaLaunchConfig_t lc{};
-    lc.gridDim = dim3((unsigned)grid, 1, 1);
-    lc.blockDim = dim3((unsigned)threads, 1, 1);
-    lc.dynamicSmemBytes = (size_t)smem;
-    lc.stream = st;
-    attr->id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr->val.programmaticStreamSerializationAllowed = 1;
-    lc.attrs = attr;
-    lc.numAttrs = env_int("MXFP6_PDL", 1) ? 1 : 0;
-    return lc;
-}
-
-template <class Cfg>
-static int launch_cfg(DeviceState& d, const Plan& pl, const CUtensorMap& tp, const CUtensorMap& tq,
-                      const CUtensorMap& tsp, const CUtensorMap& tsq, const GemmParams& P, cudaStream_t st) {
-    auto kern = mxfp6_gemm_kernel<Cfg>;
-    {
-        std::lock_guard<std::mutex> lk(g_mu);
-        if (!d.smem_attr_set[(const void*)kern]) {
-            CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_ALLOC));
-            d.smem_attr_set[(const void*)kern] = true;
-        }
-    }
-    cudaLaunchAttribute attr{};
-    cudaLaunchConfig_t lc = launch_config(pl.grid, Cfg::THREADS, Cfg::SMEM_ALLOC, st, &attr);
-    CUDA_TRY(cudaLaunchKernelEx(&lc, kern, tp, tq, tsp, tsq, P));
-    return MXFP6_OK;
-}
-
 // Where the [M,N] result goes: n copies (the first is local, the others may be peer GPUs' memory), each the
 // first element of the block inside a row-major matrix with a row stride of ldc elements.
 struct Dest {
@@ -290,10 +301,145 @@ struct Affine {
     const float* bias_n = nullptr;    // [N]
 };
 
+// Where split-tile scratch comes from.
+enum WsMode : int { kWsOwn = 0,       // the library's per-device buffer, allocated on first need
+                    kWsCaller = 1,    // the caller's buffer
+                    kWsBuiltin = 2 }; // the buffer built into the library image (mxfp6_gemm_noalloc)
+
+// The operand-dependent facts the kernel choice needs, and the choice itself: one place for every entry point.
+static bool scales_by_tma(const void* sfa, const void* sfb, int64_t K) {
+    return ((K / 32) % 16 == 0) && !((uintptr_t)sfa & 15) && !((uintptr_t)sfb & 15) && !options().no_sf_tma;
+}
+static bool dest_by_tma(const Dest& dst) {
+    bool ok = (dst.ldc % 8) == 0;      // the pair kernel stores C by TMA: 16-byte aligned destinations and row stride
+    for (int i = 0; i < dst.n; ++i) ok = ok && !((uintptr_t)dst.c[i] & 15);
+    return ok;
+}
+static Plan plan_for(const void* sfa, const void* sfb, const Dest& dst, int64_t M, int64_t N, int64_t K, int sm_count) {
+    // several destinations are written untransposed from whole tiles
+    return make_plan(M, N, K, sm_count, scales_by_tma(sfa, sfb, K) && dest_by_tma(dst), dst.n > 1);
+}
+
+// Everything a call passes in.  Two calls with equal keys launch the same kernel with the same arguments, so the
+// launch recipe of the first is reused by the second.  (Zero-filled before use: compared bytewise.)
+struct CallKey {
+    const void *a, *sfa, *b, *sfb;
+    void* c[8];
+    int64_t ldc, M, N, K;
+    void* ws; size_t ws_bytes;
+    void *q_out, *q_scales;
+    const float *scale_m, *scale_n, *bias_n;
+    int n_dst, fmt_a, fmt_b, ws_mode, q_fmt, dev;
+    unsigned flags, epoch;
+};
+
+struct Recipe {
+    CallKey key;
+    bool valid = false;
+    const void* func = nullptr;
+    int grid = 0, threads = 0, smem = 0;
+    bool pair = false, pdl = true;
+    size_t counter_bytes = 0;    // built-in scratch: counters to clear before every launch
+    void* counter_ptr = nullptr;
+    CUtensorMap tp, tq, tsp, tsq;
+    CMaps cm;
+    GemmParams P;
+};
+
+// A small per-thread table: no lock on the hit path.
+constexpr int kRecipeSlots = 16;
+struct RecipeCache {
+    Recipe slot[kRecipeSlots];
+    unsigned next = 0;
+};
+static thread_local std::unique_ptr<RecipeCache> t_cache;
+
+static int launch_recipe(const Recipe& r, cudaStream_t st) {
+    if (r.counter_bytes) CUDA_TRY(cudaMemsetAsync(r.counter_ptr, 0, r.counter_bytes, st));
+    cudaLaunchConfig_t lc{};
+    lc.gridDim = dim3((unsigned)r.grid, 1, 1);
+    lc.blockDim = dim3((unsigned)r.threads, 1, 1);
+    lc.dynamicSmemBytes = (size_t)r.smem;
+    lc.stream = st;
+    // Programmatic stream serialisation lets the next kernel of the stream begin its set-up (barriers, TMEM,
+    // descriptor prefetch) before this one has drained; the kernels call griddepcontrol.wait before their first
+    // global access.
+    cudaLaunchAttribute attr{};
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    lc.attrs = &attr;
+    lc.numAttrs = r.pdl ? 1 : 0;
+    if (r.pair) {
+        void* args[] = {(void*)&r.tp, (void*)&r.tq, (void*)&r.tsp, (void*)&r.tsq, (void*)&r.cm, (void*)&r.P};
+        CUDA_TRY(cudaLaunchKernelExC(&lc, r.func, args));
+    } else {
+        void* args[] = {(void*)&r.tp, (void*)&r.tq, (void*)&r.tsp, (void*)&r.tsq, (void*)&r.P};
+        CUDA_TRY(cudaLaunchKernelExC(&lc, r.func, args));
+    }
+    return MXFP6_OK;
+}
+
+template <class Cfg>
+static int bind_cfg(DeviceState& d, Recipe& r) {
+    auto kern = mxfp6_gemm_kernel<Cfg>;
+    r.func = (const void*)kern;
+    r.threads = Cfg::THREADS;
+    r.smem = Cfg::SMEM_ALLOC;
+    return ensure_smem_attr(d, r.func, Cfg::SMEM_ALLOC);
+}
+
+// Library-owned scratch of at least `bytes`.  Buffers are never freed or moved: an earlier launch, or a CUDA graph
+// captured earlier, may still hold the address it was given.  A larger request gets a new, larger buffer.
+static int own_scratch(DeviceState& d, size_t bytes, cudaStream_t st, void** out) {
+    std::lock_guard<std::mutex> lk(g_mu);
+    if (d.ws_bytes < bytes) {
+        cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+        if (cudaStreamIsCapturing(st, &cap) == cudaSuccess && cap != cudaStreamCaptureStatusNone)
+            return fail(MXFP6_ERR_BAD_ARG,
+                        "this shape needs %zu bytes of scratch and the library holds %zu: it cannot allocate while the stream is "
+                        "being captured; call once before the capture, or pass scratch through mxfp6_gemm_ws", bytes, d.ws_bytes);
+        size_t want = d.ws_bytes * 2 > bytes ? d.ws_bytes * 2 : bytes;
+        if (want < (size_t)(8u << 20)) want = (size_t)(8u << 20);
+        void* p = nullptr;
+        if (cudaMalloc(&p, want) != cudaSuccess) {
+            (void)cudaGetLastError();
+            want = bytes;
+            CUDA_TRY(cudaMalloc(&p, want));
+        }
+        CUDA_TRY(cudaMemset(p, 0, want));
+        d.ws_all.emplace_back(p, want);
+        d.ws = p;
+        d.ws_bytes = want;
+    }
+    *out = d.ws;
+    return MXFP6_OK;
+}
+
 static int gemm_impl(const void* a, const void* sfa, const void* b, const void* sfb, const Dest& dst, int64_t M, int64_t N,
-                     int64_t K, int fmt_a, int fmt_b, void* ws, size_t ws_bytes, bool own_ws, void* stream,
+                     int64_t K, int fmt_a, int fmt_b, void* ws, size_t ws_bytes, int ws_mode, void* stream,
                      unsigned flags = 0, void* q_out = nullptr, void* q_scales = nullptr, int q_fmt = -1,
                      const Affine& aff = Affine{}) {
+    cudaStream_t st = (cudaStream_t)stream;
+    // ---- the recipe of an identical earlier call
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess) { (void)cudaGetLastError(); dev = -1; }   // no usable device: the checks below still answer
+    CallKey key;
+    memset(&key, 0, sizeof key);
+    key.a = a; key.sfa = sfa; key.b = b; key.sfb = sfb;
+    if (dst.n >= 1 && dst.n <= 8) for (int i = 0; i < dst.n; ++i) key.c[i] = dst.c[i];
+    key.ldc = dst.ldc; key.M = M; key.N = N; key.K = K;
+    key.ws = ws; key.ws_bytes = ws_bytes;
+    key.q_out = q_out; key.q_scales = q_scales;
+    key.scale_m = aff.scale_m; key.scale_n = aff.scale_n; key.bias_n = aff.bias_n;
+    key.n_dst = dst.n; key.fmt_a = fmt_a; key.fmt_b = fmt_b; key.ws_mode = ws_mode; key.q_fmt = q_fmt; key.dev = dev;
+    key.flags = flags; key.epoch = g_opt_epoch.load(std::memory_order_acquire);
+    if (!t_cache) t_cache.reset(new RecipeCache());      // a few tens of KB per calling thread
+    for (int i = 0; i < kRecipeSlots && dev >= 0; ++i) {
+        const Recipe& r = t_cache->slot[i];
+        if (r.valid && !memcmp(&r.key, &key, sizeof key)) return launch_recipe(r, st);
+    }
+
+    // ---- first call of this kind: check, plan, build
     void* c = dst.c[0];
     if (M < 0 || N < 0 || K < 0) return fail(MXFP6_ERR_BAD_ARG, "negative dimension (M=%lld N=%lld K=%lld)", (long long)M, (long long)N, (long long)K);
     if (K % 128 != 0) return fail(MXFP6_ERR_BAD_ARG, "K=%lld must be a multiple of 128", (long long)K);
@@ -302,7 +448,6 @@ static int gemm_impl(const void* a, const void* sfa, const void* b, const void* 
     if (M > 0x7fffff00LL || N > 0x7fffff00LL || K > 0x7fffff00LL) return fail(MXFP6_ERR_BAD_ARG, "dimension too large");
     if (M == 0 || N == 0) return MXFP6_OK;
     if (!c) return fail(MXFP6_ERR_BAD_ARG, "null C");
-    cudaStream_t st = (cudaStream_t)stream;
     if (dst.n < 1 || dst.n > 8) return fail(MXFP6_ERR_BAD_ARG, "1 to 8 destinations, got %d", dst.n);
     if (dst.ldc < N) return fail(MXFP6_ERR_BAD_ARG, "ldc=%lld is smaller than N=%lld", (long long)dst.ldc, (long long)N);
     for (int i = 0; i < dst.n; ++i) {
@@ -318,34 +463,28 @@ static int gemm_impl(const void* a, const void* sfa, const void* b, const void* 
     if (((uintptr_t)a & (fmt_is_fp8(fmt_a) ? 15 : 31)) || ((uintptr_t)b & (fmt_is_fp8(fmt_b) ? 15 : 31)))
         return fail(MXFP6_ERR_BAD_ARG, "operands must be 32-byte aligned (fp6) / 16-byte aligned (fp8)");
     if (((uintptr_t)sfa & 3) || ((uintptr_t)sfb & 3)) return fail(MXFP6_ERR_BAD_ARG, "scale arrays must be 4-byte aligned");
-    if ((uintptr_t)c & 1) return fail(MXFP6_ERR_BAD_ARG, "C must be 2-byte aligned");
 
     DeviceState* dp = nullptr;
     int rc = get_device_state(&dp);
     if (rc) return rc;
     DeviceState& d = *dp;
-    const bool sf_tma_ok = ((K / 32) % 16 == 0) && !((uintptr_t)sfa & 15) && !((uintptr_t)sfb & 15) && !env_int("MXFP6_NO_SF_TMA", 0);
-    // the pair kernel stores C by TMA: 16-byte aligned destinations and row stride
-    bool c_tma_ok = (dst.ldc % 8) == 0;
-    for (int i = 0; i < dst.n; ++i) c_tma_ok = c_tma_ok && !((uintptr_t)dst.c[i] & 15);
-    // several destinations are written untransposed from whole tiles; a re-quantised result may take the swapped,
-    // K-split form (its blocks of 32 along N are then 32 rows of D: one per lane)
-    Plan pl = make_plan(M, N, K, d.sm_count, sf_tma_ok && c_tma_ok, dst.n > 1);
+    const Options& o = options();
+    const bool sf_tma = scales_by_tma(sfa, sfb, K);
+    const Plan pl = plan_for(sfa, sfb, dst, M, N, K, d.sm_count);
 
+    Recipe r;
+    r.key = key;
     if (pl.ws_bytes) {
-        if (own_ws) {
-            std::lock_guard<std::mutex> lk(g_mu);
-            if (d.ws_bytes < pl.ws_bytes) {
-                if (d.ws) { CUDA_TRY(cudaDeviceSynchronize()); CUDA_TRY(cudaFree(d.ws)); d.ws = nullptr; d.ws_bytes = 0; }
-                size_t want = pl.ws_bytes < (size_t)(8u << 20) ? (size_t)(8u << 20) : pl.ws_bytes;
-                CUDA_TRY(cudaMalloc(&d.ws, want));
-                CUDA_TRY(cudaMemset(d.ws, 0, want));
-                d.ws_bytes = want;
-            }
-            ws = d.ws;
+        if (ws_mode == kWsOwn) {
+            if ((rc = own_scratch(d, pl.ws_bytes, st, &ws))) return rc;
         } else {
             if (!ws || ws_bytes < pl.ws_bytes) return fail(MXFP6_ERR_BAD_ARG, "workspace too small: need %zu bytes, got %zu", pl.ws_bytes, ws_bytes);
             if ((uintptr_t)ws & 255) return fail(MXFP6_ERR_BAD_ARG, "workspace must be 256-byte aligned");
+            if (ws_mode == kWsBuiltin) {
+                // that buffer keeps whatever the previous call left: the arrival counters of this call's tiles must be zero
+                r.counter_ptr = ws;
+                r.counter_bytes = (size_t)pl.tiles_p * pl.tiles_q * sizeof(unsigned int);
+            }
         }
     }
 
@@ -354,18 +493,17 @@ static int gemm_impl(const void* a, const void* sfa, const void* b, const void* 
     const int64_t prow = pl.swap ? N : M, qrow = pl.swap ? M : N;
     const int fp = pl.swap ? fmt_b : fmt_a, fq = pl.swap ? fmt_a : fmt_b;
 
-    CUtensorMap tp, tq, tsp, tsq;
-    if ((rc = make_map(pp, prow, K, 128, fmt_is_fp8(fp) ? 3 : 0, &tp))) return rc;
-    const bool sf_tma = sf_tma_ok;
-    if ((rc = make_map(qp, qrow, K, pl.pair ? 128 : pl.bn, fmt_is_fp8(fq) ? 3 : 0, &tq))) return rc;
+    if ((rc = make_map(pp, prow, K, 128, fmt_is_fp8(fp) ? 3 : 0, &r.tp))) return rc;
+    if ((rc = make_map(qp, qrow, K, pl.pair ? 128 : pl.bn, fmt_is_fp8(fq) ? 3 : 0, &r.tq))) return rc;
     if (sf_tma) {
-        if ((rc = make_map(sp, prow, K / 32, 128, 1, &tsp))) return rc;
-        if ((rc = make_map(sq, qrow, K / 32, pl.bn, 1, &tsq))) return rc;   // pair kernel: all 256 Q rows per CTA
+        if ((rc = make_map(sp, prow, K / 32, 128, 1, &r.tsp))) return rc;
+        if ((rc = make_map(sq, qrow, K / 32, pl.bn, 1, &r.tsq))) return rc;   // pair kernel: all 256 Q rows per CTA
     } else {
-        tsp = tp; tsq = tq;   // unused by the kernel in this mode
+        r.tsp = r.tp; r.tsq = r.tq;   // unused by the kernel in this mode
     }
 
-    GemmParams P{};
+    GemmParams& P = r.P;
+    memset(&P, 0, sizeof P);
     P.p_rows = (int)prow; P.q_rows = (int)qrow;
     P.kblocks = (int)(K / 128);
     P.tiles_p = pl.tiles_p; P.tiles_q = pl.tiles_q;
@@ -386,51 +524,51 @@ static int gemm_impl(const void* a, const void* sfa, const void* b, const void* 
     P.ws_slots = pl.ws_slots;
     P.status = d.status;
     P.wait_cycles = d.wait_cycles;
+    r.pdl = o.pdl != 0;
     // B is the P operand of the swapped (skinny-M) form; with programmatic dependent launch its first stages may be
     // requested while the preceding kernel is still draining
-    P.early_p = (pl.swap && (flags & MXFP6_FLAG_B_STATIC) && env_int("MXFP6_PDL", 1)) ? 1 : 0;
-    P.group_p = env_int("MXFP6_GROUP_P", 16);   // 16 pair-tiles (4096 rows of A) share each tile of B
-    if (P.group_p < 1) P.group_p = 1;
+    P.early_p = (pl.swap && (flags & MXFP6_FLAG_B_STATIC) && o.pdl) ? 1 : 0;
+    P.group_p = o.group_p;   // 16 pair-tiles (4096 rows of A) share each tile of B
+    P.l2_load = o.l2_load; P.l2_store = o.l2_store;
     P.scale_m = aff.scale_m; P.scale_n = aff.scale_n; P.bias_n = aff.bias_n;
 
+    r.grid = pl.grid;
+    r.pair = pl.pair;
     if (pl.pair) {
-        auto kern = mxfp6_gemm_pair_kernel;
-        {
-            std::lock_guard<std::mutex> lk(g_mu);
-            if (!d.smem_attr_set[(const void*)kern]) {
-                CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, PairCfg::SMEM_ALLOC));
-                d.smem_attr_set[(const void*)kern] = true;
-            }
-        }
-        CMaps cm;
+        r.func = (const void*)mxfp6_gemm_pair_kernel;
+        r.threads = PairCfg::THREADS;
+        r.smem = PairCfg::SMEM_ALLOC;
+        if ((rc = ensure_smem_attr(d, r.func, PairCfg::SMEM_ALLOC))) return rc;
         for (int i = 0; i < 8; ++i) {
-            if (i >= dst.n) { cm.m[i] = cm.m[0]; continue; }     // unused slots hold a valid map all the same
+            if (i >= dst.n) { r.cm.m[i] = r.cm.m[0]; continue; }     // unused slots hold a valid map all the same
             if (q_fmt >= 0) {       // the pieces of a re-quantised result are code bytes, not bf16
-                if ((rc = make_map(q_out, M, fmt_is_fp8(q_fmt) ? N : N * 3 / 4, 128, fmt_is_fp8(q_fmt) ? 7 : 6, &cm.m[i]))) return rc;
-            } else if ((rc = make_map(dst.c[i], M, N, 128, 2, &cm.m[i], dst.ldc * 2))) return rc;
+                if ((rc = make_map(q_out, M, fmt_is_fp8(q_fmt) ? N : N * 3 / 4, 128, fmt_is_fp8(q_fmt) ? 7 : 6, &r.cm.m[i]))) return rc;
+            } else if ((rc = make_map(dst.c[i], M, N, 128, 2, &r.cm.m[i], dst.ldc * 2))) return rc;
         }
-        cudaLaunchAttribute attr{};
-        cudaLaunchConfig_t lc = launch_config(pl.grid, PairCfg::THREADS, PairCfg::SMEM_ALLOC, st, &attr);
-        CUDA_TRY(cudaLaunchKernelEx(&lc, kern, tp, tq, tsp, tsq, cm, P));
-        return MXFP6_OK;
-    }
+    } else {
+        rc = -1;
 #define MXFP6_CASE(BN_, SWAP_, SK_)                                                              \
-    if (pl.bn == BN_ && pl.swap == SWAP_ && pl.streamk == SK_)                                   \
-        return launch_cfg<GemmCfg<BN_, SWAP_, SK_>>(d, pl, tp, tq, tsp, tsq, P, st);
-    MXFP6_CASE(256, false, false)
-    MXFP6_CASE(128, false, false)
-    MXFP6_CASE(256, false, true)
-    MXFP6_CASE(128, false, true)
-    MXFP6_CASE(16, true, true)
-    MXFP6_CASE(32, true, true)
-    MXFP6_CASE(64, true, true)
-    MXFP6_CASE(128, true, true)
-    MXFP6_CASE(16, true, false)
-    MXFP6_CASE(32, true, false)
-    MXFP6_CASE(64, true, false)
-    MXFP6_CASE(128, true, false)
+        if (pl.bn == BN_ && pl.swap == SWAP_ && pl.streamk == SK_) rc = bind_cfg<GemmCfg<BN_, SWAP_, SK_>>(d, r);
+        MXFP6_CASE(256, false, false)
+        MXFP6_CASE(128, false, false)
+        MXFP6_CASE(256, false, true)
+        MXFP6_CASE(128, false, true)
+        MXFP6_CASE(16, true, true)
+        MXFP6_CASE(32, true, true)
+        MXFP6_CASE(64, true, true)
+        MXFP6_CASE(128, true, true)
+        MXFP6_CASE(16, true, false)
+        MXFP6_CASE(32, true, false)
+        MXFP6_CASE(64, true, false)
+        MXFP6_CASE(128, true, false)
 #undef MXFP6_CASE
-    return fail(MXFP6_ERR_BAD_ARG, "no kernel for bn=%d swap=%d streamk=%d", pl.bn, (int)pl.swap, (int)pl.streamk);
+        if (rc == -1) return fail(MXFP6_ERR_BAD_ARG, "no kernel for bn=%d swap=%d streamk=%d", pl.bn, (int)pl.swap, (int)pl.streamk);
+        if (rc) return rc;
+    }
+    if ((rc = launch_recipe(r, st))) return rc;
+    r.valid = true;
+    t_cache->slot[t_cache->next++ % kRecipeSlots] = r;
+    return MXFP6_OK;
 }
 
 // ---------------------------------------------------------------------------------- quantise / dequantise
@@ -571,7 +709,7 @@ extern "C" const char* mxfp6_last_error(void) { return g_err.c_str(); }
 
 extern "C" int mxfp6_gemm(const void* a, const void* sfa, const void* b, const void* sfb, void* c, int64_t M, int64_t N,
                           int64_t K, int fmt_a, int fmt_b, void* stream) {
-    return gemm_impl(a, sfa, b, sfb, Dest{{c}, 1, N}, M, N, K, fmt_a, fmt_b, nullptr, 0, true, stream);
+    return gemm_impl(a, sfa, b, sfb, Dest{{c}, 1, N}, M, N, K, fmt_a, fmt_b, nullptr, 0, kWsOwn, stream);
 }
 
 extern "C" size_t mxfp6_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K) {
@@ -583,13 +721,13 @@ extern "C" size_t mxfp6_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K) {
 
 extern "C" int mxfp6_gemm_ws(const void* a, const void* sfa, const void* b, const void* sfb, void* c, int64_t M, int64_t N,
                              int64_t K, int fmt_a, int fmt_b, void* workspace, size_t workspace_bytes, void* stream) {
-    return gemm_impl(a, sfa, b, sfb, Dest{{c}, 1, N}, M, N, K, fmt_a, fmt_b, workspace, workspace_bytes, false, stream);
+    return gemm_impl(a, sfa, b, sfb, Dest{{c}, 1, N}, M, N, K, fmt_a, fmt_b, workspace, workspace_bytes, kWsCaller, stream);
 }
 
 extern "C" int mxfp6_gemm_ex(const void* a, const void* sfa, const void* b, const void* sfb, void* c, int64_t M, int64_t N,
                              int64_t K, int fmt_a, int fmt_b, unsigned flags, void* stream) {
     if (flags & ~(unsigned)MXFP6_FLAG_B_STATIC) return fail(MXFP6_ERR_BAD_ARG, "unknown flag bits 0x%x", flags);
-    return gemm_impl(a, sfa, b, sfb, Dest{{c}, 1, N}, M, N, K, fmt_a, fmt_b, nullptr, 0, true, stream, flags);
+    return gemm_impl(a, sfa, b, sfb, Dest{{c}, 1, N}, M, N, K, fmt_a, fmt_b, nullptr, 0, kWsOwn, stream, flags);
 }
 
 extern "C" int mxfp6_gemm_requant(const void* a, const void* sfa, const void* b, const void* sfb, void* out, void* out_scales,
@@ -598,12 +736,13 @@ extern "C" int mxfp6_gemm_requant(const void* a, const void* sfa, const void* b,
     if (N % 64 != 0) return fail(MXFP6_ERR_BAD_ARG, "requant: N=%lld must be a multiple of 64", (long long)N);
     if (M > 0 && N > 0 && (!out || !out_scales)) return fail(MXFP6_ERR_BAD_ARG, "requant: null output");
     if ((uintptr_t)out & 15) return fail(MXFP6_ERR_BAD_ARG, "requant: output must be 16-byte aligned");
+    if ((uintptr_t)out_scales & 1) return fail(MXFP6_ERR_BAD_ARG, "requant: out_scales must be 2-byte aligned");
     if (K == 0 && M > 0 && N > 0) {   // all-zero result: codes 0, scale byte 0
         CUDA_TRY(cudaMemsetAsync(out, 0, (size_t)M * (fmt_is_fp8(out_fmt) ? N : N * 3 / 4), (cudaStream_t)stream));
         CUDA_TRY(cudaMemsetAsync(out_scales, 0, (size_t)M * (N / 32), (cudaStream_t)stream));
         return MXFP6_OK;
     }
-    return gemm_impl(a, sfa, b, sfb, Dest{{out}, 1, N}, M, N, K, fmt_a, fmt_b, nullptr, 0, true, stream, 0, out, out_scales, out_fmt);
+    return gemm_impl(a, sfa, b, sfb, Dest{{out}, 1, N}, M, N, K, fmt_a, fmt_b, nullptr, 0, kWsOwn, stream, 0, out, out_scales, out_fmt);
 }
 
 // C = bias broadcast along rows: what the scaled GEMM yields for K = 0
@@ -628,7 +767,7 @@ extern "C" int mxfp6_gemm_scaled(const void* a, const void* sfa, const void* b, 
     }
     Affine aff;
     aff.scale_m = scale_a; aff.scale_n = scale_b; aff.bias_n = bias;
-    return gemm_impl(a, sfa, b, sfb, Dest{{c}, 1, N}, M, N, K, fmt_a, fmt_b, nullptr, 0, true, stream, 0, nullptr, nullptr, -1, aff);
+    return gemm_impl(a, sfa, b, sfb, Dest{{c}, 1, N}, M, N, K, fmt_a, fmt_b, nullptr, 0, kWsOwn, stream, 0, nullptr, nullptr, -1, aff);
 }
 
 extern "C" int mxfp6_gemm_multi(const void* a, const void* sfa, const void* b, const void* sfb, void* const* c_dst,
@@ -640,7 +779,7 @@ extern "C" int mxfp6_gemm_multi(const void* a, const void* sfa, const void* b, c
     for (int i = 0; i < n_dst; ++i) d.c[i] = c_dst[i];
     d.n = n_dst;
     d.ldc = ldc;
-    return gemm_impl(a, sfa, b, sfb, d, M, N, K, fmt_a, fmt_b, nullptr, 0, true, stream);
+    return gemm_impl(a, sfa, b, sfb, d, M, N, K, fmt_a, fmt_b, nullptr, 0, kWsOwn, stream);
 }
 
 // ---------------------------------------------------------------------------------- GEMM without allocation
@@ -655,12 +794,11 @@ extern "C" int mxfp6_gemm_noalloc(const void* a, const void* sfa, const void* b,
                                   int64_t N, int64_t K, int fmt_a, int fmt_b, void* stream) {
     // malformed or empty problems take the common path, which rejects or finishes them without any scratch
     if (M <= 0 || N <= 0 || K <= 0 || K % 128 != 0)
-        return gemm_impl(a, sfa, b, sfb, Dest{{c}, 1, N}, M, N, K, fmt_a, fmt_b, nullptr, 0, false, stream);
+        return gemm_impl(a, sfa, b, sfb, Dest{{c}, 1, N}, M, N, K, fmt_a, fmt_b, nullptr, 0, kWsCaller, stream);
     DeviceState* d = nullptr;
-    int rc = get_device_state(&d);
-    if (rc) return rc;
     int dev = 0;
-    CUDA_TRY(cudaGetDevice(&dev));
+    int rc = get_device_state(&d, &dev);
+    if (rc) return rc;
     void* scratch = nullptr;
     {
         std::lock_guard<std::mutex> lk(g_mu);
@@ -672,19 +810,15 @@ extern "C" int mxfp6_gemm_noalloc(const void* a, const void* sfa, const void* b,
         }
         scratch = g_builtin_scratch_addr[dev];
     }
-    const bool sf_tma_ok = ((K / 32) % 16 == 0) && !((uintptr_t)sfa & 15) && !((uintptr_t)sfb & 15) && !env_int("MXFP6_NO_SF_TMA", 0);
-    const Plan pl = make_plan(M, N, K, d->sm_count, sf_tma_ok);
+    const Dest dst{{c}, 1, N};
+    const Plan pl = plan_for(sfa, sfb, dst, M, N, K, d->sm_count);      // the plan the common path will make
     if (pl.ws_bytes > kBuiltinScratchBytes)
         return fail(MXFP6_ERR_BAD_ARG,
                     "mxfp6_gemm_noalloc: M=%lld N=%lld K=%lld needs %zu bytes of scratch but the built-in buffer holds %zu; "
                     "use mxfp6_gemm or mxfp6_gemm_ws for this shape",
                     (long long)M, (long long)N, (long long)K, pl.ws_bytes, kBuiltinScratchBytes);
-    if (pl.ws_bytes) {
-        // the buffer keeps whatever the previous call left: the arrival counters of this call's tiles must be zero
-        const size_t counters = (size_t)pl.tiles_p * pl.tiles_q * sizeof(unsigned int);
-        CUDA_TRY(cudaMemsetAsync(scratch, 0, counters, (cudaStream_t)stream));
-    }
-    return gemm_impl(a, sfa, b, sfb, Dest{{c}, 1, N}, M, N, K, fmt_a, fmt_b, scratch, kBuiltinScratchBytes, false, stream);
+    // (the common path clears the arrival counters of this call's tiles on the stream before every launch)
+    return gemm_impl(a, sfa, b, sfb, dst, M, N, K, fmt_a, fmt_b, scratch, kBuiltinScratchBytes, kWsBuiltin, stream);
 }
 
 extern "C" int mxfp6_quantize(const void* src, int src_dtype, int64_t rows, int64_t K, int fmt, void* packed, void* scales,
@@ -707,9 +841,8 @@ extern "C" int mxfp6_quantize(const void* src, int src_dtype, int64_t rows, int6
     // source, codes and scales), else the plain-load kernel with one thread per 4 elements.  MXFP6_QUANT_PATH=quad
     // forces the latter (for tests).  Measured on 8192 x 8192: fp32 source 55 us against 74 us, bf16 38 against 73 us.
     const int64_t nblk = rows * K / 32;
-    const char* path_env = getenv("MXFP6_QUANT_PATH");
     const bool tma_ok = !((uintptr_t)src & 15) && !((uintptr_t)packed & 15) && !((uintptr_t)scales & 15) && nblk < 0x7fffff00LL;
-    const int path = (tma_ok && !(path_env && !strcmp(path_env, "quad"))) ? 2 : 0;
+    const int path = (tma_ok && !options().quant_quad) ? 2 : 0;
     if (path == 2) {
         CUtensorMap tm;
         if ((rc = make_map(src, nblk, 32, 128, src_dtype == 0 ? 4 : 5, &tm))) return rc;
@@ -719,15 +852,17 @@ extern "C" int mxfp6_quantize(const void* src, int src_dtype, int64_t rows, int6
 #define QT(T, F)                                                                                                     \
         do {                                                                                                         \
             auto kern = quantize_tma_kernel<T, F>;                                                                   \
-            {                                                                                                        \
-                std::lock_guard<std::mutex> lk(g_mu);                                                                \
-                if (!d->smem_attr_set[(const void*)kern]) {                                                          \
-                    CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, QuantCfg<T, F>::SMEM_ALLOC)); \
-                    d->smem_attr_set[(const void*)kern] = true;                                                      \
-                }                                                                                                    \
-            }                                                                                                        \
+            if ((rc = ensure_smem_attr(*d, (const void*)kern, QuantCfg<T, F>::SMEM_ALLOC))) return rc;                \
             cudaLaunchAttribute attr{};                                                                              \
-            cudaLaunchConfig_t lc = launch_config((int)grid, QuantCfg<T, F>::THREADS, QuantCfg<T, F>::SMEM_ALLOC, st, &attr); \
+            cudaLaunchConfig_t lc{};                                                                                 \
+            lc.gridDim = dim3(grid, 1, 1);                                                                           \
+            lc.blockDim = dim3(QuantCfg<T, F>::THREADS, 1, 1);                                                       \
+            lc.dynamicSmemBytes = QuantCfg<T, F>::SMEM_ALLOC;                                                        \
+            lc.stream = st;                                                                                          \
+            attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;                                            \
+            attr.val.programmaticStreamSerializationAllowed = 1;                                                     \
+            lc.attrs = &attr;                                                                                        \
+            lc.numAttrs = options().pdl ? 1 : 0;                                                                     \
             CUDA_TRY(cudaLaunchKernelEx(&lc, kern, tm, (long long)nblk, (uint8_t*)packed, (uint8_t*)scales, d->status, d->wait_cycles)); \
         } while (0)
         if (src_dtype == 0) {
@@ -789,7 +924,7 @@ extern "C" int mxfp6_device_status(int* status_out) {
         CUDA_TRY(cudaMemset(d->status, 0, sizeof h));
         // arrival counters of split tiles may be left non-zero by an aborted launch
         std::lock_guard<std::mutex> lk(g_mu);
-        if (d->ws) CUDA_TRY(cudaMemset(d->ws, 0, d->ws_bytes));
+        for (auto& w : d->ws_all) CUDA_TRY(cudaMemset(w.first, 0, w.second));
         return fail(MXFP6_ERR_DEVICE_WAIT, "a bounded wait ran out on the device: role %d, CTA %d", h[0] & 0xff, h[0] >> 8);
     }
     return MXFP6_OK;
@@ -809,6 +944,15 @@ extern "C" int mxfp6_debug_wait_timeout(int budget_us, void* stream) {
     return MXFP6_OK;
 }
 
+extern "C" int mxfp6_debug_option(const char* name, const char* value) {
+    if (!name) return fail(MXFP6_ERR_BAD_ARG, "debug_option: null name");
+    (void)options();                      // the environment is read first, once
+    std::lock_guard<std::mutex> lk(g_mu);
+    if (!set_option(name, value)) return fail(MXFP6_ERR_BAD_ARG, "debug_option: unknown option %s", name);
+    g_opt_epoch.fetch_add(1, std::memory_order_acq_rel);      // launch recipes built under the old values are not reused
+    return MXFP6_OK;
+}
+
 extern "C" int mxfp6_debug_tma_dump(const void* packed, int64_t rows, int64_t K, int64_t row0, int64_t k0, void* out16k,
                                     void* stream) {
     if (!packed || !out16k || K <= 0 || K % 128 || k0 % 128 || rows <= 0) return fail(MXFP6_ERR_BAD_ARG, "tma_dump: bad argument");
@@ -820,7 +964,7 @@ extern "C" int mxfp6_debug_tma_dump(const void* packed, int64_t rows, int64_t K,
     if ((rc = make_map(packed, rows, K, 128, 0, &tm))) return rc;
     static bool attr = false;
     if (!attr) { CUDA_TRY(cudaFuncSetAttribute(tma_dump_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 16384 + 2048)); attr = true; }
-    const uint32_t tx = 128u * (uint32_t)env_int("MXFP6_TX_BYTES_PER_ROW", 96);
+    const uint32_t tx = 128u * 96u;     // the bytes the box occupies in global memory: 96 per 128-element row
     tma_dump_kernel<<<1, 128, 16384 + 2048, (cudaStream_t)stream>>>(tm, (int)k0, (int)row0, tx, d->wait_cycles / 20, (uint8_t*)out16k, d->status);
     CUDA_TRY(cudaGetLastError());
     return MXFP6_OK;

@@ -11,7 +11,13 @@ Two exchanges:
 * `gather="fused"` (default on GPUs): the full C of every rank lives in symmetric memory (peer-mapped over
   NVLink); the GEMM kernel's epilogue stores each finished 128x64 piece by TMA into the right column window of
   the local C and of every peer's C (`mxfp6_gemm_multi`), so the gather overlaps the remaining tiles and no
-  re-layout pass exists.  A cross-GPU barrier on the stream closes the step.
+  re-layout pass exists.  A cross-GPU barrier on the stream closes the step.  Ordering between steps: a peer's
+  pushes of the next step must not land in a C this rank is still reading.  With `depth=2` (the default) the
+  operator owns two full-size C buffers and alternates between them, so the C a call returns stays untouched
+  until the call after the next one: by then every rank has passed the barrier that closed the next call, which
+  on each rank's stream lies behind its own readers of this C.  With `depth=1` there is one C, and every call
+  opens with a second cross-GPU barrier on the stream (all ranks' queued readers of the previous C are done)
+  before any tile is pushed.  Either way the reader's work must be queued on the same stream before the next call.
 * `gather="nccl"`: one NCCL (or gloo, on CPU) all-gather of the contiguous [M, N/g] shards into a [g, M, N/g]
   buffer followed by a strided copy into row-major C.  The baseline, and the path the CPU tests use.
 """
@@ -49,7 +55,11 @@ def assemble_columns(gathered: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
 class ColumnParallelGemm:
     """Holds the communicator and the reusable buffers of one sharded GEMM shape."""
 
-    def __init__(self, M: int, N: int, K: int, group=None, device=None, fmt: int = E2M3, gather: str | None = None):
+    def __init__(self, M: int, N: int, K: int, group=None, device=None, fmt: int = E2M3, gather: str | None = None,
+                 depth: int = 2):
+        if depth not in (1, 2):
+            raise ValueError("depth must be 1 or 2")
+        self.depth, self.calls = depth, 0
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
@@ -66,12 +76,15 @@ class ColumnParallelGemm:
         if self.mode == "fused" and self.world > 1:
             import torch.distributed._symmetric_memory as symm
 
-            self.c_full = symm.empty((M, N), dtype=torch.bfloat16, device=device)
-            self.symm = symm.rendezvous(self.c_full, dist.group.WORLD if group is None else group)
             # destination 0 is local, the rest are the peers' copies of C, rotated so that ranks do not all
             # push to the same peer at the same moment
             order = [(self.rank + i) % self.world for i in range(self.world)]
-            self.dests = [self.c_full] + [self.symm.get_buffer(r, (M, N), torch.bfloat16) for r in order[1:]]
+            self.bufs = []
+            for _ in range(depth):
+                c = symm.empty((M, N), dtype=torch.bfloat16, device=device)
+                h = symm.rendezvous(c, dist.group.WORLD if group is None else group)
+                self.bufs.append((c, h, [c] + [h.get_buffer(r, (M, N), torch.bfloat16) for r in order[1:]]))
+            self.c_full, self.symm, self.dests = self.bufs[0]
             self.c_shard = self.c_full[:, self.lo:self.hi]
             self.gathered = None
         else:
@@ -85,6 +98,7 @@ class ColumnParallelGemm:
         if self.mode == "fused" and self.world > 1:
             from .gemm import dispatch_multi
 
+            # (into the buffer of the latest call: no peer is written, so no ordering is needed)
             dispatch_multi(A, B_shard, self.dests[:1], self.lo, scale_A, scale_B_shard, self.fmt)
         else:
             dispatch_micro(A, B_shard, self.c_shard, scale_A, scale_B_shard, self.fmt)
@@ -100,6 +114,11 @@ class ColumnParallelGemm:
         if self.mode == "fused" and self.world > 1:
             from .gemm import dispatch_multi
 
+            self.c_full, self.symm, self.dests = self.bufs[self.calls % self.depth]
+            self.c_shard = self.c_full[:, self.lo:self.hi]
+            if self.depth == 1 and self.calls > 0:
+                self.symm.barrier()      # every rank's readers of the previous C are done before anyone overwrites it
+            self.calls += 1
             dispatch_multi(A, B_shard, self.dests, self.lo, scale_A, scale_B_shard, self.fmt)
             self.symm.barrier()          # every rank's pushes have landed before anyone reads C
             return self.c_full
@@ -113,7 +132,11 @@ class RowParallelGemm:
     blocks are additionally pushed to every peer by the GEMM epilogue (symmetric memory), so that each rank ends
     with all of C; row blocks are contiguous, so no re-layout is involved either way."""
 
-    def __init__(self, M: int, N: int, K: int, group=None, device=None, fmt: int = E2M3, gather: bool = False):
+    def __init__(self, M: int, N: int, K: int, group=None, device=None, fmt: int = E2M3, gather: bool = False,
+                 depth: int = 2):
+        if depth not in (1, 2):
+            raise ValueError("depth must be 1 or 2")
+        self.depth, self.calls = depth, 0
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
@@ -124,11 +147,14 @@ class RowParallelGemm:
         if self.push:
             import torch.distributed._symmetric_memory as symm
 
-            self.c_full = symm.empty((M, N), dtype=torch.bfloat16, device=device)
-            self.symm = symm.rendezvous(self.c_full, dist.group.WORLD if group is None else group)
             order = [(self.rank + i) % self.world for i in range(self.world)]
-            bufs = [self.c_full] + [self.symm.get_buffer(r, (M, N), torch.bfloat16) for r in order[1:]]
-            self.dests = [b[self.lo:self.hi] for b in bufs]
+            self.bufs = []
+            for _ in range(depth):        # same ordering contract between steps as ColumnParallelGemm
+                c = symm.empty((M, N), dtype=torch.bfloat16, device=device)
+                h = symm.rendezvous(c, dist.group.WORLD if group is None else group)
+                views = [c] + [h.get_buffer(r, (M, N), torch.bfloat16) for r in order[1:]]
+                self.bufs.append((c, h, [b[self.lo:self.hi] for b in views]))
+            self.c_full, self.symm, self.dests = self.bufs[0]
             self.c_rows = self.dests[0]
         else:
             self.c_rows = torch.empty((self.hi - self.lo, N), dtype=torch.bfloat16, device=device)
@@ -139,6 +165,11 @@ class RowParallelGemm:
         if self.push:
             from .gemm import dispatch_multi
 
+            self.c_full, self.symm, self.dests = self.bufs[self.calls % self.depth]
+            self.c_rows = self.dests[0]
+            if self.depth == 1 and self.calls > 0:
+                self.symm.barrier()
+            self.calls += 1
             dispatch_multi(A_rows, B, self.dests, 0, scale_A_rows, scale_B, self.fmt)
             self.symm.barrier()
             return self.c_full

@@ -16,7 +16,10 @@
  *   - the return value is 0 on success, a MXFP6_ERR_* code otherwise; mxfp6_last_error() gives
  *     the message of the calling thread's last failure;
  *   - the first call on a device (and the first call of a kernel variant) does one-time set-up (attribute
- *     calls, a memset, for split shapes a cudaMalloc): make it before any stream capture;
+ *     calls, a memset, for split shapes a cudaMalloc): make it before any stream capture.  Later calls
+ *     with the same pointers, sizes and formats reuse the launch recipe (tensor maps, kernel choice) of the first;
+ *   - the test hooks (MXFP6_FORCE_CFG and the like) are read from the environment once, when the library is
+ *     first used; afterwards only mxfp6_debug_option changes them;
  *   - preconditions: K % 128 == 0; packed operand pointers 32-byte aligned; C 2-byte aligned
  *     (16-byte aligned C with N % 8 == 0 takes the vector store path); M, N >= 0.
  *
@@ -63,7 +66,11 @@ const char* mxfp6_last_error(void);
  *   c   [M, N] bf16, written in place
  * Shapes that split output tiles along K use a per-device scratch buffer that the library
  * allocates on first need (cudaMalloc) and keeps; concurrent calls on different streams of one
- * device must use mxfp6_gemm_ws with their own scratch instead.
+ * device must use mxfp6_gemm_ws with their own scratch instead.  A scratch buffer is never freed or
+ * moved once a launch has been given it (a CUDA graph captured earlier keeps replaying into it): a shape
+ * that needs more gets an additional, larger buffer.  That allocation cannot happen while the stream is
+ * being captured; the call then fails with MXFP6_ERR_BAD_ARG and says so -- run the shape once before
+ * the capture, or use mxfp6_gemm_ws.
  */
 int mxfp6_gemm(const void* a, const void* sfa, const void* b, const void* sfb, void* c,
                int64_t M, int64_t N, int64_t K, int fmt_a, int fmt_b, void* stream);
@@ -84,7 +91,7 @@ int mxfp6_gemm_ex(const void* a, const void* sfa, const void* b, const void* sfb
  * C as an MX operand, blocks of 32 along N (the next layer's K): out [M, 3N/4] (fp6) or [M, N] (fp8) bytes and
  * out_scales [M, N/32] E8M0 bytes, quantised from the fp32 accumulators with the rule of mxfp6_quantize
  * (so a 2-byte round trip of C through HBM and a quantiser launch disappear).  N % 64 == 0, out 16-byte
- * aligned.  (No counterpart in the reference; the nearest is the epilogue scaling of
+ * aligned, out_scales 2-byte aligned (two scale bytes are stored at a time).  (No counterpart in the reference; the nearest is the epilogue scaling of
  * kernels/torch_scaled/scaled_matmul.cu:253-265.)
  */
 int mxfp6_gemm_requant(const void* a, const void* sfa, const void* b, const void* sfb, void* out, void* out_scales,
@@ -176,6 +183,14 @@ int mxfp6_device_status(int* status_out);
  * that can be bounded.)
  */
 int mxfp6_debug_wait_timeout(int budget_us, void* stream);
+
+/*
+ * Test hook: sets one of the library's switches (the names of the environment variables that give their first
+ * values: "MXFP6_FORCE_CFG" = "bn,swap,streamk[,pair]" forces a kernel variant, "MXFP6_NO_SF_TMA", "MXFP6_PDL",
+ * "MXFP6_GROUP_P", "MXFP6_QUANT_PATH", "MXFP6_L2", "MXFP6_TAIL_SPLIT", "MXFP6_DECODE_ROWS"); value NULL restores the
+ * default.  Takes effect for calls made after it returns.  (No counterpart in the reference.)
+ */
+int mxfp6_debug_option(const char* name, const char* value);
 
 /*
  * Diagnostic: TMA-loads one 128-row x 128-element box of a packed operand (rows row0.., elements

@@ -38,9 +38,16 @@ def run_gpu(pa, sa, pb, sb, fmt, fmt_b=None, guard=True):
     return C.float().cpu().numpy()
 
 
+# Elements whose error exceeds ULP_TOL but lies inside the fp32 accumulation noise floor of their own sum
+# (2^-20 * sum_k |a_k b_k|: results that cancel to almost nothing) are excused by the oracle's report and counted as
+# n_floor.  Their share is bounded: at most one element in 100 000, which means none at all in the small cases.
+FLOOR_SHARE = 1e-5
+
+
 def check(c, ref, absdot):
     assert not np.isnan(c).any(), f"{int(np.isnan(c).sum())} elements of C were not written"
     rep = R.error_report(c, ref, absdot)
     assert rep["row_rel"] <= ROW_REL_TOL, rep
     assert rep["max_ulp"] <= ULP_TOL, rep
+    assert rep["n_floor"] <= int(FLOOR_SHARE * c.size), rep
     return rep

@@ -45,6 +45,12 @@ def test_bad_arguments_rejected_without_gpu():
     assert L.mxfp6_quantize(None, 0, 0, 32, 0, None, None, None) == _lib.OK
     assert L.mxfp6_dequantize(None, None, 4, 32, 3, None, None) == _lib.ERR_BAD_ARG
     assert L.mxfp6_gemm_workspace_bytes(16, 16, 100) == 0
+    # the re-quantising GEMM stores two scale bytes at a time: an odd out_scales pointer is refused
+    assert L.mxfp6_gemm_requant(None, None, None, None, 256, 257, 64, 64, 128, 0, 0, 0, None) == _lib.ERR_BAD_ARG
+    assert b"2-byte aligned" in L.mxfp6_last_error()
+    assert L.mxfp6_debug_option(b"MXFP6_NO_SUCH_SWITCH", b"1") == _lib.ERR_BAD_ARG
+    assert L.mxfp6_debug_option(b"MXFP6_GROUP_P", b"8") == _lib.OK
+    assert L.mxfp6_debug_option(b"MXFP6_GROUP_P", None) == _lib.OK
 
 
 def test_python_wrapper_rejects_cpu_and_bad_tensors():

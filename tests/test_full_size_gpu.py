@@ -1,7 +1,8 @@
-"""Parity at the full benchmark sizes.  The CPU oracle cannot produce a whole 8192 x 8192 result in seconds, so
-each configuration is checked on a seeded sample of complete rows of C against the fp64 oracle (every column of
-those rows, hence every tile column and every K-block of the kernel's schedule), and, where two different
-kernels can compute the same problem, on agreement between them over the whole matrix."""
+"""Parity at the full benchmark sizes against the fp64 oracle (the exactly dequantised operands multiplied in
+float64 on the host cores): the whole 8192 x 8192 result of the headline configuration, and for the larger
+configurations a seeded sample of 512 complete rows of C (every column of those rows, hence every tile column and
+every K-block of the kernel's schedule); where two different kernels can compute the same problem, also agreement
+between them over the whole matrix."""
 import os
 
 import numpy as np
@@ -10,7 +11,7 @@ import torch
 
 import hipkittensp_b200 as hk
 from oracle import mxfp6_ref as R
-from tests.gpu_util import ROW_REL_TOL, ULP_TOL
+from tests.gpu_util import FLOOR_SHARE, ROW_REL_TOL, ULP_TOL
 
 pytestmark = pytest.mark.gpu
 
@@ -18,7 +19,7 @@ pytestmark = pytest.mark.gpu
 @pytest.fixture(autouse=True)
 def _clean_env():
     yield
-    os.environ.pop("MXFP6_FORCE_CFG", None)
+    hk.debug_option("MXFP6_FORCE_CFG", None)
 
 
 def _quantized(config, M, N, K, fmt, seed):
@@ -28,17 +29,29 @@ def _quantized(config, M, N, K, fmt, seed):
     return pa, sa, pb, sb
 
 
-def _check_rows(C, pa, sa, pb, sb, fmt, rows):
-    """Rows `rows` of the GPU result against the fp64 oracle (tolerances of the parity tests)."""
+def _check_rows(C, pa, sa, pb, sb, fmt, rows, block=1024):
+    """Rows `rows` of the GPU result against the fp64 oracle (tolerances of the parity tests), in blocks of rows."""
     Bd = torch.from_numpy(R.c_dequantize(pb, sb, fmt)).double()
-    Ad = torch.from_numpy(R.c_dequantize(pa[rows], sa[rows], fmt)).double()
-    ref = (Ad @ Bd.t()).numpy()
-    absdot = (Ad.abs() @ Bd.abs().t()).numpy()
-    got = C[torch.as_tensor(rows, device=C.device)].float().cpu().numpy()
-    assert not np.isnan(got).any()
-    rep = R.error_report(got, ref, absdot)
-    assert rep["row_rel"] <= ROW_REL_TOL and rep["max_ulp"] <= ULP_TOL, rep
-    return rep
+    Bd_abs = None
+    worst = dict(row_rel=0.0, max_ulp=0.0, n_floor=0)
+    rows = np.asarray(rows)
+    for i in range(0, len(rows), block):
+        rb = rows[i:i + block]
+        Ad = torch.from_numpy(R.c_dequantize(pa[rb], sa[rb], fmt)).double()
+        ref = (Ad @ Bd.t()).numpy()
+        got = C[torch.as_tensor(rb, device=C.device)].float().cpu().numpy()
+        assert not np.isnan(got).any()
+        rep = R.error_report(got, ref, None)
+        if rep["max_ulp"] > ULP_TOL:
+            # some element is more than ULP_TOL off: is it inside the accumulation noise floor of its own sum?
+            if Bd_abs is None:
+                Bd_abs = Bd.abs()
+            rep = R.error_report(got, ref, (Ad.abs() @ Bd_abs.t()).numpy())
+        assert rep["row_rel"] <= ROW_REL_TOL and rep["max_ulp"] <= ULP_TOL, rep
+        worst = dict(row_rel=max(worst["row_rel"], rep["row_rel"]), max_ulp=max(worst["max_ulp"], rep["max_ulp"]),
+                     n_floor=worst["n_floor"] + rep["n_floor"])
+    assert worst["n_floor"] <= int(FLOOR_SHARE * len(rows) * C.shape[1]), worst
+    return worst
 
 
 def _gpu(pa, sa, pb, sb, fmt):
@@ -52,11 +65,9 @@ def test_config_8192_cubed_lognormal():
     M = N = K = 8192
     pa, sa, pb, sb = _quantized("lognormal", M, N, K, R.E2M3, seed=0)
     C = _gpu(pa, sa, pb, sb, R.E2M3)
-    rows = np.sort(np.random.default_rng(0).choice(M, 48, replace=False))
-    rows[:4] = [0, 127, 128, M - 1]                        # tile edges
-    _check_rows(C, pa, sa, pb, sb, R.E2M3, np.sort(rows))
+    _check_rows(C, pa, sa, pb, sb, R.E2M3, np.arange(M))      # the whole matrix, as the reference's own check scans it (8_wave.cu:479-496)
     # the single-CTA kernel computes the same matrix
-    os.environ["MXFP6_FORCE_CFG"] = "256,0,0,0"
+    hk.debug_option("MXFP6_FORCE_CFG", "256,0,0,0")
     C1 = _gpu(pa, sa, pb, sb, R.E2M3)
     diff = (C.float() - C1.float()).abs()
     assert float((diff / C1.float().abs().clamp_min(1e-30)).max()) <= 2 ** -7, "pair and single-CTA kernels disagree by more than 1 bf16 ulp"
@@ -67,8 +78,9 @@ def test_config_ffn_e3m2_with_outlier_channels():
     M, N, K = 4096, 14336, 8192
     pa, sa, pb, sb = _quantized("ffn", M, N, K, R.E3M2, seed=0)
     C = _gpu(pa, sa, pb, sb, R.E3M2)
-    rows = np.sort(np.random.default_rng(1).choice(M, 24, replace=False))
-    _check_rows(C, pa, sa, pb, sb, R.E3M2, rows)
+    rows = np.sort(np.random.default_rng(1).choice(M, 512, replace=False))
+    rows[:4] = [0, 127, 128, M - 1]                        # tile edges
+    _check_rows(C, pa, sa, pb, sb, R.E3M2, np.sort(rows), block=512)
 
 
 @pytest.mark.parametrize("M", [1, 16, 64])
@@ -79,7 +91,7 @@ def test_config_decode_full(M):
     rows = np.arange(M) if M <= 16 else np.sort(np.random.default_rng(2).choice(M, 16, replace=False))
     _check_rows(C, pa, sa, pb, sb, R.E2M3, rows)
     # whole-tile kernel (no K split) gives the same result up to the summation order of split tiles
-    os.environ["MXFP6_FORCE_CFG"] = "%d,1,0" % (16 if M <= 16 else 64)
+    hk.debug_option("MXFP6_FORCE_CFG", "%d,1,0" % (16 if M <= 16 else 64))
     C1 = _gpu(pa, sa, pb, sb, R.E2M3)
     assert float(((C.float() - C1.float()).abs() / C1.float().abs().clamp_min(1e-30)).median()) == 0.0
     assert float((C != C1).float().mean()) < 2e-2
@@ -90,8 +102,8 @@ def test_config_sharded_one_shard():
     M, N, K = 16384, 7168, 8192
     pa, sa, pb, sb = _quantized("normal", M, N, K, R.E2M3, seed=3)
     C = _gpu(pa, sa, pb, sb, R.E2M3)
-    rows = np.sort(np.random.default_rng(3).choice(M, 32, replace=False))
-    _check_rows(C, pa, sa, pb, sb, R.E2M3, rows)
+    rows = np.sort(np.random.default_rng(3).choice(M, 512, replace=False))
+    _check_rows(C, pa, sa, pb, sb, R.E2M3, rows, block=512)
 
 
 # ------------------------------------------------------------------------------- size-independent properties

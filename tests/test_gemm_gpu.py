@@ -20,13 +20,13 @@ pytestmark = pytest.mark.gpu
 @pytest.fixture(autouse=True)
 def _clean_env():
     yield
-    os.environ.pop("MXFP6_FORCE_CFG", None)
-    os.environ.pop("MXFP6_NO_SF_TMA", None)
+    hk.debug_option("MXFP6_FORCE_CFG", None)
+    hk.debug_option("MXFP6_NO_SF_TMA", None)
 
 
 def _case(config, M, N, K, fmt=R.E2M3, seed=0, force=None, fmt_b=None):
     if force:
-        os.environ["MXFP6_FORCE_CFG"] = force
+        hk.debug_option("MXFP6_FORCE_CFG", force)
     pa, sa, pb, sb = quantized_inputs(config, M, N, K, fmt, seed, fmt_b)
     c = run_gpu(pa, sa, pb, sb, fmt, fmt_b)
     ref, absdot = oracle_f64(pa, sa, pb, sb, fmt, fmt_b)
@@ -50,7 +50,7 @@ def test_tma_image_of_packed_fp6():
 
 
 def test_single_tile_unit_scales():
-    os.environ["MXFP6_FORCE_CFG"] = "128,0,0"
+    hk.debug_option("MXFP6_FORCE_CFG", "128,0,0")
     pa, sa, pb, sb = quantized_inputs("normal", 128, 128, 128)
     sa[:] = 127
     sb[:] = 127
@@ -62,7 +62,7 @@ def test_single_tile_unit_scales():
 def test_identity_operand_exposes_layout():
     """B = identity-like one-hot rows: C[m,n] must reproduce A[m,n] exactly (any operand- or scale-layout
     mistake permutes or rescales it)."""
-    os.environ["MXFP6_FORCE_CFG"] = "128,0,0"
+    hk.debug_option("MXFP6_FORCE_CFG", "128,0,0")
     M = N = K = 256
     A, _ = R.make_inputs("lognormal", M, N, K, seed=5)
     pa, sa = R.quantize(A, R.E2M3)
@@ -73,7 +73,7 @@ def test_identity_operand_exposes_layout():
 
 
 def test_distinct_power_of_two_scales_per_block():
-    os.environ["MXFP6_FORCE_CFG"] = "128,0,0"
+    hk.debug_option("MXFP6_FORCE_CFG", "128,0,0")
     M, N, K = 128, 128, 1024
     pa, sa, pb, sb = quantized_inputs("normal", M, N, K, seed=2)
     rng = np.random.default_rng(0)
@@ -105,7 +105,7 @@ def test_ragged_n(N):
 
 
 def test_scale_plain_load_path():
-    os.environ["MXFP6_NO_SF_TMA"] = "1"
+    hk.debug_option("MXFP6_NO_SF_TMA", "1")
     _case("lognormal", 256, 256, 1024, seed=4)
 
 
@@ -172,7 +172,7 @@ def test_multi_destination_column_window(shape, force):
     """mxfp6_gemm_multi: the block lands in the same column window of every destination and nowhere else."""
     M, N, K = shape
     if force:
-        os.environ["MXFP6_FORCE_CFG"] = force
+        hk.debug_option("MXFP6_FORCE_CFG", force)
     pa, sa, pb, sb = quantized_inputs("lognormal", M, N, K, seed=11)
     t = [torch.from_numpy(x).cuda() for x in (pa, sa, pb, sb)]
     ldc, off = N + 264, 136
@@ -262,7 +262,7 @@ def _exact_inputs(M, N, K, seed):
 def test_requant_epilogue_bit_exact_on_exact_sums(out_fmt, shape, force):
     M, N, K = shape
     if force:
-        os.environ["MXFP6_FORCE_CFG"] = force
+        hk.debug_option("MXFP6_FORCE_CFG", force)
     A, B = _exact_inputs(M, N, K, seed=M + out_fmt)
     pa, sa = R.quantize(A, R.E2M3)
     pb, sb = R.quantize(B, R.E2M3)
@@ -325,7 +325,7 @@ def test_scaled_epilogue_bit_exact_on_exact_sums(shape, force, which):
     in every order the result must equal the same arithmetic done on the CPU, bit for bit."""
     M, N, K = shape
     if force:
-        os.environ["MXFP6_FORCE_CFG"] = force
+        hk.debug_option("MXFP6_FORCE_CFG", force)
     A, B = _exact_inputs(M, N, K, seed=7 * M + N)
     pa, sa = R.quantize(A, R.E2M3)
     pb, sb = R.quantize(B, R.E2M3)

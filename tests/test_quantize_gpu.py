@@ -15,9 +15,9 @@ pytestmark = pytest.mark.gpu
 def _quantiser_path(request):
     """Every test runs on both quantiser kernels: the TMA-fed streaming kernel (default) and the plain-load kernel."""
     if request.param == "quad":
-        os.environ["MXFP6_QUANT_PATH"] = "quad"
+        hk.debug_option("MXFP6_QUANT_PATH", "quad")
     yield
-    os.environ.pop("MXFP6_QUANT_PATH", None)
+    hk.debug_option("MXFP6_QUANT_PATH", None)
 
 
 @pytest.mark.parametrize("fmt", [R.E2M3, R.E4M3])

@@ -1,5 +1,7 @@
 """Column-parallel GEMM on 2+ GPUs: every rank's gathered C equals the single-GPU result bit for bit (same
-kernel, same tile arithmetic), for both exchanges.  Runs as child processes, one per GPU."""
+kernel, same tile arithmetic), for both exchanges.  Every step has its own A, a reader of C is queued behind
+each step without a host synchronisation, and the ranks take turns falling behind, so a step that overwrote a
+C still being read on a slower rank would show as a mismatch.  Runs as child processes, one per GPU."""
 import os
 import socket
 import subprocess
@@ -15,29 +17,48 @@ WORKER = r'''
 import os, sys, torch, torch.distributed as dist
 sys.path.insert(0, os.environ["MXFP6_ROOT"])
 import hipkittensp_b200 as hk
-from hipkittensp_b200.sharded import ColumnParallelGemm, shard_rows
+from hipkittensp_b200.sharded import ColumnParallelGemm, RowParallelGemm, shard_rows
 rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
 torch.cuda.set_device(rank); dev = torch.device("cuda", rank)
 dist.init_process_group("nccl", device_id=dev)
 M, N, K = 512, 2048, 1024
 g = torch.Generator(device=dev).manual_seed(5)
-A = torch.randn(M, K, device=dev, generator=g); B = torch.randn(N, K, device=dev, generator=g)
-pa, sa = hk.quantize(A); pb, sb = hk.quantize(B)
-want = hk.gemm(pa, sa, pb, sb)                      # single-GPU result of the whole problem
+B = torch.randn(N, K, device=dev, generator=g)
+pb, sb = hk.quantize(B)
+# a different A for every step, and the single-GPU result of each whole problem
+STEPS = 6
+ops, want = [], []
+for i in range(STEPS):
+    pa, sa = hk.quantize(torch.randn(M, K, device=dev, generator=g))
+    ops.append((pa, sa)); want.append(hk.gemm(pa, sa, pb, sb))
+def digest(C):
+    # a reader of C queued on the stream right behind the step (no host synchronisation in between)
+    return (C.view(torch.int16).to(torch.int64) * torch.arange(1, C.numel() + 1, device=dev).view_as(C)).sum()
+want_digest = [digest(w) for w in want]
 ok = True
-for mode in ("nccl", "fused"):
-    op = ColumnParallelGemm(M, N, K, device=dev, gather=mode)
-    for rep in range(2):
-        C = op(pa, sa, shard_rows(pb, world, rank), shard_rows(sb, world, rank))
-        torch.cuda.synchronize()
-        ok = ok and bool(torch.equal(C.view(torch.int16), want.view(torch.int16)))
-from hipkittensp_b200.sharded import RowParallelGemm
-for g in (False, True):
-    rp = RowParallelGemm(M, N, K, device=dev, gather=g)
-    out = rp(shard_rows(pa, world, rank), shard_rows(sa, world, rank), pb, sb)
+pbs, sbs = shard_rows(pb, world, rank), shard_rows(sb, world, rank)
+for mode, depth in (("nccl", 2), ("fused", 2), ("fused", 1)):
+    op = ColumnParallelGemm(M, N, K, device=dev, gather=mode, depth=depth)
+    got = []
+    for i in range(STEPS):
+        C = op(ops[i][0], ops[i][1], pbs, sbs)
+        got.append(digest(C))                 # the next step follows without waiting for this reader on the host
+        if rank == i % world:
+            torch.cuda._sleep(2000000)        # one rank falls behind: its peers run ahead into the next step
     torch.cuda.synchronize()
-    exp = want if g else want[rp.lo:rp.hi]
-    ok = ok and bool(torch.equal(out.view(torch.int16), exp.contiguous().view(torch.int16)))
+    ok = ok and all(int(a) == int(b) for a, b in zip(got, want_digest))
+    ok = ok and bool(torch.equal(C.view(torch.int16), want[-1].view(torch.int16)))
+for gth, depth in ((False, 2), (True, 2), (True, 1)):
+    rp = RowParallelGemm(M, N, K, device=dev, gather=gth, depth=depth)
+    got = []
+    for i in range(STEPS):
+        out = rp(shard_rows(ops[i][0], world, rank), shard_rows(ops[i][1], world, rank), pb, sb)
+        exp = want[i] if gth else want[i][rp.lo:rp.hi]
+        got.append((digest(out.contiguous()), digest(exp.contiguous())))
+        if rank == i % world:
+            torch.cuda._sleep(2000000)
+    torch.cuda.synchronize()
+    ok = ok and all(int(a) == int(b) for a, b in got)
 assert hk.device_status() == 0
 flag = torch.tensor([1 if ok else 0], device=dev)
 dist.all_reduce(flag, op=dist.ReduceOp.MIN)
