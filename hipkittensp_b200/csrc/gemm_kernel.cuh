@@ -35,7 +35,10 @@ enum : int {
 struct GemmParams {
     int p_rows, q_rows;        // valid rows of P and Q
     int kblocks;               // K / 128
-    int tiles_p, tiles_q;      // ceil(p_rows/128), ceil(q_rows/BN)
+    int tiles_p, tiles_q;      // ceil(p_rows/p_tile_rows), ceil(q_rows/q_tile_rows)
+    int p_tile_rows;           // rows of P one tile covers (<= 128; 128 unless the rows of a streamed operand are dealt evenly to the CTAs)
+    int q_tile_rows;           // rows of Q one tile covers (<= BN)
+    int raw_tx_bytes;          // bytes the two scale-slab loads of a group report to their mbarrier
     int ldc;                   // row stride of C in elements (= N)
     int c_rows, c_cols;        // M, N
     uint32_t idesc;            // instruction descriptor without scale ids
@@ -47,6 +50,7 @@ struct GemmParams {
     __nv_bfloat16* c;          // first element of this GEMM's block inside destination 0 (row stride ldc)
     __nv_bfloat16* c_more[7];  // the same position in further destinations (peer GPUs' copies of C)
     int ndst;                  // number of destinations, 1..8
+    int c_tma;                 // pair kernel: C is stored by TMA (16-byte aligned destinations and row stride); else by plain stores
     uint8_t* q_out;            // re-quantised output instead of bf16 C: operand bytes [M, 3N/4 or N] ...
     uint8_t* q_scales;         // ... and E8M0 scales [M, N/32], blocks of 32 along N
     long long q_ld;            // row stride of q_out in bytes
@@ -57,6 +61,9 @@ struct GemmParams {
     int* status;               // device status word
     unsigned long long wait_cycles;  // budget of one wait in clock cycles
     int group_p;               // pair kernel: P-tiles per rasterisation group
+    int tail_first;            // pair kernel: first tile of the last partial wave that is cut into column slices (= tile count if none)
+    int tail_split;            // pair kernel: slices per such tile (1, 2 or 4)
+    int stage_tx_bytes_tail;   // pair kernel: bytes one CTA's loads of a slice's stage report
     int early_p;               // swapped form: P (the weights) may be read before the preceding kernel has finished
     int l2_load, l2_store;     // L2 eviction policy of the operand loads / of the stores of C (0 normal, 1 evict_first, 2 evict_last)
     // optional fp32 epilogue, applied to the finished sum before it is rounded (null = absent):
@@ -122,30 +129,34 @@ __device__ __forceinline__ void affine_chunk(const GemmParams& P, uint32_t (&v)[
     }
 }
 
-template <int BN_, bool SWAP_, bool STREAMK_>
+// CTAS_ = 2: a smaller pipeline so that two CTAs share an SM (BN <= 32: half the shared memory, a quarter of TMEM each).
+template <int BN_, bool SWAP_, bool STREAMK_, int CTAS_ = 1>
 struct GemmCfg {
     static constexpr int BN = BN_;
     static constexpr bool SWAP = SWAP_;
     static constexpr bool STREAMK = STREAMK_;
+    static constexpr int CTAS = CTAS_;
     static constexpr int BM = 128;
     static constexpr int BK = 128;                       // elements of K per pipeline stage (= bytes in smem)
     static constexpr int P_BYTES = BM * BK;
     static constexpr int Q_BYTES = BN * BK;
     static constexpr int STAGE_BYTES = P_BYTES + Q_BYTES;
-    static constexpr int STAGES = BN >= 256 ? 4 : BN >= 128 ? 6 : BN >= 64 ? 8 : BN >= 32 ? 9 : 11;
+    static constexpr int STAGES = CTAS_ == 2 ? (BN <= 16 ? 5 : 4)
+                                             : BN >= 256 ? 4 : BN >= 128 ? 6 : BN >= 64 ? 8 : BN >= 32 ? 9 : 11;
     static constexpr int LOAD_BATCH = SWAP_ ? (STAGES >= 8 ? 4 : 2) : 1;   // K-blocks the producer requests together
     static constexpr int QATOMS = (BN + 127) / 128;      // 128-row scale atoms on the Q side
-    static constexpr int RAW_SLOTS = BN >= 256 ? 2 : 4;  // each raw slab covers 4 K-blocks (16 scale bytes per row)
+    static constexpr int RAW_SLOTS = (BN >= 256 || CTAS_ == 2) ? 2 : 4;  // each raw slab covers 4 K-blocks (16 scale bytes per row)
     static constexpr int RAW_Q_ROWS = BN < 32 ? 32 : BN;
     static constexpr int RAW_BYTES = (BM + RAW_Q_ROWS) * 16;
-    static constexpr int RAW_TX_BYTES = (BM + BN) * 16;
     static constexpr int ATOM_BYTES = 512 * (1 + QATOMS);  // scale atoms of one K-block: P atom + Q atoms
     static constexpr int GROUP_BYTES = 4 * ATOM_BYTES;     // a group = the 4 K-blocks one raw slab covers
-    static constexpr int ATOM_GROUPS = BN >= 256 ? 3 : 4;
+    static constexpr int ATOM_GROUPS = (BN >= 256 || CTAS_ == 2) ? 3 : 4;
     static constexpr bool OVERLAP = BN == 256;           // two 256-column accumulators share 32 columns
     static constexpr int ACC_COL1 = OVERLAP ? 224 : BN;
     static constexpr int SF_COL = OVERLAP ? 480 : 2 * BN;
-    static constexpr int TMEM_COLS = 512;
+    // two CTAs of an SM share its 512 columns: each takes the power of two that holds its two accumulators and 32 scale columns
+    static constexpr int TMEM_COLS = CTAS_ == 2 ? (2 * BN + 32 <= 64 ? 64 : 2 * BN + 32 <= 128 ? 128 : 256) : 512;
+    static_assert(CTAS_ == 1 || (CTAS_ == 2 && BN <= 64 && !STREAMK_), "two CTAs per SM: small accumulators, whole tiles");
     static constexpr int NUM_BARS = 2 * STAGES + 2 * RAW_SLOTS + 2 * ATOM_GROUPS + 5;
     // unswapped form: column scale and bias of the current tile for the fp32 epilogue (2 x BN floats, 16-byte aligned)
     static constexpr int AFF_BYTES = SWAP ? 0 : 2 * BN * 4 + 16;
@@ -154,7 +165,7 @@ struct GemmCfg {
     static constexpr int SMEM_ALLOC = SMEM_BYTES + 1024;  // slack for the 1024-byte alignment of the operand ring
     static constexpr int THREADS = 256;
     static constexpr int GROUP_P = 8;                     // tile rasterisation: groups of 8 P-tiles share Q-tiles
-    static_assert(SMEM_ALLOC <= 232448, "exceeds the 227 KiB of shared memory a CTA can have");
+    static_assert(SMEM_ALLOC <= 232448 / CTAS_ - (CTAS_ == 2 ? 1024 : 0), "exceeds the shared memory this CTA can have");
 };
 
 // One unit of work of a CTA: a K range of one output tile.
@@ -191,8 +202,8 @@ struct SegIter {
         int group = t / per_group, in = t % per_group;
         int first_p = group * Cfg::GROUP_P;
         int gsz = min(P.tiles_p - first_p, Cfg::GROUP_P);
-        p0 = (first_p + in % gsz) * Cfg::BM;
-        q0 = (in / gsz) * Cfg::BN;
+        p0 = (first_p + in % gsz) * P.p_tile_rows;
+        q0 = (in / gsz) * P.q_tile_rows;
     }
     __device__ bool next(Segment& s) {
         if (Cfg::STREAMK) {
@@ -262,7 +273,7 @@ __device__ __forceinline__ bool wait_bar_warp(uint32_t bar, uint32_t parity, vol
 
 
 template <class Cfg>
-__global__ void __launch_bounds__(Cfg::THREADS, 1)
+__global__ void __launch_bounds__(Cfg::THREADS, Cfg::CTAS)
 mxfp6_gemm_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__ CUtensorMap tm_q,
                   const __grid_constant__ CUtensorMap tm_sfp, const __grid_constant__ CUtensorMap tm_sfq,
                   const GemmParams P) {
@@ -340,7 +351,7 @@ mxfp6_gemm_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constan
                     if (P.sf_tma && (k == s2.k0 || (k & 3) == 0)) {
                         if (slabs && pre_raw < (uint32_t)Cfg::RAW_SLOTS) {
                             if (elect_one_sync()) {
-                                mbar_arrive_expect_tx(bar_raw_full(pre_raw), Cfg::RAW_TX_BYTES);
+                                mbar_arrive_expect_tx(bar_raw_full(pre_raw), (uint32_t)P.raw_tx_bytes);
                                 tma_load_2d(raw_base + pre_raw * Cfg::RAW_BYTES, &tm_sfp, bar_raw_full(pre_raw), (k >> 2) * 16, s2.p0);
                             }
                             ++pre_raw;
@@ -373,7 +384,7 @@ mxfp6_gemm_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constan
                         if (elect_one_sync()) {
                             const uint32_t dst = raw_base + r * Cfg::RAW_BYTES;
                             if (n_raw >= pre_raw) {
-                                mbar_arrive_expect_tx(bar_raw_full(r), Cfg::RAW_TX_BYTES);
+                                mbar_arrive_expect_tx(bar_raw_full(r), (uint32_t)P.raw_tx_bytes);
                                 tma_load_2d(dst, &tm_sfp, bar_raw_full(r), (k >> 2) * 16, sg.p0);
                             }
                             tma_load_2d(dst + Cfg::BM * 16, &tm_sfq, bar_raw_full(r), (k >> 2) * 16, sg.q0);
@@ -620,7 +631,8 @@ mxfp6_gemm_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constan
                                           qc + i, sg.p0 + quad * 32, qc + i < P.c_rows && sg.p0 + quad * 32 < P.c_cols);
                 } else if (Cfg::SWAP) {
                     // D[p,q] -> C[q,p]: consecutive lanes write consecutive bf16 of one C row
-                    if (p < P.c_cols) {
+                    // (rows past the tile's own rows belong to the next tile)
+                    if (p < P.c_cols && prow < P.p_tile_rows) {
 #pragma unroll
                         for (int i = 0; i < CW; ++i)
                             if (qc + i < P.c_rows)
@@ -633,14 +645,16 @@ mxfp6_gemm_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constan
                             quant_store32(v, P.q_fmt, P.q_out, (size_t)P.q_ld, P.q_scales, P.c_cols, p, qc);
                     }
                 } else {
+                    // columns past the tile's own columns belong to the next tile
+                    const int q_lim = min(P.c_cols, sg.q0 + P.q_tile_rows);
                     if (p < P.c_rows)
                     for (int d = 0; d < P.ndst; ++d) {          // every destination gets the tile (d > 0: peer memory)
                         __nv_bfloat16* cbase = d == 0 ? P.c : P.c_more[d - 1];
                         __nv_bfloat16* dst = cbase + (size_t)p * P.ldc + qc;
-                        const bool vec = ((P.ldc & 7) == 0) && ((reinterpret_cast<uintptr_t>(cbase) & 15) == 0);
+                        const bool vec = ((P.ldc & 7) == 0) && ((reinterpret_cast<uintptr_t>(cbase) & 15) == 0) && ((P.q_tile_rows & 7) == 0);
 #pragma unroll
                         for (int i = 0; i < CW; i += 8) {
-                            if (vec && qc + i + 8 <= P.c_cols) {
+                            if (vec && qc + i + 8 <= q_lim) {
                                 uint4 o;
                                 o.x = pack_bf16x2(__uint_as_float(v[i + 0]), __uint_as_float(v[i + 1]));
                                 o.y = pack_bf16x2(__uint_as_float(v[i + 2]), __uint_as_float(v[i + 3]));
@@ -650,7 +664,7 @@ mxfp6_gemm_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constan
                             } else {
 #pragma unroll
                                 for (int e = 0; e < 8; ++e)
-                                    if (qc + i + e < P.c_cols) dst[i + e] = __float2bfloat16_rn(__uint_as_float(v[i + e]));
+                                    if (qc + i + e < q_lim) dst[i + e] = __float2bfloat16_rn(__uint_as_float(v[i + e]));
                             }
                         }
                     }

@@ -92,8 +92,33 @@ __device__ __forceinline__ void pair_coords(const GemmParams& P, int t, int& p0,
     q0 = (in / gsz) * 256;
 }
 
+// One unit of work of a pair: a whole 256x256 tile, or, in the last partial wave of a problem, a 256 x 128 or 256 x 64
+// column slice of one, so that the tiles that are left over when the tile count is not a multiple of the number of
+// pairs spread over more pairs.  A slice is an independent piece of C with the full K loop: nothing is summed across
+// units, and every element is accumulated exactly as in a whole tile.
+struct PairUnit {
+    int p0, q0;      // first row of A / first row of B (column of C) of the unit
+    int ncols;       // columns of C: 256, 128 or 64
+};
+// Unit number `it` of cluster `cluster_id`; false when the cluster has no more work.
+__device__ __forceinline__ bool pair_unit(const GemmParams& P, int it, int cluster_id, int n_clusters, PairUnit& u) {
+    const int t = cluster_id + it * n_clusters;
+    if (t < P.tail_first) {
+        pair_coords(P, t, u.p0, u.q0);
+        u.ncols = 256;
+        return true;
+    }
+    const int idx = t - P.tail_first;               // slices of the left-over tiles, tile-major
+    if (idx >= (P.tiles_p * P.tiles_q - P.tail_first) * P.tail_split) return false;
+    pair_coords(P, P.tail_first + idx / P.tail_split, u.p0, u.q0);
+    u.ncols = 256 / P.tail_split;
+    u.q0 += (idx % P.tail_split) * u.ncols;
+    return true;
+}
+
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PairCfg::THREADS, 1)
 mxfp6_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__ CUtensorMap tm_q,
+                       const __grid_constant__ CUtensorMap tm_q_tail,
                        const __grid_constant__ CUtensorMap tm_sfp, const __grid_constant__ CUtensorMap tm_sfq,
                        const __grid_constant__ CMaps cmaps, const GemmParams P) {
     using Cfg = PairCfg;
@@ -127,7 +152,6 @@ mxfp6_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_co
     const uint32_t rank = cluster_ctarank();              // 0 = even CTA (issues the MMAs), 1 = its peer
     const bool leader = rank == 0;
     const int cluster_id = blockIdx.x >> 1, n_clusters = gridDim.x >> 1;
-    const int num_tiles = P.tiles_p * P.tiles_q;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < Cfg::STAGES; ++s) { mbar_init(bar_full(s), 1); mbar_init(bar_empty(s), 1); }
@@ -140,6 +164,7 @@ mxfp6_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_co
     }
     if (warp == 0 && lane == 0) {
         tma_prefetch_desc(&tm_p); tma_prefetch_desc(&tm_q); tma_prefetch_desc(&tm_sfp); tma_prefetch_desc(&tm_sfq);
+        if (P.tail_split > 1) tma_prefetch_desc(&tm_q_tail);
     }
     if (warp == 1) {
         tmem_alloc_pair(smem_u32(tmem_slot), Cfg::TMEM_COLS);
@@ -160,12 +185,16 @@ mxfp6_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_co
         uint32_t n_stage = 0, n_raw = 0;
         bool ok = true;
         const uint64_t pol_ld = l2_policy(P.l2_load);
-        for (int tile = cluster_id; tile < num_tiles && ok; tile += n_clusters) {
-            int p0, q0;
-            pair_coords(P, tile, p0, q0);
-            const int my_p = p0 + 128 * (int)rank, my_q = q0 + 128 * (int)rank;
+        PairUnit u;
+        for (int it = 0; ok && pair_unit(P, it, cluster_id, n_clusters, u); ++it) {
+            const int p0 = u.p0, q0 = u.q0;
+            const bool whole = u.ncols == 256;
+            // each CTA brings its 128 rows of A and its half of the unit's rows of B
+            const int my_p = p0 + 128 * (int)rank, my_q = q0 + (u.ncols >> 1) * (int)rank;
+            const CUtensorMap* tq = whole ? &tm_q : &tm_q_tail;
+            const uint32_t tx = whole ? (uint32_t)P.stage_tx_bytes : (uint32_t)P.stage_tx_bytes_tail;
             for (int kb = 0; kb < P.kblocks && ok; ++kb) {
-                if ((kb & 3) == 0) {
+                if (P.sf_tma && (kb & 3) == 0) {
                     const int r = n_raw % Cfg::RAW_SLOTS;
                     ok = wait_bar_warp(bar_raw_empty(r), ((n_raw / Cfg::RAW_SLOTS) & 1) ^ 1, abort_flag, P, kStatusTimeoutProducer);
                     if (!ok) break;
@@ -184,9 +213,9 @@ mxfp6_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_co
                     const uint32_t dst = stage_base + s * Cfg::STAGE_BYTES;
                     const uint32_t full0 = mapa_shared(bar_full(s), 0);
                     // the even CTA announces the bytes of both CTAs' loads for this stage
-                    if (leader) mbar_arrive_expect_tx(bar_full(s), 2u * (uint32_t)P.stage_tx_bytes);
+                    if (leader) mbar_arrive_expect_tx(bar_full(s), 2u * tx);
                     tma_load_2d_pair_hint(dst, &tm_p, full0, kb * Cfg::BK, my_p, pol_ld);
-                    tma_load_2d_pair_hint(dst + Cfg::P_BYTES, &tm_q, full0, kb * Cfg::BK, my_q, pol_ld);
+                    tma_load_2d_pair_hint(dst + Cfg::P_BYTES, tq, full0, kb * Cfg::BK, my_q, pol_ld);
                 }
                 __syncwarp();
                 ++n_stage;
@@ -199,9 +228,12 @@ mxfp6_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_co
         if (leader) {
             uint32_t n_kb = 0, n_seg = 0, n_grp = 0;
             bool ok = true;
-            for (int tile = cluster_id; tile < num_tiles && ok; tile += n_clusters) {
+            PairUnit u;
+            for (int it = 0; ok && pair_unit(P, it, cluster_id, n_clusters, u); ++it) {
                 const int b = n_seg & 1;
                 const uint32_t acc = tmem_base + (b ? Cfg::ACC_COL1 : 0);
+                // the instruction's N is the unit's column count (bits 17..22 hold N / 8)
+                const uint32_t idesc = (P.idesc & ~(0x3fu << 17)) | ((uint32_t)(u.ncols >> 3) << 17);
                 if (n_seg > 0) ok = wait_bar_cluster_warp(bar_ovl, (n_seg - 1) & 1, abort_flag, P, kStatusTimeoutMma);
                 if (!ok) break;
                 tc_fence_after();
@@ -227,7 +259,7 @@ mxfp6_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_co
                         const uint64_t bdesc = smem_desc_sw128(sp + Cfg::P_BYTES);
 #pragma unroll
                         for (uint32_t k = 0; k < 4; ++k) {
-                            mma_mxf8f6f4_pair(acc, adesc + 2 * k, bdesc + 2 * k, idesc_with_sf(P.idesc, k),
+                            mma_mxf8f6f4_pair(acc, adesc + 2 * k, bdesc + 2 * k, idesc_with_sf(idesc, k),
                                               sfa | (k << 30), sfb | (k << 30), (kb > 0 || k > 0) ? 1u : 0u);
                         }
                         tc_commit_pair(bar_empty(s), 3);
@@ -251,25 +283,48 @@ mxfp6_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_co
     else if (warp == 2 || warp == 3) {
         uint32_t n_grp = 0;
         bool ok = true;
-        for (int tile = cluster_id; tile < num_tiles && ok; tile += n_clusters) {
+        PairUnit u;
+        for (int it = 0; ok && pair_unit(P, it, cluster_id, n_clusters, u); ++it) {
             for (int kb = 0; kb < P.kblocks && ok; kb += 4, ++n_grp) {
                 if ((int)(n_grp & 1) != warp - 2) continue;
                 uint32_t rp[4][4], rq[8][4];
-                const int r = n_grp % Cfg::RAW_SLOTS;
-                ok = wait_bar_warp(bar_raw_full(r), (n_grp / Cfg::RAW_SLOTS) & 1, abort_flag, P, kStatusTimeoutScale);
-                if (!ok) break;
-                const uint8_t* raw = smem_gen + (raw_base - smem_base) + r * Cfg::RAW_BYTES;
+                if (P.sf_tma) {
+                    const int r = n_grp % Cfg::RAW_SLOTS;
+                    ok = wait_bar_warp(bar_raw_full(r), (n_grp / Cfg::RAW_SLOTS) & 1, abort_flag, P, kStatusTimeoutScale);
+                    if (!ok) break;
+                    const uint8_t* raw = smem_gen + (raw_base - smem_base) + r * Cfg::RAW_BYTES;
 #pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    const uint4 v = *reinterpret_cast<const uint4*>(raw + (lane + 32 * c) * 16);
-                    rp[c][0] = v.x; rp[c][1] = v.y; rp[c][2] = v.z; rp[c][3] = v.w;
-                }
+                    for (int c = 0; c < 4; ++c) {
+                        const uint4 v = *reinterpret_cast<const uint4*>(raw + (lane + 32 * c) * 16);
+                        rp[c][0] = v.x; rp[c][1] = v.y; rp[c][2] = v.z; rp[c][3] = v.w;
+                    }
 #pragma unroll
-                for (int c = 0; c < 8; ++c) {
-                    const uint4 v = *reinterpret_cast<const uint4*>(raw + Cfg::BM * 16 + (lane + 32 * c) * 16);
-                    rq[c][0] = v.x; rq[c][1] = v.y; rq[c][2] = v.z; rq[c][3] = v.w;
+                    for (int c = 0; c < 8; ++c) {
+                        const uint4 v = *reinterpret_cast<const uint4*>(raw + Cfg::BM * 16 + (lane + 32 * c) * 16);
+                        rq[c][0] = v.x; rq[c][1] = v.y; rq[c][2] = v.z; rq[c][3] = v.w;
+                    }
+                    mbar_arrive(bar_raw_empty(r));
+                } else {
+                    // scale rows that cannot be TMA boxes (K/32 not a multiple of 16, or unaligned arrays): the 4-byte
+                    // words of the group's K-blocks are read from global memory directly
+                    const int p0 = u.p0, q0 = u.q0;
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        const int row = p0 + 128 * (int)rank + lane + 32 * c;
+#pragma unroll
+                        for (int jj = 0; jj < 4; ++jj)
+                            rp[c][jj] = (row < P.p_rows && kb + jj < P.kblocks)
+                                ? __ldg(reinterpret_cast<const uint32_t*>(P.sfp + (size_t)row * P.sf_ld + (kb + jj) * 4)) : 0u;
+                    }
+#pragma unroll
+                    for (int c = 0; c < 8; ++c) {
+                        const int row = q0 + lane + 32 * c;
+#pragma unroll
+                        for (int jj = 0; jj < 4; ++jj)
+                            rq[c][jj] = (row < P.q_rows && kb + jj < P.kblocks)
+                                ? __ldg(reinterpret_cast<const uint32_t*>(P.sfq + (size_t)row * P.sf_ld + (kb + jj) * 4)) : 0u;
+                    }
                 }
-                mbar_arrive(bar_raw_empty(r));
                 const int g = n_grp % Cfg::ATOM_GROUPS;
                 ok = wait_bar_warp(bar_atom_empty(g), ((n_grp / Cfg::ATOM_GROUPS) & 1) ^ 1, abort_flag, P, kStatusTimeoutScale);
                 if (!ok) break;
@@ -297,9 +352,9 @@ mxfp6_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_co
         bool ok = true;
         const uint32_t ovl0 = mapa_shared(bar_ovl, 0);
         const uint64_t pol_st = l2_policy(P.l2_store);
-        for (int tile = cluster_id; tile < num_tiles && ok; tile += n_clusters) {
-            int p0, q0;
-            pair_coords(P, tile, p0, q0);
+        PairUnit u;
+        for (int it = 0; ok && pair_unit(P, it, cluster_id, n_clusters, u); ++it) {
+            const int p0 = u.p0, q0 = u.q0;
             const int b = n_seg & 1;
             const int my_p0 = p0 + 128 * (int)rank;
             const bool affine = has_affine(P);
@@ -324,7 +379,7 @@ mxfp6_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_co
             }
             const uint32_t tacc = tmem_base + ((uint32_t)(quad * 32) << 16) + (b ? Cfg::ACC_COL1 : 0);
             constexpr int OC = Cfg::OUT_COLS;                 // columns per piece
-            constexpr int NP = 256 / OC;
+            const int NP = u.ncols / OC;
 #pragma unroll 1
             for (int ci = 0; ci < NP; ++ci) {
                 // the piece that holds the 32 columns shared by the two accumulators goes first
@@ -415,6 +470,31 @@ mxfp6_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_co
                     const uint32_t x3 = pack_bf16x2(__uint_as_float(v[8 * c + 6]), __uint_as_float(v[8 * c + 7]));
                     asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};"
                                  ::"r"(rowaddr + ((c ^ sw) << 4)), "r"(x0), "r"(x1), "r"(x2), "r"(x3) : "memory");
+                }
+                if (!P.c_tma) {
+                    // C whose rows are not 16-byte multiples cannot be a TMA destination: the staged piece is written out
+                    // with plain stores, a warp per row at a time (32 lanes x 2 columns = the row's 128 bytes)
+                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                    const uint8_t* stage = smem_gen + (buf - smem_base);
+                    const int col = q0 + piece * OC + 2 * lane;
+#pragma unroll 4
+                    for (int r = quad * 32; r < quad * 32 + 32; ++r) {
+                        const int row = my_p0 + r;
+                        if (row >= P.c_rows) break;
+                        const uint32_t x = *reinterpret_cast<const uint32_t*>(stage + r * (OC * 2) + ((((lane >> 2) ^ (r & 7)) << 4) | ((lane & 3) << 2)));
+                        for (int d = 0; d < P.ndst; ++d) {
+                            __nv_bfloat16* dst = (d == 0 ? P.c : P.c_more[d - 1]) + (size_t)row * P.ldc + col;
+                            if (col + 1 < P.c_cols && (reinterpret_cast<uintptr_t>(dst) & 3) == 0) {
+                                *reinterpret_cast<uint32_t*>(dst) = x;
+                            } else {
+                                if (col < P.c_cols) dst[0] = __ushort_as_bfloat16((unsigned short)(x & 0xffffu));
+                                if (col + 1 < P.c_cols) dst[1] = __ushort_as_bfloat16((unsigned short)(x >> 16));
+                            }
+                        }
+                    }
+                    // (the next use of this buffer is two pieces away, behind the barrier that opens every piece)
+                    ++n_out;
+                    continue;
                 }
                 fence_proxy_async_smem();
                 asm volatile("bar.sync 1, 128;" ::: "memory");

@@ -210,6 +210,9 @@ static uint32_t fmt_mma_code(int f) {      // operand format field of kind::mxf8
 struct Plan {
     int bn; bool swap; bool streamk;
     bool pair;                  // CTA-pair kernel (256x256 tile per cluster of 2)
+    int ctas;                   // CTAs per SM the kernel variant is built for (1 or 2)
+    int p_tile, q_tile;         // rows of P / Q one tile covers (128 / bn unless a streamed operand's rows are dealt evenly to the CTAs)
+    int tail_first, tail_split; // pair kernel: first tile of the last partial wave and the number of column slices its tiles are cut into
     int grid;
     int tiles_p, tiles_q;
     int ws_slots;
@@ -221,8 +224,10 @@ static int ceil_div(int64_t a, int64_t b) { return (int)((a + b - 1) / b); }
 // Most output tiles a problem may have and still split tiles along K (bounds the counter region).
 constexpr int64_t kMaxSplitTiles = 65536;
 
-static Plan make_plan(int64_t M, int64_t N, int64_t K, int sm_count, bool allow_pair = true, bool plain = false) {
+static Plan make_plan(int64_t M, int64_t N, int64_t K, int sm_count, bool allow_pair = true, bool plain = false,
+                      bool even_rows_ok = true) {
     Plan p{};
+    p.ctas = 1;
     const Options& o = options();
     const int kb = (int)(K / 128);
     const int fbn = o.force_bn, fswap = o.force_swap, fsk = o.force_sk, fpair = o.force_pair;
@@ -246,11 +251,11 @@ static Plan make_plan(int64_t M, int64_t N, int64_t K, int sm_count, bool allow_
     }
     // one 256x256 tile per CTA pair as soon as that occupies at least half of the pairs (measured: 2048^3 with
     // 64 pair tiles runs in 11.6 us against 17 us with 128x128 tiles)
-    p.pair = !p.swap && !wide_rows && N >= 256 && (K / 32) % 16 == 0 &&
+    p.pair = !p.swap && !wide_rows && N >= 256 &&
              (int64_t)ceil_div(M, 256) * ceil_div(N, 256) >= sm_count / 4;
     if (fbn) { p.bn = fbn; p.pair = false; }
     if (fpair >= 0) p.pair = fpair != 0;
-    if (!allow_pair) p.pair = false;      // the pair kernel takes its scales by TMA only
+    if (!allow_pair) p.pair = false;
     if (p.pair) { p.bn = 256; p.swap = false; p.streamk = false; }
     if (fswap >= 0 && !p.pair) p.swap = fswap != 0;
     if (fsk >= 0 && !p.pair) p.streamk = fsk != 0;
@@ -260,13 +265,41 @@ static Plan make_plan(int64_t M, int64_t N, int64_t K, int sm_count, bool allow_
         if (t > kMaxSplitTiles) p.streamk = false;
     }
     const int64_t prow = p.swap ? N : M, qrow = p.swap ? M : N;
-    p.tiles_p = ceil_div(prow, p.pair ? 256 : 128);
-    p.tiles_q = ceil_div(qrow, p.bn);
+    p.p_tile = p.pair ? 256 : 128;
+    p.q_tile = p.bn;
+    // Skinny M with many weight rows: instead of 128-row tiles split along K, the weight rows are dealt evenly to the
+    // CTAs, each CTA runs the whole K loop over its own rows and stores its block of C itself -- no partial sums, no
+    // arrival counters, every CTA streams the same number of bytes.  M <= 32: swapped form, two CTAs per SM (97 rows
+    // each at N = 28672).  32 < M <= 128: unswapped 128 x 256 tiles whose column count is N / SMs rounded up to 8.
+    const bool forced = fbn || fswap >= 0 || fsk >= 0 || fpair >= 0;
+    if (even_rows_ok && o.decode_rows && !forced && !p.pair && !plain) {
+        if (p.swap && p.bn <= 32) {
+            const int64_t slots = 2 * (int64_t)sm_count;
+            const int64_t waves = ceil_div(N, slots * 128);
+            const int64_t rows = ceil_div(N, slots * waves);
+            if (rows >= 48) { p.streamk = false; p.ctas = 2; p.p_tile = (int)rows; }
+        } else if (!p.swap && wide_rows && p.bn == 256) {
+            const int64_t waves = ceil_div(N, (int64_t)sm_count * 256);
+            const int64_t rows = (ceil_div(N, (int64_t)sm_count * waves) + 7) / 8 * 8;
+            if (rows >= 128 && rows <= 256) p.q_tile = (int)rows;
+        }
+    }
+    p.tiles_p = ceil_div(prow, p.p_tile);
+    p.tiles_q = ceil_div(qrow, p.q_tile);
     const int64_t tiles = (int64_t)p.tiles_p * p.tiles_q;
+    p.tail_first = (int)tiles; p.tail_split = 1;
     if (p.pair) {
         const int64_t clusters = tiles < sm_count / 2 ? tiles : sm_count / 2;
         p.grid = (int)(2 * clusters);
         p.ws_slots = 0; p.ws_counter_bytes = 0; p.ws_bytes = 0;
+        // The tiles left over after the last full wave occupy only some of the pairs for a whole tile's time.  When
+        // they are at most half (a quarter) as many as the pairs, each is cut into 2 (4) column slices of 128 (64)
+        // columns, which run side by side (4096^3: 256 tiles on 74 pairs = 3 waves + 34 tiles -> 68 slices).
+        const int64_t left = tiles % clusters;
+        if (o.tail_split && tiles > clusters && left > 0 && 2 * left <= clusters) {
+            p.tail_split = 4 * left <= clusters ? 4 : 2;
+            p.tail_first = (int)(tiles - left);
+        }
     } else if (p.streamk) {
         const int64_t U = tiles * kb;
         int64_t g = U / 4; if (g < 1) g = 1;
@@ -280,7 +313,8 @@ static Plan make_plan(int64_t M, int64_t N, int64_t K, int sm_count, bool allow_
         p.ws_counter_bytes = (size_t)kMaxSplitTiles * 4;
         p.ws_bytes = p.ws_counter_bytes + (size_t)tiles * maxseg * (size_t)p.bn * 128 * 4;
     } else {
-        p.grid = (int)(tiles < sm_count ? tiles : sm_count);
+        const int64_t resident = (int64_t)sm_count * p.ctas;
+        p.grid = (int)(tiles < resident ? tiles : resident);
         p.ws_slots = 0; p.ws_counter_bytes = 0; p.ws_bytes = 0;
     }
     return p;
@@ -315,9 +349,12 @@ static bool dest_by_tma(const Dest& dst) {
     for (int i = 0; i < dst.n; ++i) ok = ok && !((uintptr_t)dst.c[i] & 15);
     return ok;
 }
-static Plan plan_for(const void* sfa, const void* sfb, const Dest& dst, int64_t M, int64_t N, int64_t K, int sm_count) {
-    // several destinations are written untransposed from whole tiles
-    return make_plan(M, N, K, sm_count, scales_by_tma(sfa, sfb, K) && dest_by_tma(dst), dst.n > 1);
+static Plan plan_for(const void* sfa, const void* sfb, const Dest& dst, int64_t M, int64_t N, int64_t K, int sm_count,
+                     bool requant = false) {
+    // several destinations are written untransposed from whole tiles; a re-quantised result needs tiles that start on
+    // multiples of 32 rows and columns
+    (void)sfa; (void)sfb; (void)dst;
+    return make_plan(M, N, K, sm_count, true, dst.n > 1, !requant);
 }
 
 // Everything a call passes in.  Two calls with equal keys launch the same kernel with the same arguments, so the
@@ -341,7 +378,7 @@ struct Recipe {
     bool pair = false, pdl = true;
     size_t counter_bytes = 0;    // built-in scratch: counters to clear before every launch
     void* counter_ptr = nullptr;
-    CUtensorMap tp, tq, tsp, tsq;
+    CUtensorMap tp, tq, tq_tail, tsp, tsq;
     CMaps cm;
     GemmParams P;
 };
@@ -370,7 +407,7 @@ static int launch_recipe(const Recipe& r, cudaStream_t st) {
     lc.attrs = &attr;
     lc.numAttrs = r.pdl ? 1 : 0;
     if (r.pair) {
-        void* args[] = {(void*)&r.tp, (void*)&r.tq, (void*)&r.tsp, (void*)&r.tsq, (void*)&r.cm, (void*)&r.P};
+        void* args[] = {(void*)&r.tp, (void*)&r.tq, (void*)&r.tq_tail, (void*)&r.tsp, (void*)&r.tsq, (void*)&r.cm, (void*)&r.P};
         CUDA_TRY(cudaLaunchKernelExC(&lc, r.func, args));
     } else {
         void* args[] = {(void*)&r.tp, (void*)&r.tq, (void*)&r.tsp, (void*)&r.tsq, (void*)&r.P};
@@ -470,7 +507,7 @@ static int gemm_impl(const void* a, const void* sfa, const void* b, const void* 
     DeviceState& d = *dp;
     const Options& o = options();
     const bool sf_tma = scales_by_tma(sfa, sfb, K);
-    const Plan pl = plan_for(sfa, sfb, dst, M, N, K, d.sm_count);
+    const Plan pl = plan_for(sfa, sfb, dst, M, N, K, d.sm_count, q_fmt >= 0);
 
     Recipe r;
     r.key = key;
@@ -493,11 +530,14 @@ static int gemm_impl(const void* a, const void* sfa, const void* b, const void* 
     const int64_t prow = pl.swap ? N : M, qrow = pl.swap ? M : N;
     const int fp = pl.swap ? fmt_b : fmt_a, fq = pl.swap ? fmt_a : fmt_b;
 
-    if ((rc = make_map(pp, prow, K, 128, fmt_is_fp8(fp) ? 3 : 0, &r.tp))) return rc;
-    if ((rc = make_map(qp, qrow, K, pl.pair ? 128 : pl.bn, fmt_is_fp8(fq) ? 3 : 0, &r.tq))) return rc;
+    const int p_box = pl.pair ? 128 : pl.p_tile, q_box = pl.pair ? 128 : pl.q_tile;      // rows one operand load brings
+    if ((rc = make_map(pp, prow, K, p_box, fmt_is_fp8(fp) ? 3 : 0, &r.tp))) return rc;
+    if ((rc = make_map(qp, qrow, K, q_box, fmt_is_fp8(fq) ? 3 : 0, &r.tq))) return rc;
+    r.tq_tail = r.tq;
+    if (pl.pair && pl.tail_split > 1 && (rc = make_map(qp, qrow, K, 128 / pl.tail_split, fmt_is_fp8(fq) ? 3 : 0, &r.tq_tail))) return rc;
     if (sf_tma) {
-        if ((rc = make_map(sp, prow, K / 32, 128, 1, &r.tsp))) return rc;
-        if ((rc = make_map(sq, qrow, K / 32, pl.bn, 1, &r.tsq))) return rc;   // pair kernel: all 256 Q rows per CTA
+        if ((rc = make_map(sp, prow, K / 32, p_box, 1, &r.tsp))) return rc;
+        if ((rc = make_map(sq, qrow, K / 32, pl.q_tile, 1, &r.tsq))) return rc;   // pair kernel: all 256 Q rows per CTA
     } else {
         r.tsp = r.tp; r.tsq = r.tq;   // unused by the kernel in this mode
     }
@@ -507,16 +547,21 @@ static int gemm_impl(const void* a, const void* sfa, const void* b, const void* 
     P.p_rows = (int)prow; P.q_rows = (int)qrow;
     P.kblocks = (int)(K / 128);
     P.tiles_p = pl.tiles_p; P.tiles_q = pl.tiles_q;
+    P.p_tile_rows = pl.p_tile; P.q_tile_rows = pl.q_tile;
+    P.raw_tx_bytes = (p_box + pl.q_tile) * 16;
     P.ldc = (int)dst.ldc; P.c_rows = (int)M; P.c_cols = (int)N;
     P.idesc = make_idesc_m(fmt_mma_code(fp), fmt_mma_code(fq), pl.pair ? 256u : 128u, (uint32_t)pl.bn);
     P.sf_tma = sf_tma ? 1 : 0;
     P.sf_ld = (int)(K / 32);
     // bytes a stage's two loads credit to its mbarrier: the global bytes of the boxes (fp6: 96 per 128 elements)
-    P.stage_tx_bytes = 128 * fmt_row_bytes_per_128(fp) + (pl.pair ? 128 : pl.bn) * fmt_row_bytes_per_128(fq);
+    P.stage_tx_bytes = p_box * fmt_row_bytes_per_128(fp) + q_box * fmt_row_bytes_per_128(fq);
+    P.tail_first = pl.tail_first; P.tail_split = pl.tail_split;
+    P.stage_tx_bytes_tail = p_box * fmt_row_bytes_per_128(fp) + (128 / pl.tail_split) * fmt_row_bytes_per_128(fq);
     P.sfp = (const uint8_t*)sp; P.sfq = (const uint8_t*)sq;
     P.c = (__nv_bfloat16*)c;
     for (int i = 1; i < dst.n; ++i) P.c_more[i - 1] = (__nv_bfloat16*)dst.c[i];
     P.ndst = dst.n;
+    P.c_tma = (q_fmt >= 0 || dest_by_tma(dst)) ? 1 : 0;
     P.q_out = (uint8_t*)q_out; P.q_scales = (uint8_t*)q_scales; P.q_fmt = q_fmt;
     P.q_ld = q_fmt < 0 ? 0 : (fmt_is_fp8(q_fmt) ? N : N * 3 / 4);
     P.ws_counter = (unsigned int*)ws;
@@ -543,12 +588,16 @@ static int gemm_impl(const void* a, const void* sfa, const void* b, const void* 
             if (i >= dst.n) { r.cm.m[i] = r.cm.m[0]; continue; }     // unused slots hold a valid map all the same
             if (q_fmt >= 0) {       // the pieces of a re-quantised result are code bytes, not bf16
                 if ((rc = make_map(q_out, M, fmt_is_fp8(q_fmt) ? N : N * 3 / 4, 128, fmt_is_fp8(q_fmt) ? 7 : 6, &r.cm.m[i]))) return rc;
+            } else if (!P.c_tma) {
+                r.cm.m[i] = r.tp;       // plain stores: the slot only has to hold a valid map
             } else if ((rc = make_map(dst.c[i], M, N, 128, 2, &r.cm.m[i], dst.ldc * 2))) return rc;
         }
     } else {
         rc = -1;
 #define MXFP6_CASE(BN_, SWAP_, SK_)                                                              \
-        if (pl.bn == BN_ && pl.swap == SWAP_ && pl.streamk == SK_) rc = bind_cfg<GemmCfg<BN_, SWAP_, SK_>>(d, r);
+        if (pl.ctas == 1 && pl.bn == BN_ && pl.swap == SWAP_ && pl.streamk == SK_) rc = bind_cfg<GemmCfg<BN_, SWAP_, SK_>>(d, r);
+        if (pl.ctas == 2 && pl.bn == 16 && pl.swap && !pl.streamk) rc = bind_cfg<GemmCfg<16, true, false, 2>>(d, r);
+        if (pl.ctas == 2 && pl.bn == 32 && pl.swap && !pl.streamk) rc = bind_cfg<GemmCfg<32, true, false, 2>>(d, r);
         MXFP6_CASE(256, false, false)
         MXFP6_CASE(128, false, false)
         MXFP6_CASE(256, false, true)

@@ -12,6 +12,7 @@ with the CPU oracle).
     python -m hipkittensp_b200.harness                 # the reference's shape list, E2M3
     python -m hipkittensp_b200.harness --check         # asserting run on a few shapes
     python -m hipkittensp_b200.harness --quantize      # GB/s of the block quantiser
+    python -m hipkittensp_b200.harness --edge          # shapes off the preferred multiples (odd K, unaligned N)
 """
 from __future__ import annotations
 
@@ -35,6 +36,12 @@ finally:
 # shapes of the reference's sweep (kernels/gemm/bf16fp32/bench.py:9-18), (m, n, k)
 BENCH_SHAPES = [(8192, 8192, 8192), (4096, 8192, 2048), (8192, 4096, 2048), (8192, 2048, 4096),
                 (4096, 4096, 4096), (2048, 4096, 4096), (2048, 2048, 4096), (2048, 2048, 2048)]
+
+
+# Shapes off the fast path's preferred multiples, to show what they cost: K / 32 not a multiple of 16 (scale rows that
+# cannot be TMA boxes), a Llama-2 FFN width (11008 = 21.5 x 512), an N whose rows are not 16-byte multiples
+EDGE_SHAPES = [(8192, 8192, 8192 + 128), (8192, 8192, 8192 - 128), (4096, 11008, 4096), (4096, 4096, 11008),
+               (8192, 8196, 8192), (4096, 4096, 4096)]
 
 
 def print_title(title: str, width: int = 30) -> None:
@@ -124,6 +131,7 @@ def main(argv=None) -> None:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--check", action="store_true", help="asserting run instead of the timing sweep")
     ap.add_argument("--quantize", action="store_true", help="time the block quantiser instead of the GEMM")
+    ap.add_argument("--edge", action="store_true", help="time shapes off the preferred multiples instead of the reference's list")
     ap.add_argument("--fmt", choices=["e2m3", "e3m2", "e4m3", "e5m2"], default="e2m3")
     ap.add_argument("--warmup", type=int, default=500)
     ap.add_argument("--iters", type=int, default=500)
@@ -140,7 +148,7 @@ def main(argv=None) -> None:
             check_gemm(shape, fmt)
         return
     print_title(f"MX {args.fmt} GEMM (B200)")
-    for shape in BENCH_SHAPES:
+    for shape in (EDGE_SHAPES if args.edge else BENCH_SHAPES):
         bench_gemm({"shape": shape, "fmt": fmt}, None, args.warmup, args.iters)
 
 

@@ -109,6 +109,83 @@ def test_scale_plain_load_path():
     _case("lognormal", 256, 256, 1024, seed=4)
 
 
+@pytest.mark.parametrize("shape", [(512, 768, 640), (300, 520, 384), (1536, 1792, 1152)])
+def test_pair_kernel_scale_plain_load_path(shape):
+    """K / 32 not a multiple of 16: the scale rows cannot be TMA boxes, the CTA-pair kernel reads them with plain
+    loads (forced on the small shapes, chosen by itself on the large one)."""
+    M, N, K = shape
+    _case("lognormal", M, N, K, seed=K, force=None if M * N >= 1536 * 1792 else "256,0,0,1")
+
+
+def test_pair_kernel_scale_plain_load_path_unaligned_scales():
+    hk.debug_option("MXFP6_NO_SF_TMA", "1")
+    _case("lognormal", 512, 768, 1024, seed=6, force="256,0,0,1")
+
+
+@pytest.mark.parametrize("M,N,K", [(16, 296 * 48, 512), (1, 296 * 48 + 40, 384), (32, 296 * 60 + 8, 640), (7, 38000, 256),
+                                   (64, 148 * 160, 512), (128, 148 * 200 + 24, 384), (48, 148 * 256 + 72, 256)])
+def test_even_rows_forms(M, N, K):
+    """Skinny M against many weight rows: the weight rows are dealt evenly to the CTAs (tiles of 48..128 rows of B in
+    the swapped form for M <= 32, column tiles of a multiple of 8 between 128 and 256 in the unswapped form), including
+    tile counts that do not divide N and more than one tile per CTA."""
+    _case("decode", M, N, K, seed=M + N)
+
+
+def test_even_rows_form_matches_k_split_form():
+    """Both skinny forms on the same problem: equal up to the summation order of split tiles."""
+    pa, sa, pb, sb = quantized_inputs("decode", 16, 296 * 64, 1024, seed=3)
+    c1 = run_gpu(pa, sa, pb, sb, R.E2M3)
+    hk.debug_option("MXFP6_DECODE_ROWS", "0")
+    try:
+        c0 = run_gpu(pa, sa, pb, sb, R.E2M3)
+    finally:
+        hk.debug_option("MXFP6_DECODE_ROWS", None)
+    assert np.median(np.abs(c1 - c0)) == 0.0
+    assert (c1 != c0).mean() < 2e-2
+
+
+@pytest.mark.parametrize("M,N,K,fmt", [(4096, 4096, 512, R.E2M3),        # 256 tiles on 74 pairs: 34 left over, 2 slices each
+                                       (2304, 2560, 256, R.E3M2),        # 90 tiles: 16 left over, 4 slices each
+                                       (2204, 2500, 384, R.E2M3)])       # the same with ragged edges and plain-load scales
+def test_pair_kernel_tail_slices(M, N, K, fmt):
+    """The tiles left over after the last full wave of the CTA-pair kernel are cut into column slices.  Every element is
+    still accumulated over K in one accumulator, so the result is bit for bit that of whole tiles."""
+    pa, sa, pb, sb = quantized_inputs("lognormal", M, N, K, fmt, seed=M)
+    c = run_gpu(pa, sa, pb, sb, fmt)
+    ref, absdot = oracle_f64(pa, sa, pb, sb, fmt)
+    check(c, ref, absdot)
+    hk.debug_option("MXFP6_TAIL_SPLIT", "0")
+    try:
+        c_whole = run_gpu(pa, sa, pb, sb, fmt)
+    finally:
+        hk.debug_option("MXFP6_TAIL_SPLIT", None)
+    np.testing.assert_array_equal(c, c_whole)
+
+
+@pytest.mark.parametrize("shape,force", [((512, 772, 512), "256,0,0,1"), ((300, 514, 384), "256,0,0,1"), ((1536, 1797, 256), None)])
+def test_pair_kernel_plain_store_path(shape, force):
+    """N not a multiple of 8: rows of C are not 16-byte multiples, so C cannot be a TMA destination and the CTA-pair
+    kernel writes its staged pieces with plain stores."""
+    M, N, K = shape
+    _case("lognormal", M, N, K, seed=N, force=force)
+
+
+def test_pair_kernel_plain_store_odd_window():
+    """Several destinations whose column window starts at an odd element of rows with an odd stride."""
+    hk.debug_option("MXFP6_FORCE_CFG", "256,0,0,1")
+    M, N, K = 300, 520, 256
+    pa, sa, pb, sb = quantized_inputs("lognormal", M, N, K, seed=12)
+    t = [torch.from_numpy(x).cuda() for x in (pa, sa, pb, sb)]
+    ldc, off = N + 263, 137
+    dests = [torch.full((M, ldc), float("nan"), dtype=torch.bfloat16, device="cuda") for _ in range(2)]
+    hk.dispatch_multi(t[0], t[2], dests, off, t[1], t[3], R.E2M3)
+    assert hk.device_status() == 0
+    ref, absdot = oracle_f64(pa, sa, pb, sb, R.E2M3)
+    for d in dests:
+        check(d[:, off:off + N].float().cpu().numpy(), ref, absdot)
+        assert torch.isnan(d[:, :off]).all() and torch.isnan(d[:, off + N:]).all(), "write outside the window"
+
+
 def test_zero_and_max_blocks():
     M, N, K = 128, 128, 256
     A, B = R.make_inputs("normal", M, N, K, seed=9)
