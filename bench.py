@@ -296,11 +296,11 @@ def run_single(args, torch, hk, device, peaks):
 
     flops_step = 2.0 * M * N * K
     # ---- device-resident timing: W warm-up steps, then exactly K steps between two events
+    sampler = ClockSampler(device.index)
+    sampler.start()                      # before the warm-up: the thread and NVML are in their stride when the region starts
     for i in range(W):
         step(i)
     assert hk.device_status() == 0
-    sampler = ClockSampler(device.index)
-    sampler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     torch.cuda.synchronize()
     t0 = time.perf_counter()
@@ -322,24 +322,6 @@ def run_single(args, torch, hk, device, peaks):
     torch.cuda.synchronize()
     kernel_ms = statistics.mean(s.elapsed_time(e) for s, e in kev)
 
-    # ---- a seconds-long run of the same step: the power-capped regime, with its own clock record
-    sustained = None
-    if headline and not args.no_extras:
-        n_long = max(K_steps, int(1.5 / (ms_total / K_steps * 1e-3)))
-        torch.cuda.synchronize()
-        ts0 = time.perf_counter()
-        e0.record()
-        for i in range(n_long):
-            step(i)
-        e1.record()
-        torch.cuda.synchronize()
-        ts1 = time.perf_counter()
-        ms_long = e0.elapsed_time(e1)
-        tf_long = flops_step * n_long / (ms_long * 1e-3) / 1e12
-        tp_long = tensor_peaks(peaks, ms_long * 1e-3)
-        sustained = {"steps": n_long, "seconds": round(ms_long * 1e-3, 3), "value": round(tf_long, 2), "unit": UNIT,
-                     "frac_of_sustained_peak": round(tf_long / tp_long["sustained"], 4), "peak": round(tp_long["sustained"], 1),
-                     "clocks": sampler.summary(ts0 + 0.3 * (ts1 - ts0), ts1)}
     sampler.stop()
 
     # ---- the result of the timed operands against the CPU oracle, on sampled rows (outside every timed region)
@@ -359,6 +341,13 @@ def run_single(args, torch, hk, device, peaks):
         check = {"ok": bool(ok), "rows": int(n_rows), "row_rel": float(f"{rep['row_rel']:.3e}"), "max_ulp": round(rep["max_ulp"], 3),
                  "n_floor": rep["n_floor"], "against": "fp64-accumulated product of the dequantised operands on the host cores",
                  "tolerance": "row_rel <= 1e-2, max_ulp <= 2 bf16 ulp"}
+
+    # ---- the other single-GPU configurations, before anything long has heated the part (a short pause lets the
+    # clocks settle as they would between unrelated kernels)
+    extras = None
+    if headline and not args.no_extras:
+        time.sleep(1.0)
+        extras = extra_configs(torch, hk, device, peaks)
 
     # ---- end to end: operands start in pinned host memory, result ends in pinned host memory
     a, sa, b, sb = sets[0]
@@ -381,6 +370,28 @@ def run_single(args, torch, hk, device, peaks):
     torch.cuda.synchronize()
     ms_e2e = e0.elapsed_time(e1) / n_e2e
     del pipe
+
+    # ---- a seconds-long run of the same step: the power-capped regime, with its own clock record
+    sustained = None
+    if headline and not args.no_extras:
+        sampler.samples.clear()
+        sampler.start()
+        n_long = max(K_steps, int(1.5 / (ms_total / K_steps * 1e-3)))
+        torch.cuda.synchronize()
+        ts0 = time.perf_counter()
+        e0.record()
+        for i in range(n_long):
+            step(i)
+        e1.record()
+        torch.cuda.synchronize()
+        ts1 = time.perf_counter()
+        ms_long = e0.elapsed_time(e1)
+        tf_long = flops_step * n_long / (ms_long * 1e-3) / 1e12
+        tp_long = tensor_peaks(peaks, ms_long * 1e-3)
+        sustained = {"steps": n_long, "seconds": round(ms_long * 1e-3, 3), "value": round(tf_long, 2), "unit": UNIT,
+                     "frac_of_sustained_peak": round(tf_long / tp_long["sustained"], 4), "peak": round(tp_long["sustained"], 1),
+                     "clocks": sampler.summary(ts0 + 0.3 * (ts1 - ts0), ts1)}
+        sampler.stop()
 
     ms_step = ms_total / K_steps
     value = flops_step / (ms_step * 1e-3) / 1e12
@@ -419,14 +430,12 @@ def run_single(args, torch, hk, device, peaks):
                             "peak_source": "MEASURED_PEAKS.json hbm_gbs" if "hbm_gbs" in peaks else "fallback 6.65 TB/s",
                             "frac_of_datasheet_8000": round(gbs / DATASHEET_HBM_GBS, 4),
                             "algorithmic_bytes": algorithmic_bytes(M, N, K)}
+    if extras is not None:
+        line["extra_configs"] = extras
     if sustained is not None:
         line["sustained"] = sustained
     if check is not None:
         line["check"] = check
-    if headline and not args.no_extras:
-        del sets, C, host_in, host_out
-        torch.cuda.empty_cache()
-        line["extra_configs"] = extra_configs(torch, hk, device, peaks)
     if not args.no_cpu_baseline:
         ops = [t.cpu() for t in (a, sa, b, sb)]
         line["cpu_baseline"] = cpu_baseline(ops, M, N, K, budget_s=20.0)
@@ -462,11 +471,11 @@ def run_sharded(args, torch, hk, device, peaks, world, rank):
         torch.cuda.synchronize()
 
     flops_step = 2.0 * M * N * K
+    sampler = ClockSampler(device.index)
+    sampler.start()                      # before the warm-up: the thread and NVML are in their stride when the region starts
     for i in range(W):
         step(i)
     assert hk.device_status() == 0
-    sampler = ClockSampler(device.index)
-    sampler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     t0 = time.perf_counter()

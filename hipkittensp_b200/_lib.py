@@ -20,7 +20,7 @@ OK, ERR_BAD_ARG, ERR_CUDA, ERR_DEVICE_WAIT, ERR_UNSUPPORTED = 0, 1, 2, 3, 4
 # every symbol include/mxfp6.h declares
 SYMBOLS = ("mxfp6_version", "mxfp6_last_error", "mxfp6_gemm", "mxfp6_gemm_workspace_bytes", "mxfp6_gemm_ws",
            "mxfp6_gemm_noalloc", "mxfp6_gemm_multi", "mxfp6_gemm_ex", "mxfp6_gemm_requant", "mxfp6_gemm_scaled",
-           "mxfp6_quantize", "mxfp6_dequantize", "mxfp6_device_status", "mxfp6_debug_tma_dump", "mxfp6_debug_wait_timeout", "mxfp6_debug_option")
+           "mxfp6_quantize", "mxfp6_dequantize", "mxfp6_device_status", "mxfp6_debug_tma_dump", "mxfp6_debug_wait_timeout", "mxfp6_debug_option", "mxfp6_debug_plan")
 
 
 class Mxfp6Error(RuntimeError):
@@ -69,6 +69,8 @@ def _load() -> ctypes.CDLL:
     lib.mxfp6_debug_wait_timeout.argtypes = [ci, vp]
     lib.mxfp6_debug_option.restype = ci
     lib.mxfp6_debug_option.argtypes = [ctypes.c_char_p, ctypes.c_char_p]
+    lib.mxfp6_debug_plan.restype = ci
+    lib.mxfp6_debug_plan.argtypes = [i64, i64, i64, ci, ci, ci, ctypes.POINTER(ci)]
     lib.mxfp6_debug_tma_dump.restype = ci
     lib.mxfp6_debug_tma_dump.argtypes = [vp, i64, i64, i64, i64, vp, vp]
     return lib
@@ -80,6 +82,16 @@ lib = _load()
 def check(rc: int) -> None:
     if rc != OK:
         raise Mxfp6Error(rc, lib.mxfp6_last_error().decode())
+
+
+PLAN_FIELDS = ("bn", "swap", "streamk", "pair", "ctas", "p_tile", "q_tile", "tiles_p", "tiles_q", "grid", "tail_first", "tail_split")
+
+
+def debug_plan(M: int, N: int, K: int, sm_count: int = 148, n_dst: int = 1, requant: bool = False) -> dict:
+    """Test hook: the kernel choice and tiling for a problem on a device with sm_count SMs (touches no device)."""
+    out = (ctypes.c_int * 12)()
+    check(lib.mxfp6_debug_plan(M, N, K, sm_count, n_dst, int(requant), out))
+    return dict(zip(PLAN_FIELDS, out))
 
 
 def debug_option(name: str, value: str | None) -> None:

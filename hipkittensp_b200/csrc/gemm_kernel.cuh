@@ -39,6 +39,12 @@ struct GemmParams {
     int p_tile_rows;           // rows of P one tile covers (<= 128; 128 unless the rows of a streamed operand are dealt evenly to the CTAs)
     int q_tile_rows;           // rows of Q one tile covers (<= BN)
     int raw_tx_bytes;          // bytes the two scale-slab loads of a group report to their mbarrier
+    // two-CTAs-per-SM form: the operand ring is laid out at run time, because a tile of fewer than 128 rows of P needs
+    // less than the 16 KB a full box takes and the space saved buys more stages
+    int n_stages;              // stages in the ring (<= STAGES_MAX)
+    int stage_stride;          // bytes from one stage to the next (a multiple of 1024)
+    int q_off;                 // offset of the Q box inside a stage (rows of P rounded up to 8, times 128)
+    int load_batch;            // K-blocks the producer requests back to back
     int ldc;                   // row stride of C in elements (= N)
     int c_rows, c_cols;        // M, N
     uint32_t idesc;            // instruction descriptor without scale ids
@@ -144,6 +150,7 @@ struct GemmCfg {
     static constexpr int STAGES = CTAS_ == 2 ? (BN <= 16 ? 5 : 4)
                                              : BN >= 256 ? 4 : BN >= 128 ? 6 : BN >= 64 ? 8 : BN >= 32 ? 9 : 11;
     static constexpr int LOAD_BATCH = SWAP_ ? (STAGES >= 8 ? 4 : 2) : 1;   // K-blocks the producer requests together
+    static constexpr int STAGES_MAX = CTAS_ == 2 ? 8 : STAGES;             // barrier pairs provided (see GemmParams::n_stages)
     static constexpr int QATOMS = (BN + 127) / 128;      // 128-row scale atoms on the Q side
     static constexpr int RAW_SLOTS = (BN >= 256 || CTAS_ == 2) ? 2 : 4;  // each raw slab covers 4 K-blocks (16 scale bytes per row)
     static constexpr int RAW_Q_ROWS = BN < 32 ? 32 : BN;
@@ -157,7 +164,7 @@ struct GemmCfg {
     // two CTAs of an SM share its 512 columns: each takes the power of two that holds its two accumulators and 32 scale columns
     static constexpr int TMEM_COLS = CTAS_ == 2 ? (2 * BN + 32 <= 64 ? 64 : 2 * BN + 32 <= 128 ? 128 : 256) : 512;
     static_assert(CTAS_ == 1 || (CTAS_ == 2 && BN <= 64 && !STREAMK_), "two CTAs per SM: small accumulators, whole tiles");
-    static constexpr int NUM_BARS = 2 * STAGES + 2 * RAW_SLOTS + 2 * ATOM_GROUPS + 5;
+    static constexpr int NUM_BARS = 2 * STAGES_MAX + 2 * RAW_SLOTS + 2 * ATOM_GROUPS + 5;
     // unswapped form: column scale and bias of the current tile for the fp32 epilogue (2 x BN floats, 16-byte aligned)
     static constexpr int AFF_BYTES = SWAP ? 0 : 2 * BN * 4 + 16;
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + RAW_SLOTS * RAW_BYTES + ATOM_GROUPS * GROUP_BYTES +
@@ -288,12 +295,18 @@ mxfp6_gemm_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constan
     const uint32_t atom_base = raw_base + Cfg::RAW_SLOTS * Cfg::RAW_BYTES;
     const uint32_t bar_base = atom_base + Cfg::ATOM_GROUPS * Cfg::GROUP_BYTES;
     auto bar_full = [&](int s) { return bar_base + 8u * s; };
-    auto bar_empty = [&](int s) { return bar_base + 8u * (Cfg::STAGES + s); };
-    auto bar_raw_full = [&](int s) { return bar_base + 8u * (2 * Cfg::STAGES + s); };
-    auto bar_raw_empty = [&](int s) { return bar_base + 8u * (2 * Cfg::STAGES + Cfg::RAW_SLOTS + s); };
-    auto bar_atom_full = [&](int s) { return bar_base + 8u * (2 * Cfg::STAGES + 2 * Cfg::RAW_SLOTS + s); };
-    auto bar_atom_empty = [&](int s) { return bar_base + 8u * (2 * Cfg::STAGES + 2 * Cfg::RAW_SLOTS + Cfg::ATOM_GROUPS + s); };
-    const uint32_t bar_misc = bar_base + 8u * (2 * Cfg::STAGES + 2 * Cfg::RAW_SLOTS + 2 * Cfg::ATOM_GROUPS);
+    constexpr int SM_ = Cfg::STAGES_MAX;
+    auto bar_empty = [&](int s) { return bar_base + 8u * (SM_ + s); };
+    auto bar_raw_full = [&](int s) { return bar_base + 8u * (2 * SM_ + s); };
+    auto bar_raw_empty = [&](int s) { return bar_base + 8u * (2 * SM_ + Cfg::RAW_SLOTS + s); };
+    auto bar_atom_full = [&](int s) { return bar_base + 8u * (2 * SM_ + 2 * Cfg::RAW_SLOTS + s); };
+    auto bar_atom_empty = [&](int s) { return bar_base + 8u * (2 * SM_ + 2 * Cfg::RAW_SLOTS + Cfg::ATOM_GROUPS + s); };
+    const uint32_t bar_misc = bar_base + 8u * (2 * SM_ + 2 * Cfg::RAW_SLOTS + 2 * Cfg::ATOM_GROUPS);
+    // ring geometry: fixed at compile time, except in the two-CTAs-per-SM form
+    const int n_stages = Cfg::CTAS == 2 ? P.n_stages : Cfg::STAGES;
+    const uint32_t stage_stride = Cfg::CTAS == 2 ? (uint32_t)P.stage_stride : (uint32_t)Cfg::STAGE_BYTES;
+    const uint32_t q_off = Cfg::CTAS == 2 ? (uint32_t)P.q_off : (uint32_t)Cfg::P_BYTES;
+    const int load_batch = Cfg::CTAS == 2 ? P.load_batch : Cfg::LOAD_BATCH;
     auto bar_acc_full = [&](int b) { return bar_misc + 8u * b; };
     auto bar_acc_empty = [&](int b) { return bar_misc + 8u * (2 + b); };
     const uint32_t bar_ovl = bar_misc + 8u * 4;
@@ -308,7 +321,7 @@ mxfp6_gemm_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constan
     pdl_launch_dependents();     // the next kernel may set itself up on SMs this grid has left
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < Cfg::STAGES; ++s) { mbar_init(bar_full(s), 1); mbar_init(bar_empty(s), 1); }
+        for (int s = 0; s < n_stages; ++s) { mbar_init(bar_full(s), 1); mbar_init(bar_empty(s), 1); }
         for (int s = 0; s < Cfg::RAW_SLOTS; ++s) { mbar_init(bar_raw_full(s), 1); mbar_init(bar_raw_empty(s), 32); }
         for (int s = 0; s < Cfg::ATOM_GROUPS; ++s) { mbar_init(bar_atom_full(s), 32); mbar_init(bar_atom_empty(s), 1); }
         for (int b = 0; b < 2; ++b) { mbar_init(bar_acc_full(b), 1); mbar_init(bar_acc_empty(b), 128); }
@@ -325,10 +338,18 @@ mxfp6_gemm_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constan
         tmem_alloc(smem_u32(tmem_slot), Cfg::TMEM_COLS);
         tmem_relinquish();
     }
+    // The producer warp (which has just initialised the barriers) does not wait for the TMEM allocation: it announces
+    // itself at the CTA's meeting point and goes on to request the first stages; everybody else meets there.
     tc_fence_before();
-    __syncthreads();
+    if (warp == 0) {
+        __syncwarp();
+        __threadfence_block();
+        asm volatile("bar.arrive 2, 256;" ::: "memory");
+    } else {
+        asm volatile("bar.sync 2, 256;" ::: "memory");
+    }
     tc_fence_after();
-    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t tmem_base = warp == 0 ? 0u : *tmem_slot;
     // Nothing above touches global memory; everything below may.  With early_p the producer warp alone goes
     // ahead and requests the first stages of P (weights that the preceding kernel does not write) before it waits.
     const bool early = Cfg::SWAP && P.early_p != 0;
@@ -346,8 +367,8 @@ mxfp6_gemm_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constan
             SegIter<Cfg> it2(P);
             Segment s2;
             bool slabs = P.sf_tma != 0;
-            while (pre_stage < (uint32_t)Cfg::STAGES && it2.next(s2)) {
-                for (int k = s2.k0; k < s2.k1 && pre_stage < (uint32_t)Cfg::STAGES; ++k) {
+            while (pre_stage < (uint32_t)n_stages && it2.next(s2)) {
+                for (int k = s2.k0; k < s2.k1 && pre_stage < (uint32_t)n_stages; ++k) {
                     if (P.sf_tma && (k == s2.k0 || (k & 3) == 0)) {
                         if (slabs && pre_raw < (uint32_t)Cfg::RAW_SLOTS) {
                             if (elect_one_sync()) {
@@ -361,7 +382,7 @@ mxfp6_gemm_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constan
                     }
                     if (elect_one_sync()) {
                         mbar_arrive_expect_tx(bar_full(pre_stage), (uint32_t)P.stage_tx_bytes);
-                        tma_load_2d(stage_base + pre_stage * Cfg::STAGE_BYTES, &tm_p, bar_full(pre_stage), k * Cfg::BK, s2.p0);
+                        tma_load_2d(stage_base + pre_stage * stage_stride, &tm_p, bar_full(pre_stage), k * Cfg::BK, s2.p0);
                     }
                     __syncwarp();
                     ++pre_stage;
@@ -373,7 +394,7 @@ mxfp6_gemm_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constan
             for (int kb = sg.k0; kb < sg.k1 && ok;) {
                 // LOAD_BATCH K-blocks are requested back to back, so that each row's adjacent 96-byte pieces
                 // reach DRAM together (one page activation serves the whole run)
-                const int nb = min(Cfg::LOAD_BATCH, sg.k1 - kb);
+                const int nb = min(load_batch, sg.k1 - kb);
                 for (int j = 0; j < nb && ok; ++j) {
                     const int k = kb + j;
                     if (P.sf_tma && (k == sg.k0 || (k & 3) == 0)) {
@@ -395,17 +416,17 @@ mxfp6_gemm_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constan
                 if (!ok) break;
                 // stages are released in order: when the last one of the batch is free, all of them are
                 const uint32_t last = n_stage + nb - 1;
-                ok = wait_bar_warp(bar_empty(last % Cfg::STAGES), ((last / Cfg::STAGES) & 1) ^ 1, abort_flag, P, kStatusTimeoutProducer);
+                ok = wait_bar_warp(bar_empty(last % n_stages), ((last / n_stages) & 1) ^ 1, abort_flag, P, kStatusTimeoutProducer);
                 if (!ok) break;
                 if (elect_one_sync()) {
                     for (int j = 0; j < nb; ++j) {
-                        const int s = (n_stage + j) % Cfg::STAGES;
-                        const uint32_t dst = stage_base + s * Cfg::STAGE_BYTES;
+                        const int s = (n_stage + j) % n_stages;
+                        const uint32_t dst = stage_base + s * stage_stride;
                         if (n_stage + j >= pre_stage) {
                             mbar_arrive_expect_tx(bar_full(s), (uint32_t)P.stage_tx_bytes);
                             tma_load_2d(dst, &tm_p, bar_full(s), (kb + j) * Cfg::BK, sg.p0);
                         }
-                        tma_load_2d(dst + Cfg::P_BYTES, &tm_q, bar_full(s), (kb + j) * Cfg::BK, sg.q0);
+                        tma_load_2d(dst + q_off, &tm_q, bar_full(s), (kb + j) * Cfg::BK, sg.q0);
                     }
                 }
                 __syncwarp();
@@ -431,12 +452,12 @@ mxfp6_gemm_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constan
             if (!ok) break;
             tc_fence_after();
             for (int kb = sg.k0; kb < sg.k1; ++kb) {
-                const int s = n_kb % Cfg::STAGES;
+                const int s = n_kb % n_stages;
                 const int g = n_grp % Cfg::ATOM_GROUPS;
                 // the scale atoms arrive per group of 4 K-blocks (one raw slab)
                 if (kb == sg.k0 || (kb & 3) == 0)
                     ok = wait_bar_warp(bar_atom_full(g), (n_grp / Cfg::ATOM_GROUPS) & 1, abort_flag, P, kStatusTimeoutMma);
-                ok = ok && wait_bar_warp(bar_full(s), (n_kb / Cfg::STAGES) & 1, abort_flag, P, kStatusTimeoutMma);
+                ok = ok && wait_bar_warp(bar_full(s), (n_kb / n_stages) & 1, abort_flag, P, kStatusTimeoutMma);
                 if (!ok) break;
                 const bool group_done = (kb & 3) == 3 || kb == sg.k1 - 1;
                 if (elect_one_sync()) {
@@ -448,9 +469,9 @@ mxfp6_gemm_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constan
 #pragma unroll
                     for (int q = 0; q < Cfg::QATOMS; ++q) tc_cp_32x128b_warpx4(sfb + 4 * q, smem_desc_sf(atom + 512 * (1 + q)));
                     }
-                    const uint32_t sp = stage_base + s * Cfg::STAGE_BYTES;
+                    const uint32_t sp = stage_base + s * stage_stride;
                     const uint64_t adesc = smem_desc_sw128(sp);
-                    const uint64_t bdesc = smem_desc_sw128(sp + Cfg::P_BYTES);
+                    const uint64_t bdesc = smem_desc_sw128(sp + q_off);
 #pragma unroll
                     for (uint32_t k = 0; k < 4; ++k) {
                         mma_mxf8f6f4(acc, adesc + 2 * k, bdesc + 2 * k, idesc_with_sf(P.idesc, k),

@@ -55,6 +55,7 @@ struct Options {
     int l2_load = 0, l2_store = 0;   // MXFP6_L2 = "load,store": eviction policy of the pair kernel's TMA traffic
     int tail_split = 1;      // MXFP6_TAIL_SPLIT: the pair kernel splits the tiles of its last partial wave along K
     int decode_rows = 1;     // MXFP6_DECODE_ROWS: skinny problems take the row-balanced kernel when they qualify
+    int decode_stages = 0, decode_batch = 0;   // MXFP6_DECODE_RING = "stages,batch": ring of that kernel (0 = chosen by the library)
 };
 static Options g_opt;
 static std::once_flag g_opt_once;
@@ -75,11 +76,15 @@ static bool set_option(const char* name, const char* v) {
         if (v) sscanf(v, "%d,%d", &g_opt.l2_load, &g_opt.l2_store);
     } else if (!strcmp(name, "MXFP6_TAIL_SPLIT")) g_opt.tail_split = v ? atoi(v) : d.tail_split;
     else if (!strcmp(name, "MXFP6_DECODE_ROWS")) g_opt.decode_rows = v ? atoi(v) : d.decode_rows;
+    else if (!strcmp(name, "MXFP6_DECODE_RING")) {
+        g_opt.decode_stages = d.decode_stages; g_opt.decode_batch = d.decode_batch;
+        if (v) sscanf(v, "%d,%d", &g_opt.decode_stages, &g_opt.decode_batch);
+    }
     else return false;
     return true;
 }
 static const char* const kOptionNames[] = {"MXFP6_FORCE_CFG", "MXFP6_NO_SF_TMA", "MXFP6_PDL", "MXFP6_GROUP_P", "MXFP6_QUANT_PATH",
-                                           "MXFP6_WAIT_MS", "MXFP6_L2", "MXFP6_TAIL_SPLIT", "MXFP6_DECODE_ROWS"};
+                                           "MXFP6_WAIT_MS", "MXFP6_L2", "MXFP6_TAIL_SPLIT", "MXFP6_DECODE_ROWS", "MXFP6_DECODE_RING"};
 static const Options& options() {
     std::call_once(g_opt_once, [] {
         for (const char* n : kOptionNames)
@@ -549,6 +554,19 @@ static int gemm_impl(const void* a, const void* sfa, const void* b, const void* 
     P.tiles_p = pl.tiles_p; P.tiles_q = pl.tiles_q;
     P.p_tile_rows = pl.p_tile; P.q_tile_rows = pl.q_tile;
     P.raw_tx_bytes = (p_box + pl.q_tile) * 16;
+    if (pl.ctas == 2) {
+        // ring of the two-CTAs-per-SM form: a stage holds the tile's rows of P rounded up to 8 (whole 1024-byte swizzle
+        // groups) and the Q box; as many stages as the ring's bytes allow (5 x 18 KB for BN = 16, 4 x 20 KB for BN = 32)
+        const int ring = pl.bn <= 16 ? 5 * (16384 + 16 * 128) : 4 * (16384 + 32 * 128);
+        P.q_off = (pl.p_tile + 7) / 8 * 1024;
+        P.stage_stride = P.q_off + pl.bn * 128;
+        int ns = ring / P.stage_stride;
+        if (ns > 8) ns = 8;
+        if (o.decode_stages >= 2 && o.decode_stages <= ns) ns = o.decode_stages;
+        P.n_stages = ns;
+        P.load_batch = ns >= 8 ? 4 : ns >= 6 ? 3 : 2;
+        if (o.decode_batch >= 1 && o.decode_batch <= ns / 2) P.load_batch = o.decode_batch;
+    }
     P.ldc = (int)dst.ldc; P.c_rows = (int)M; P.c_cols = (int)N;
     P.idesc = make_idesc_m(fmt_mma_code(fp), fmt_mma_code(fq), pl.pair ? 256u : 128u, (uint32_t)pl.bn);
     P.sf_tma = sf_tma ? 1 : 0;
@@ -999,6 +1017,16 @@ extern "C" int mxfp6_debug_option(const char* name, const char* value) {
     std::lock_guard<std::mutex> lk(g_mu);
     if (!set_option(name, value)) return fail(MXFP6_ERR_BAD_ARG, "debug_option: unknown option %s", name);
     g_opt_epoch.fetch_add(1, std::memory_order_acq_rel);      // launch recipes built under the old values are not reused
+    return MXFP6_OK;
+}
+
+extern "C" int mxfp6_debug_plan(int64_t M, int64_t N, int64_t K, int sm_count, int n_dst, int requant, int* out12) {
+    if (!out12 || M <= 0 || N <= 0 || K <= 0 || K % 128 || sm_count < 2 || n_dst < 1 || n_dst > 8)
+        return fail(MXFP6_ERR_BAD_ARG, "debug_plan: bad argument");
+    const Plan p = make_plan(M, N, K, sm_count, true, n_dst > 1, !requant);
+    const int v[12] = {p.bn, p.swap, p.streamk, p.pair, p.ctas, p.p_tile, p.q_tile, p.tiles_p, p.tiles_q, p.grid,
+                       p.tail_first, p.tail_split};
+    memcpy(out12, v, sizeof v);
     return MXFP6_OK;
 }
 

@@ -187,10 +187,19 @@ int mxfp6_debug_wait_timeout(int budget_us, void* stream);
 /*
  * Test hook: sets one of the library's switches (the names of the environment variables that give their first
  * values: "MXFP6_FORCE_CFG" = "bn,swap,streamk[,pair]" forces a kernel variant, "MXFP6_NO_SF_TMA", "MXFP6_PDL",
- * "MXFP6_GROUP_P", "MXFP6_QUANT_PATH", "MXFP6_L2", "MXFP6_TAIL_SPLIT", "MXFP6_DECODE_ROWS"); value NULL restores the
+ * "MXFP6_GROUP_P", "MXFP6_QUANT_PATH", "MXFP6_L2", "MXFP6_TAIL_SPLIT", "MXFP6_DECODE_ROWS", "MXFP6_DECODE_RING"); value NULL restores the
  * default.  Takes effect for calls made after it returns.  (No counterpart in the reference.)
  */
 int mxfp6_debug_option(const char* name, const char* value);
+
+/*
+ * Test hook: the kernel choice and tiling the GEMM entry points would make for this problem on a device with
+ * sm_count SMs (no device is touched), as 12 ints: tile width BN, operands swapped, tiles split along K, CTA-pair
+ * kernel, CTAs per SM, rows of the first / second operand per tile, tile counts along both, grid size, first tile of
+ * the pair kernel's last partial wave and the number of column slices its tiles are cut into.  (No counterpart in
+ * the reference, whose tiling is fixed at compile time: kernels/gemm/bf16fp32/256_256_64_32_with16x32.cpp:23-32.)
+ */
+int mxfp6_debug_plan(int64_t M, int64_t N, int64_t K, int sm_count, int n_dst, int requant, int* out12);
 
 /*
  * Diagnostic: TMA-loads one 128-row x 128-element box of a packed operand (rows row0.., elements

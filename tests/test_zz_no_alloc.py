@@ -53,8 +53,8 @@ def test_noalloc_matches_allocating_entry_point_twice(shape):
 
 
 def test_noalloc_refuses_more_scratch_than_it_has():
-    # 600 split tiles with 32-wide fp32 partials need far more than the 8 MiB the library carries
-    M, N, K = 32, 128 * 600, 1024
+    # 300 split tiles with 64-wide fp32 partials need far more than the 8 MiB the library carries
+    M, N, K = 64, 128 * 300, 1024
     need = hk.lib.mxfp6_gemm_workspace_bytes(M, N, K)
     assert need > 8 << 20
     dummy = torch.zeros(64, dtype=torch.uint8, device="cuda")
