@@ -82,6 +82,9 @@ class ClockSampler:
             pynvml.nvmlInit()
             self.h = pynvml.nvmlDeviceGetHandleByIndex(self._physical_index(gpu_index))
             self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM))
+            for _ in range(3):      # the first queries of a process are slow: make them here, not inside a timed region
+                pynvml.nvmlDeviceGetClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+                pynvml.nvmlDeviceGetPowerUsage(self.h)
         except Exception as e:      # no NVML: the line says so
             self.nv, self.err = None, repr(e)
 
@@ -126,11 +129,17 @@ class ClockSampler:
         if self.nv is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvml unavailable: " + str(self.err)]}
         sel = [s for s in self.samples if (t0 is None or s[0] >= t0) and (t1 is None or s[0] <= t1)]
+        note = "samples with a host time inside the region"
+        if not sel and t0 is not None and self.samples:
+            # a region of a few ms can fall between two answers of NVML: take the samples nearest to it
+            mid = 0.5 * (t0 + t1)
+            sel = sorted(self.samples, key=lambda s: abs(s[0] - mid))[:3]
+            note = "no sample inside the region: the 3 nearest in time (%.1f ms away at most)" % (1e3 * max(abs(s[0] - mid) for s in sel))
         names = ((0x8, "hw_slowdown"), (0x40, "hw_thermal_slowdown"), (0x20, "sw_thermal_slowdown"), (0x4, "sw_power_cap"))
         reasons = sorted({n for s in sel for bit, n in names if s[3] & bit})
         return {"sm_mhz": statistics.median(s[1] for s in sel) if sel else None, "sm_max_mhz": self.max_mhz,
                 "power_w_max": max((s[2] for s in sel), default=None), "samples": len(sel), "reasons": reasons,
-                "how": "NVML polled from a thread of this process; samples with a host time inside the region"}
+                "how": "NVML polled from a thread of this process; " + note}
 
 
 # ------------------------------------------------------------------------------------------ inputs
@@ -197,58 +206,50 @@ def oracle_rows_check(torch, C_rows, a_rows, sa_rows, b, sb, fmt):
     return worst
 
 
-def graph_time_us(torch, launch, n_launch: int = 20, reps: int = 5) -> float:
-    """Mean time of one launch inside a CUDA graph of n_launch launches (no host time between them), best of reps."""
+def graph_time_us(torch, launch, n_launch: int = 20, reps: int = 9, warm_ms: float = 10.0):
+    """Time of one launch inside a CUDA graph of n_launch launches (no host time between them): the graph is replayed
+    for at least warm_ms first (clocks up, caches in their steady state), then reps times between two events each.
+    Returns (median, best) in microseconds."""
     launch(0)
     torch.cuda.synchronize()
     g = torch.cuda.CUDAGraph()
     with torch.cuda.graph(g):
         for i in range(n_launch):
             launch(i)
-    g.replay()
-    torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    best = None
+    e0.record()
+    g.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    first = max(e0.elapsed_time(e1), 1e-3)
+    for _ in range(max(2, int(warm_ms / first))):
+        g.replay()
+    torch.cuda.synchronize()
+    ts = []
     for _ in range(reps):
         e0.record()
         g.replay()
         e1.record()
         torch.cuda.synchronize()
-        t = e0.elapsed_time(e1) * 1e3 / n_launch
-        best = t if best is None else min(best, t)
-    return best
+        ts.append(e0.elapsed_time(e1) * 1e3 / n_launch)
+    return statistics.median(ts), min(ts)
 
 
 # ------------------------------------------------------------------------------------------ single GPU
 def extra_configs(torch, hk, device, peaks):
-    """The other single-GPU configurations, kernel-timed in CUDA graphs of 20 launches on rotating operand sets."""
+    """The other single-GPU configurations, kernel-timed in CUDA graphs of 20 launches on rotating operand sets (median of
+    9 replays after a few ms of warm-up replays).  Each is measured as a short burst after an idle pause, the memory-bound
+    decode shapes first: a part that has just run a seconds-long dense GEMM stays power-capped for a while (SM clock about
+    1.2 GHz of 1.965), which slows whatever is measured next, memory-bound kernels included.  The power-capped regime
+    itself is the `sustained` figure of the headline configuration."""
     out = []
     hbm = peaks.get("hbm_gbs", 6650.0)
     hbm_src = "MEASURED_PEAKS.json hbm_gbs" if "hbm_gbs" in peaks else "fallback 6650"
     tp = tensor_peaks(peaks, 0.0)
 
-    def tensor_case(name, M, N, K, fmt, a_kw, b_kw):
-        sets = [(make_operands(torch, hk, M, K, "normal", 40 + i, device, fmt, **a_kw),
-                 make_operands(torch, hk, N, K, "normal", 50 + i, device, fmt, **b_kw)) for i in range(2)]
-        C = torch.empty((M, N), dtype=torch.bfloat16, device=device)
-
-        def launch(i):
-            (a, sa), (b, sb) = sets[i % 2]
-            hk.dispatch_micro(a, b, C, sa, sb, fmt)
-
-        us = graph_time_us(torch, launch)
-        tf = 2.0 * M * N * K / us / 1e6
-        e = {"workload": name, "M": M, "N": N, "K": K, "bound": "tensor", "kernel_us": round(us, 2), "achieved": round(tf, 1),
-             "unit": "TFLOP/s", "frac": round(tf / tp["burst"], 4), "peak": round(tp["burst"], 1),
-             "frac_of_datasheet_4500": round(tf / DATASHEET_TFLOPS, 4)}
-        if M == N == K and M in CUTLASS_B200_TFLOPS:
-            e["vs_cutlass_b200"] = round(tf / CUTLASS_B200_TFLOPS[M], 4)
-        out.append(e)
-        del sets, C
-
-    tensor_case("mxfp6_e3m2_gemm_4096x14336x8192_ffn", 4096, 14336, 8192, hk.E3M2,
-                dict(outlier_channels=8), dict(scale=0.02))
-    tensor_case("mxfp6_e2m3_gemm_4096x4096x4096", 4096, 4096, 4096, hk.E2M3, {}, {})
+    def pause():
+        torch.cuda.synchronize()
+        time.sleep(1.0)
 
     # decode: weights N(0, 0.02), activations N(0,1); two weight sets (176 MB each) rotate, so every launch streams
     # its weights from DRAM
@@ -262,12 +263,45 @@ def extra_configs(torch, hk, device, peaks):
             b, sb = wsets[i % 2]
             hk.dispatch_micro(a, b, C, sa, sb, hk.E2M3)
 
-        us = graph_time_us(torch, launch)
+        def launch_static(i):     # MXFP6_FLAG_B_STATIC: the caller declares the weights not written by the preceding kernel
+            b, sb = wsets[i % 2]
+            hk.dispatch_micro(a, b, C, sa, sb, hk.E2M3, b_static=True)
+
+        pause()
+        us, us_best = graph_time_us(torch, launch)
+        us_static, _ = graph_time_us(torch, launch_static)
         gbs = algorithmic_bytes(M, N, K) / us / 1e3
         out.append({"workload": f"mxfp6_e2m3_gemm_{M}x{N}x{K}_decode", "M": M, "N": N, "K": K, "bound": "hbm",
-                    "kernel_us": round(us, 2), "achieved": round(gbs, 1), "unit": "GB/s", "frac": round(gbs / hbm, 4),
-                    "peak": hbm, "peak_source": hbm_src, "frac_of_datasheet_8000": round(gbs / DATASHEET_HBM_GBS, 4),
-                    "algorithmic_bytes": algorithmic_bytes(M, N, K)})
+                    "kernel_us": round(us, 2), "kernel_us_best": round(us_best, 2), "achieved": round(gbs, 1), "unit": "GB/s",
+                    "frac": round(gbs / hbm, 4), "peak": hbm, "peak_source": hbm_src,
+                    "frac_of_datasheet_8000": round(gbs / DATASHEET_HBM_GBS, 4), "algorithmic_bytes": algorithmic_bytes(M, N, K),
+                    "kernel_us_weights_static": round(us_static, 2),
+                    "frac_weights_static": round(algorithmic_bytes(M, N, K) / us_static / 1e3 / hbm, 4)})
+    del wsets
+
+    def tensor_case(name, M, N, K, fmt, a_kw, b_kw):
+        sets = [(make_operands(torch, hk, M, K, "normal", 40 + i, device, fmt, **a_kw),
+                 make_operands(torch, hk, N, K, "normal", 50 + i, device, fmt, **b_kw)) for i in range(2)]
+        C = torch.empty((M, N), dtype=torch.bfloat16, device=device)
+
+        def launch(i):
+            (a, sa), (b, sb) = sets[i % 2]
+            hk.dispatch_micro(a, b, C, sa, sb, fmt)
+
+        pause()
+        us, us_best = graph_time_us(torch, launch, warm_ms=3.0)
+        tf = 2.0 * M * N * K / us / 1e6
+        e = {"workload": name, "M": M, "N": N, "K": K, "bound": "tensor", "kernel_us": round(us, 2), "kernel_us_best": round(us_best, 2),
+             "achieved": round(tf, 1), "unit": "TFLOP/s", "frac": round(tf / tp["burst"], 4), "peak": round(tp["burst"], 1),
+             "frac_of_datasheet_4500": round(tf / DATASHEET_TFLOPS, 4)}
+        if M == N == K and M in CUTLASS_B200_TFLOPS:
+            e["vs_cutlass_b200"] = round(tf / CUTLASS_B200_TFLOPS[M], 4)
+        out.append(e)
+        del sets, C
+
+    tensor_case("mxfp6_e2m3_gemm_4096x4096x4096", 4096, 4096, 4096, hk.E2M3, {}, {})
+    tensor_case("mxfp6_e3m2_gemm_4096x14336x8192_ffn", 4096, 14336, 8192, hk.E3M2,
+                dict(outlier_channels=8), dict(scale=0.02))
     assert hk.device_status() == 0
     return out
 
@@ -282,6 +316,8 @@ def run_single(args, torch, hk, device, peaks):
         cfg.update(M=m_, N=n_, K=k_)
     headline = not (args.small or args.shape)
     M, N, K = cfg["M"], cfg["N"], cfg["K"]
+    sampler = ClockSampler(device.index)
+    sampler.start()       # long before the timed region: the thread and NVML are in their stride when it starts
     n_sets = 4            # operand sets rotate (the reference's harness rotates 4, 8_wave.cu:255); with C they exceed L2
     sets = []
     for i in range(n_sets):
@@ -296,8 +332,6 @@ def run_single(args, torch, hk, device, peaks):
 
     flops_step = 2.0 * M * N * K
     # ---- device-resident timing: W warm-up steps, then exactly K steps between two events
-    sampler = ClockSampler(device.index)
-    sampler.start()                      # before the warm-up: the thread and NVML are in their stride when the region starts
     for i in range(W):
         step(i)
     assert hk.device_status() == 0
@@ -346,7 +380,6 @@ def run_single(args, torch, hk, device, peaks):
     # clocks settle as they would between unrelated kernels)
     extras = None
     if headline and not args.no_extras:
-        time.sleep(1.0)
         extras = extra_configs(torch, hk, device, peaks)
 
     # ---- end to end: operands start in pinned host memory, result ends in pinned host memory
@@ -455,6 +488,8 @@ def run_sharded(args, torch, hk, device, peaks, world, rank):
     M, N, K = cfg["M"], cfg["N"], cfg["K"]
     lo, hi = shard_bounds(N, world, rank)
     per = hi - lo
+    sampler = ClockSampler(device.index)
+    sampler.start()       # long before the timed region: the thread and NVML are in their stride when it starts
     a, sa = make_operands(torch, hk, M, K, "normal", 10, device)             # replicated: same seed on all ranks
     b, sb = make_operands(torch, hk, per, K, "normal", 100 + rank, device)   # this rank's rows of B
     try:
@@ -471,8 +506,6 @@ def run_sharded(args, torch, hk, device, peaks, world, rank):
         torch.cuda.synchronize()
 
     flops_step = 2.0 * M * N * K
-    sampler = ClockSampler(device.index)
-    sampler.start()                      # before the warm-up: the thread and NVML are in their stride when the region starts
     for i in range(W):
         step(i)
     assert hk.device_status() == 0

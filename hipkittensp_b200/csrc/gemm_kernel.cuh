@@ -39,12 +39,13 @@ struct GemmParams {
     int p_tile_rows;           // rows of P one tile covers (<= 128; 128 unless the rows of a streamed operand are dealt evenly to the CTAs)
     int q_tile_rows;           // rows of Q one tile covers (<= BN)
     int raw_tx_bytes;          // bytes the two scale-slab loads of a group report to their mbarrier
-    // two-CTAs-per-SM form: the operand ring is laid out at run time, because a tile of fewer than 128 rows of P needs
-    // less than the 16 KB a full box takes and the space saved buys more stages
+    // forms whose tiles hold fewer rows than a full box (skinny M): the operand ring is laid out at run time, because
+    // such a tile needs less than the 16 KB + BN * 128 bytes of a full stage and the space saved buys more stages
     int n_stages;              // stages in the ring (<= STAGES_MAX)
     int stage_stride;          // bytes from one stage to the next (a multiple of 1024)
     int q_off;                 // offset of the Q box inside a stage (rows of P rounded up to 8, times 128)
     int load_batch;            // K-blocks the producer requests back to back
+    int k_rot;                 // whole tiles start their K loop at a tile-dependent K-block and wrap around (kblocks % 4 == 0)
     int ldc;                   // row stride of C in elements (= N)
     int c_rows, c_cols;        // M, N
     uint32_t idesc;            // instruction descriptor without scale ids
@@ -136,6 +137,8 @@ __device__ __forceinline__ void affine_chunk(const GemmParams& P, uint32_t (&v)[
 }
 
 // CTAS_ = 2: a smaller pipeline so that two CTAs share an SM (BN <= 32: half the shared memory, a quarter of TMEM each).
+// (A third-size build, leaving room on every SM for a CTA of the next kernel of the stream, was measured and dropped:
+// its shorter ring cost 8 % at M = 16, N = 28672, more than the overlap of consecutive kernels gave back.)
 template <int BN_, bool SWAP_, bool STREAMK_, int CTAS_ = 1>
 struct GemmCfg {
     static constexpr int BN = BN_;
@@ -149,8 +152,13 @@ struct GemmCfg {
     static constexpr int STAGE_BYTES = P_BYTES + Q_BYTES;
     static constexpr int STAGES = CTAS_ == 2 ? (BN <= 16 ? 5 : 4)
                                              : BN >= 256 ? 4 : BN >= 128 ? 6 : BN >= 64 ? 8 : BN >= 32 ? 9 : 11;
+    // bytes of the operand ring (two CTAs per SM: 6 stages of 104 x 128-byte rows + Q for BN = 16, 5 for BN = 32, the
+    // stage of a 97-row tile; laid out at run time)
+    static constexpr int RING_BYTES = CTAS_ == 2 ? (BN <= 16 ? 6 * (13312 + 2048) : 5 * (13312 + 4096)) : STAGES * STAGE_BYTES;
     static constexpr int LOAD_BATCH = SWAP_ ? (STAGES >= 8 ? 4 : 2) : 1;   // K-blocks the producer requests together
-    static constexpr int STAGES_MAX = CTAS_ == 2 ? 8 : STAGES;             // barrier pairs provided (see GemmParams::n_stages)
+    // ring laid out at run time: the two-CTAs-per-SM form and the whole-tile 128 x 256 kernel (which serves skinny M)
+    static constexpr bool RUNTIME_RING = CTAS_ == 2 || (BN_ == 256 && !SWAP_ && !STREAMK_);
+    static constexpr int STAGES_MAX = RUNTIME_RING ? 8 : STAGES;           // barrier pairs provided (see GemmParams::n_stages)
     static constexpr int QATOMS = (BN + 127) / 128;      // 128-row scale atoms on the Q side
     static constexpr int RAW_SLOTS = (BN >= 256 || CTAS_ == 2) ? 2 : 4;  // each raw slab covers 4 K-blocks (16 scale bytes per row)
     static constexpr int RAW_Q_ROWS = BN < 32 ? 32 : BN;
@@ -167,19 +175,27 @@ struct GemmCfg {
     static constexpr int NUM_BARS = 2 * STAGES_MAX + 2 * RAW_SLOTS + 2 * ATOM_GROUPS + 5;
     // unswapped form: column scale and bias of the current tile for the fp32 epilogue (2 x BN floats, 16-byte aligned)
     static constexpr int AFF_BYTES = SWAP ? 0 : 2 * BN * 4 + 16;
-    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + RAW_SLOTS * RAW_BYTES + ATOM_GROUPS * GROUP_BYTES +
+    static constexpr int SMEM_BYTES = RING_BYTES + RAW_SLOTS * RAW_BYTES + ATOM_GROUPS * GROUP_BYTES +
                                       NUM_BARS * 8 + 64 + AFF_BYTES;
     static constexpr int SMEM_ALLOC = SMEM_BYTES + 1024;  // slack for the 1024-byte alignment of the operand ring
     static constexpr int THREADS = 256;
     static constexpr int GROUP_P = 8;                     // tile rasterisation: groups of 8 P-tiles share Q-tiles
-    static_assert(SMEM_ALLOC <= 232448 / CTAS_ - (CTAS_ == 2 ? 1024 : 0), "exceeds the shared memory this CTA can have");
+    static_assert(SMEM_ALLOC <= (CTAS_ == 1 ? 232448 : 233472 / CTAS_ - 1024), "exceeds the shared memory this CTA can have");
 };
 
 // One unit of work of a CTA: a K range of one output tile.
 struct Segment {
     int tile, p0, q0, k0, k1;
     int nseg, segidx;           // how many CTAs contribute to this tile, and which of them this is
+    int kofs;                   // K-block at which position k0 of the loop sits (the loop wraps at the last K-block)
 };
+// K-block that position i of a segment's loop addresses.  Skinny problems stream one operand once, every CTA from its own
+// rows; started together at K-block 0 all CTAs would ask for the same columns of every row at the same time (addresses
+// that differ by multiples of the row pitch, which fall on few DRAM channels).  Rotating each tile's loop spreads them.
+__device__ __forceinline__ int k_at(const GemmParams& P, const Segment& sg, int i) {
+    const int k = i + sg.kofs;
+    return k < P.kblocks ? k : k - P.kblocks;
+}
 
 template <class Cfg>
 struct SegIter {
@@ -228,11 +244,13 @@ struct SegIter {
             const int first = owner(t0, U, gridDim.x), last = owner(t0 + P.kblocks - 1, U, gridDim.x);
             s.nseg = last - first + 1;
             s.segidx = (int)blockIdx.x - first;
+            s.kofs = 0;
             coords(s.tile, s.p0, s.q0);
             return true;
         } else {
             if (tile >= num_tiles) return false;
             s.tile = tile; s.k0 = 0; s.k1 = P.kblocks; s.nseg = 1; s.segidx = 0;
+            s.kofs = P.k_rot ? (int)(((long long)tile * P.kblocks) / num_tiles) & ~3 : 0;
             coords(tile, s.p0, s.q0);
             tile += gridDim.x;
             return true;
@@ -291,7 +309,7 @@ mxfp6_gemm_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constan
 
     // ---- shared-memory carve-up
     const uint32_t stage_base = smem_base;
-    const uint32_t raw_base = stage_base + Cfg::STAGES * Cfg::STAGE_BYTES;
+    const uint32_t raw_base = stage_base + Cfg::RING_BYTES;
     const uint32_t atom_base = raw_base + Cfg::RAW_SLOTS * Cfg::RAW_BYTES;
     const uint32_t bar_base = atom_base + Cfg::ATOM_GROUPS * Cfg::GROUP_BYTES;
     auto bar_full = [&](int s) { return bar_base + 8u * s; };
@@ -302,11 +320,11 @@ mxfp6_gemm_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constan
     auto bar_atom_full = [&](int s) { return bar_base + 8u * (2 * SM_ + 2 * Cfg::RAW_SLOTS + s); };
     auto bar_atom_empty = [&](int s) { return bar_base + 8u * (2 * SM_ + 2 * Cfg::RAW_SLOTS + Cfg::ATOM_GROUPS + s); };
     const uint32_t bar_misc = bar_base + 8u * (2 * SM_ + 2 * Cfg::RAW_SLOTS + 2 * Cfg::ATOM_GROUPS);
-    // ring geometry: fixed at compile time, except in the two-CTAs-per-SM form
-    const int n_stages = Cfg::CTAS == 2 ? P.n_stages : Cfg::STAGES;
-    const uint32_t stage_stride = Cfg::CTAS == 2 ? (uint32_t)P.stage_stride : (uint32_t)Cfg::STAGE_BYTES;
-    const uint32_t q_off = Cfg::CTAS == 2 ? (uint32_t)P.q_off : (uint32_t)Cfg::P_BYTES;
-    const int load_batch = Cfg::CTAS == 2 ? P.load_batch : Cfg::LOAD_BATCH;
+    // ring geometry: fixed at compile time, except where tiles can be smaller than a full box
+    const int n_stages = Cfg::RUNTIME_RING ? P.n_stages : Cfg::STAGES;
+    const uint32_t stage_stride = Cfg::RUNTIME_RING ? (uint32_t)P.stage_stride : (uint32_t)Cfg::STAGE_BYTES;
+    const uint32_t q_off = Cfg::RUNTIME_RING ? (uint32_t)P.q_off : (uint32_t)Cfg::P_BYTES;
+    const int load_batch = Cfg::RUNTIME_RING ? P.load_batch : Cfg::LOAD_BATCH;
     auto bar_acc_full = [&](int b) { return bar_misc + 8u * b; };
     auto bar_acc_empty = [&](int b) { return bar_misc + 8u * (2 + b); };
     const uint32_t bar_ovl = bar_misc + 8u * 4;
@@ -361,6 +379,7 @@ mxfp6_gemm_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constan
         SegIter<Cfg> it(P);
         Segment sg;
         uint32_t n_stage = 0, n_raw = 0;
+        uint32_t st_idx = 0, st_phase = 0;        // ring position of stage number n_stage and the parity of its round (no division: the ring size may be a run-time value)
         uint32_t pre_stage = 0, pre_raw = 0;      // stages / scale slabs whose P half is already on its way
         bool ok = true;
         if (early) {
@@ -373,7 +392,7 @@ mxfp6_gemm_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constan
                         if (slabs && pre_raw < (uint32_t)Cfg::RAW_SLOTS) {
                             if (elect_one_sync()) {
                                 mbar_arrive_expect_tx(bar_raw_full(pre_raw), (uint32_t)P.raw_tx_bytes);
-                                tma_load_2d(raw_base + pre_raw * Cfg::RAW_BYTES, &tm_sfp, bar_raw_full(pre_raw), (k >> 2) * 16, s2.p0);
+                                tma_load_2d(raw_base + pre_raw * Cfg::RAW_BYTES, &tm_sfp, bar_raw_full(pre_raw), (k_at(P, s2, k) >> 2) * 16, s2.p0);
                             }
                             ++pre_raw;
                         } else {
@@ -382,7 +401,7 @@ mxfp6_gemm_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constan
                     }
                     if (elect_one_sync()) {
                         mbar_arrive_expect_tx(bar_full(pre_stage), (uint32_t)P.stage_tx_bytes);
-                        tma_load_2d(stage_base + pre_stage * stage_stride, &tm_p, bar_full(pre_stage), k * Cfg::BK, s2.p0);
+                        tma_load_2d(stage_base + pre_stage * stage_stride, &tm_p, bar_full(pre_stage), k_at(P, s2, k) * Cfg::BK, s2.p0);
                     }
                     __syncwarp();
                     ++pre_stage;
@@ -406,31 +425,35 @@ mxfp6_gemm_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constan
                             const uint32_t dst = raw_base + r * Cfg::RAW_BYTES;
                             if (n_raw >= pre_raw) {
                                 mbar_arrive_expect_tx(bar_raw_full(r), (uint32_t)P.raw_tx_bytes);
-                                tma_load_2d(dst, &tm_sfp, bar_raw_full(r), (k >> 2) * 16, sg.p0);
+                                tma_load_2d(dst, &tm_sfp, bar_raw_full(r), (k_at(P, sg, k) >> 2) * 16, sg.p0);
                             }
-                            tma_load_2d(dst + Cfg::BM * 16, &tm_sfq, bar_raw_full(r), (k >> 2) * 16, sg.q0);
+                            tma_load_2d(dst + Cfg::BM * 16, &tm_sfq, bar_raw_full(r), (k_at(P, sg, k) >> 2) * 16, sg.q0);
                         }
                         ++n_raw;
                     }
                 }
                 if (!ok) break;
                 // stages are released in order: when the last one of the batch is free, all of them are
-                const uint32_t last = n_stage + nb - 1;
-                ok = wait_bar_warp(bar_empty(last % n_stages), ((last / n_stages) & 1) ^ 1, abort_flag, P, kStatusTimeoutProducer);
+                uint32_t last = st_idx + nb - 1, last_phase = st_phase;
+                if (last >= (uint32_t)n_stages) { last -= n_stages; last_phase ^= 1; }
+                ok = wait_bar_warp(bar_empty(last), last_phase ^ 1, abort_flag, P, kStatusTimeoutProducer);
                 if (!ok) break;
                 if (elect_one_sync()) {
                     for (int j = 0; j < nb; ++j) {
-                        const int s = (n_stage + j) % n_stages;
+                        int s = (int)st_idx + j;
+                        if (s >= n_stages) s -= n_stages;
                         const uint32_t dst = stage_base + s * stage_stride;
                         if (n_stage + j >= pre_stage) {
                             mbar_arrive_expect_tx(bar_full(s), (uint32_t)P.stage_tx_bytes);
-                            tma_load_2d(dst, &tm_p, bar_full(s), (kb + j) * Cfg::BK, sg.p0);
+                            tma_load_2d(dst, &tm_p, bar_full(s), k_at(P, sg, kb + j) * Cfg::BK, sg.p0);
                         }
-                        tma_load_2d(dst + q_off, &tm_q, bar_full(s), (kb + j) * Cfg::BK, sg.q0);
+                        tma_load_2d(dst + q_off, &tm_q, bar_full(s), k_at(P, sg, kb + j) * Cfg::BK, sg.q0);
                     }
                 }
                 __syncwarp();
                 n_stage += nb;
+                st_idx += nb;
+                if (st_idx >= (uint32_t)n_stages) { st_idx -= n_stages; st_phase ^= 1; }
                 kb += nb;
             }
         }
@@ -440,6 +463,7 @@ mxfp6_gemm_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constan
         SegIter<Cfg> it(P);
         Segment sg;
         uint32_t n_kb = 0, n_seg = 0, n_grp = 0;
+        uint32_t st_idx = 0, st_phase = 0;        // ring position and round parity of K-block number n_kb
         bool ok = true;
         while (ok && it.next(sg)) {
             const int b = n_seg & 1;
@@ -452,12 +476,12 @@ mxfp6_gemm_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constan
             if (!ok) break;
             tc_fence_after();
             for (int kb = sg.k0; kb < sg.k1; ++kb) {
-                const int s = n_kb % n_stages;
+                const int s = (int)st_idx;
                 const int g = n_grp % Cfg::ATOM_GROUPS;
                 // the scale atoms arrive per group of 4 K-blocks (one raw slab)
                 if (kb == sg.k0 || (kb & 3) == 0)
                     ok = wait_bar_warp(bar_atom_full(g), (n_grp / Cfg::ATOM_GROUPS) & 1, abort_flag, P, kStatusTimeoutMma);
-                ok = ok && wait_bar_warp(bar_full(s), (n_kb / n_stages) & 1, abort_flag, P, kStatusTimeoutMma);
+                ok = ok && wait_bar_warp(bar_full(s), st_phase, abort_flag, P, kStatusTimeoutMma);
                 if (!ok) break;
                 const bool group_done = (kb & 3) == 3 || kb == sg.k1 - 1;
                 if (elect_one_sync()) {
@@ -482,6 +506,7 @@ mxfp6_gemm_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constan
                 }
                 __syncwarp();
                 ++n_kb;
+                if (++st_idx == (uint32_t)n_stages) { st_idx = 0; st_phase ^= 1; }
                 if (group_done) ++n_grp;
             }
             if (!ok) break;
@@ -527,7 +552,7 @@ mxfp6_gemm_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constan
                         }
                         mbar_arrive(bar_raw_empty(r));
                     } else {
-                        const int kb4 = kb & ~3;
+                        const int kb4 = k_at(P, sg, kb & ~3);
 #pragma unroll
                         for (int c = 0; c < 4; ++c) {
                             const int row = sg.p0 + lane + 32 * c;

@@ -353,6 +353,7 @@ mxfp6_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_co
         const uint32_t ovl0 = mapa_shared(bar_ovl, 0);
         const uint64_t pol_st = l2_policy(P.l2_store);
         PairUnit u;
+        long long t_prev_full = 0;            // when the previous unit's accumulator became ready (SM clock)
         for (int it = 0; ok && pair_unit(P, it, cluster_id, n_clusters, u); ++it) {
             const int p0 = u.p0, q0 = u.q0;
             const int b = n_seg & 1;

@@ -52,10 +52,14 @@ struct Options {
     int group_p = 16;        // MXFP6_GROUP_P: pair tiles per rasterisation group
     int quant_quad = 0;      // MXFP6_QUANT_PATH=quad: the plain-load quantiser
     int wait_ms = 2000;      // MXFP6_WAIT_MS: budget of one bounded wait (read when a device is first used)
-    int l2_load = 0, l2_store = 0;   // MXFP6_L2 = "load,store": eviction policy of the pair kernel's TMA traffic
+    // MXFP6_L2 = "load,store": L2 eviction policy of the pair kernel's TMA traffic (0 normal, 1 evict_first, 2 evict_last).
+    // Operand tiles are asked for again by other pairs and C is written once: keeping the former and letting the latter
+    // go first measured +2.6 % at 8192^3 and +2 % at 4096^3 against no hints.
+    int l2_load = 2, l2_store = 1;
     int tail_split = 1;      // MXFP6_TAIL_SPLIT: the pair kernel splits the tiles of its last partial wave along K
     int decode_rows = 1;     // MXFP6_DECODE_ROWS: skinny problems take the row-balanced kernel when they qualify
     int decode_stages = 0, decode_batch = 0;   // MXFP6_DECODE_RING = "stages,batch": ring of that kernel (0 = chosen by the library)
+    int k_rot = 1;           // MXFP6_K_ROT: the even-rows skinny forms start each tile's K loop at its own K-block
 };
 static Options g_opt;
 static std::once_flag g_opt_once;
@@ -76,6 +80,7 @@ static bool set_option(const char* name, const char* v) {
         if (v) sscanf(v, "%d,%d", &g_opt.l2_load, &g_opt.l2_store);
     } else if (!strcmp(name, "MXFP6_TAIL_SPLIT")) g_opt.tail_split = v ? atoi(v) : d.tail_split;
     else if (!strcmp(name, "MXFP6_DECODE_ROWS")) g_opt.decode_rows = v ? atoi(v) : d.decode_rows;
+    else if (!strcmp(name, "MXFP6_K_ROT")) g_opt.k_rot = v ? atoi(v) : d.k_rot;
     else if (!strcmp(name, "MXFP6_DECODE_RING")) {
         g_opt.decode_stages = d.decode_stages; g_opt.decode_batch = d.decode_batch;
         if (v) sscanf(v, "%d,%d", &g_opt.decode_stages, &g_opt.decode_batch);
@@ -84,7 +89,7 @@ static bool set_option(const char* name, const char* v) {
     return true;
 }
 static const char* const kOptionNames[] = {"MXFP6_FORCE_CFG", "MXFP6_NO_SF_TMA", "MXFP6_PDL", "MXFP6_GROUP_P", "MXFP6_QUANT_PATH",
-                                           "MXFP6_WAIT_MS", "MXFP6_L2", "MXFP6_TAIL_SPLIT", "MXFP6_DECODE_ROWS", "MXFP6_DECODE_RING"};
+                                           "MXFP6_WAIT_MS", "MXFP6_L2", "MXFP6_TAIL_SPLIT", "MXFP6_DECODE_ROWS", "MXFP6_DECODE_RING", "MXFP6_K_ROT"};
 static const Options& options() {
     std::call_once(g_opt_once, [] {
         for (const char* n : kOptionNames)
@@ -171,10 +176,28 @@ static int get_encode_fn(EncodeTiledFn* out) {
 // kind 5: quantiser source, bf16 viewed as [blocks, 32] (64-byte rows), box 32 x box_rows, 64-byte swizzle
 // kind 6: re-quantised fp6 output bytes [rows, 3N/4] (inner = bytes per row), box 48 x box_rows, no swizzle
 // kind 7: re-quantised fp8 output bytes [rows, N], box 64 x box_rows, 64-byte swizzle
-// Encoding is pure host arithmetic (no driver state), so maps are built where they are needed and kept inside the
-// launch recipe of the call that uses them.
+// Encoded maps are kept inside the launch recipe of the call that uses them; a small per-thread table of recent
+// encodings serves callers that alternate between a few buffers with otherwise new argument combinations.
+struct MapKey {
+    const void* ptr; int64_t rows, inner, stride; int box_rows, kind;
+    bool operator==(const MapKey& o) const {
+        return ptr == o.ptr && rows == o.rows && inner == o.inner && stride == o.stride && box_rows == o.box_rows && kind == o.kind;
+    }
+};
+constexpr int kMapSlots = 64;
+struct MapCache {
+    MapKey key[kMapSlots];
+    CUtensorMap map[kMapSlots];
+    bool used[kMapSlots] = {};
+};
+static thread_local std::unique_ptr<MapCache> t_maps;
+
 static int make_map(const void* ptr, int64_t rows, int64_t inner, int box_rows, int kind, CUtensorMap* out,
                     int64_t stride_bytes = 0) {
+    const MapKey mk{ptr, rows, inner, stride_bytes, box_rows, kind};
+    if (!t_maps) t_maps.reset(new MapCache());
+    const size_t h = ((reinterpret_cast<uintptr_t>(ptr) >> 8) * 0x9E3779B97F4A7C15ull + (uint64_t)rows * 31 + (uint64_t)box_rows * 7 + (uint64_t)kind) % kMapSlots;
+    if (t_maps->used[h] && t_maps->key[h] == mk) { *out = t_maps->map[h]; return MXFP6_OK; }
     EncodeTiledFn encode = nullptr;
     int rc = get_encode_fn(&encode);
     if (rc) return rc;
@@ -200,6 +223,7 @@ static int make_map(const void* ptr, int64_t rows, int64_t inner, int box_rows, 
     if (r != CUDA_SUCCESS)
         return fail(MXFP6_ERR_CUDA, "cuTensorMapEncodeTiled(kind=%d rows=%lld inner=%lld box_rows=%d) failed with %d",
                     kind, (long long)rows, (long long)inner, box_rows, (int)r);
+    t_maps->key[h] = mk; t_maps->map[h] = *out; t_maps->used[h] = true;
     return MXFP6_OK;
 }
 
@@ -282,11 +306,16 @@ static Plan make_plan(int64_t M, int64_t N, int64_t K, int sm_count, bool allow_
             const int64_t slots = 2 * (int64_t)sm_count;
             const int64_t waves = ceil_div(N, slots * 128);
             const int64_t rows = ceil_div(N, slots * waves);
-            if (rows >= 48) { p.streamk = false; p.ctas = 2; p.p_tile = (int)rows; }
+            // (measured at K = 8192: 97 rows per CTA, N = 28672, 34.9 against 38.5 us for the K-split form; 49 rows per
+            // CTA, N = 14336, 27.7 against 24.5 us: with few rows per CTA the K-split form's parallelism along K wins)
+            if (rows >= 80) { p.streamk = false; p.ctas = 2; p.p_tile = (int)rows; }
         } else if (!p.swap && wide_rows && p.bn == 256) {
             const int64_t waves = ceil_div(N, (int64_t)sm_count * 256);
             const int64_t rows = (ceil_div(N, (int64_t)sm_count * waves) + 7) / 8 * 8;
-            if (rows >= 128 && rows <= 256) p.q_tile = (int)rows;
+            if (rows >= 128 && rows <= 256) {
+                p.q_tile = (int)rows;
+                p.p_tile = (int)((M + 7) / 8 * 8);      // the rows of A that exist: the box, and with it the stage, shrinks
+            }
         }
     }
     p.tiles_p = ceil_div(prow, p.p_tile);
@@ -389,7 +418,7 @@ struct Recipe {
 };
 
 // A small per-thread table: no lock on the hit path.
-constexpr int kRecipeSlots = 16;
+constexpr int kRecipeSlots = 32;
 struct RecipeCache {
     Recipe slot[kRecipeSlots];
     unsigned next = 0;
@@ -554,18 +583,22 @@ static int gemm_impl(const void* a, const void* sfa, const void* b, const void* 
     P.tiles_p = pl.tiles_p; P.tiles_q = pl.tiles_q;
     P.p_tile_rows = pl.p_tile; P.q_tile_rows = pl.q_tile;
     P.raw_tx_bytes = (p_box + pl.q_tile) * 16;
-    if (pl.ctas == 2) {
-        // ring of the two-CTAs-per-SM form: a stage holds the tile's rows of P rounded up to 8 (whole 1024-byte swizzle
-        // groups) and the Q box; as many stages as the ring's bytes allow (5 x 18 KB for BN = 16, 4 x 20 KB for BN = 32)
-        const int ring = pl.bn <= 16 ? 5 * (16384 + 16 * 128) : 4 * (16384 + 32 * 128);
+    if (!pl.pair && (pl.ctas == 2 || (pl.bn == 256 && !pl.swap && !pl.streamk))) {
+        // Ring laid out at run time: a stage holds the tile's rows of P and of Q, each rounded up to 8 rows (whole
+        // 1024-byte swizzle groups); as many stages as the bytes the kernel variant reserves for its ring allow
+        // (90 KB for BN = 16 and 85 KB for BN = 32 with two CTAs per SM, 4 x 48 KB for BN = 256).
+        const int ring = pl.ctas == 2 ? (pl.bn <= 16 ? 6 * (13312 + 2048) : 5 * (13312 + 4096)) : 4 * (16384 + 256 * 128);
         P.q_off = (pl.p_tile + 7) / 8 * 1024;
-        P.stage_stride = P.q_off + pl.bn * 128;
+        P.stage_stride = P.q_off + (pl.q_tile + 7) / 8 * 1024;
         int ns = ring / P.stage_stride;
         if (ns > 8) ns = 8;
         if (o.decode_stages >= 2 && o.decode_stages <= ns) ns = o.decode_stages;
         P.n_stages = ns;
-        P.load_batch = ns >= 8 ? 4 : ns >= 6 ? 3 : 2;
+        P.load_batch = !pl.swap ? 1 : ns >= 8 ? 4 : ns >= 6 ? 3 : 2;
         if (o.decode_batch >= 1 && o.decode_batch <= ns / 2) P.load_batch = o.decode_batch;
+        // the even-rows forms of skinny problems (tiles narrower than a box) rotate their K loops
+        const bool even_rows = pl.ctas == 2 || pl.q_tile != pl.bn;
+        P.k_rot = (even_rows && o.k_rot && (K / 128) % 4 == 0) ? 1 : 0;
     }
     P.ldc = (int)dst.ldc; P.c_rows = (int)M; P.c_cols = (int)N;
     P.idesc = make_idesc_m(fmt_mma_code(fp), fmt_mma_code(fq), pl.pair ? 256u : 128u, (uint32_t)pl.bn);

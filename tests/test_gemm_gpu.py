@@ -122,18 +122,18 @@ def test_pair_kernel_scale_plain_load_path_unaligned_scales():
     _case("lognormal", 512, 768, 1024, seed=6, force="256,0,0,1")
 
 
-@pytest.mark.parametrize("M,N,K", [(16, 296 * 48, 512), (1, 296 * 48 + 40, 384), (32, 296 * 60 + 8, 640), (7, 38000, 256),
-                                   (64, 148 * 160, 512), (128, 148 * 200 + 24, 384), (48, 148 * 256 + 72, 256)])
+@pytest.mark.parametrize("M,N,K", [(16, 296 * 80, 512), (1, 296 * 80 + 40, 384), (32, 296 * 90 + 8, 640), (7, 50000, 256),
+                                   (64, 148 * 160, 512), (128, 148 * 200 + 24, 384), (48, 46000, 256)])
 def test_even_rows_forms(M, N, K):
     """Skinny M against many weight rows: the weight rows are dealt evenly to the CTAs (tiles of 48..128 rows of B in
     the swapped form for M <= 32, column tiles of a multiple of 8 between 128 and 256 in the unswapped form), including
-    tile counts that do not divide N and more than one tile per CTA."""
+    tile counts that do not divide N and more than one tile per CTA (N above 296 x 128)."""
     _case("decode", M, N, K, seed=M + N)
 
 
 def test_even_rows_form_matches_k_split_form():
     """Both skinny forms on the same problem: equal up to the summation order of split tiles."""
-    pa, sa, pb, sb = quantized_inputs("decode", 16, 296 * 64, 1024, seed=3)
+    pa, sa, pb, sb = quantized_inputs("decode", 16, 296 * 88, 1024, seed=3)
     c1 = run_gpu(pa, sa, pb, sb, R.E2M3)
     hk.debug_option("MXFP6_DECODE_ROWS", "0")
     try:
@@ -311,6 +311,22 @@ def test_b_static_flag_back_to_back(M):
     want = hk.gemm(t[0], t[1], t[2], t[3])
     outs = [torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda") for _ in range(6)]
     for o in outs:                                   # six launches queued without a host sync in between
+        hk.dispatch_micro(t[0], t[2], o, t[1], t[3], R.E2M3, b_static=True)
+    assert hk.device_status() == 0
+    for o in outs:
+        assert torch.equal(o.view(torch.int16), want.view(torch.int16))
+    ref, absdot = oracle_f64(pa, sa, pb, sb, R.E2M3)
+    check(want.float().cpu().numpy(), ref, absdot)
+
+
+@pytest.mark.parametrize("M,N,K", [(16, 296 * 82, 1024), (32, 296 * 97, 512)])
+def test_b_static_flag_even_rows_form(M, N, K):
+    """The same promise in the even-rows skinny form (two CTAs per SM, rotated K loops)."""
+    pa, sa, pb, sb = quantized_inputs("decode", M, N, K, seed=M)
+    t = [torch.from_numpy(x).cuda() for x in (pa, sa, pb, sb)]
+    want = hk.gemm(t[0], t[1], t[2], t[3])
+    outs = [torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda") for _ in range(6)]
+    for o in outs:
         hk.dispatch_micro(t[0], t[2], o, t[1], t[3], R.E2M3, b_static=True)
     assert hk.device_status() == 0
     for o in outs:

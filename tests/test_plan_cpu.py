@@ -64,7 +64,7 @@ def _cover_pair(pl, M, N):
 SHAPES = [(8192, 8192, 8192), (4096, 4096, 4096), (4096, 14336, 8192), (16384, 7168, 8192), (2304, 2560, 256),
           (2204, 2500, 384), (1, 28672, 8192), (16, 28672, 8192), (32, 28672, 8192), (64, 28672, 8192), (128, 28672, 8192),
           (16, 57344, 1024), (7, 38000, 256), (16, 4096, 4096), (48, 37960, 256), (96, 23680, 512), (130, 200, 256),
-          (300, 514, 384), (1536, 1797, 256), (257, 9999, 128), (33, 1024, 1024), (16, 296 * 48, 512)]
+          (300, 514, 384), (1536, 1797, 256), (257, 9999, 128), (33, 1024, 1024), (16, 296 * 80, 512), (16, 14336, 8192)]
 
 
 @pytest.mark.parametrize("M,N,K", SHAPES)
@@ -81,7 +81,7 @@ def test_plan_covers_c_exactly_once(M, N, K):
         if pl["streamk"]:
             assert pl["p_tile"] == 128 and pl["q_tile"] == pl["bn"]        # split tiles keep the fixed tile shape
         if pl["ctas"] == 2:
-            assert pl["swap"] and not pl["streamk"] and pl["bn"] <= 32 and 48 <= pl["p_tile"] <= 128
+            assert pl["swap"] and not pl["streamk"] and pl["bn"] <= 32 and 80 <= pl["p_tile"] <= 128
         if not pl["swap"] and pl["q_tile"] != pl["bn"]:
             assert pl["q_tile"] % 8 == 0 and 128 <= pl["q_tile"] <= 256
         cover = _cover_single(pl, M, N)
