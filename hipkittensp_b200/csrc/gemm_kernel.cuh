@@ -57,6 +57,7 @@ struct GemmParams {
     __nv_bfloat16* c;          // first element of this GEMM's block inside destination 0 (row stride ldc)
     __nv_bfloat16* c_more[7];  // the same position in further destinations (peer GPUs' copies of C)
     int ndst;                  // number of destinations, 1..8
+    int push_rotate;           // pair kernel: the order in which a piece goes to the peer destinations rotates from piece to piece
     int c_tma;                 // pair kernel: C is stored by TMA (16-byte aligned destinations and row stride); else by plain stores
     uint8_t* q_out;            // re-quantised output instead of bf16 C: operand bytes [M, 3N/4 or N] ...
     uint8_t* q_scales;         // ... and E8M0 scales [M, N/32], blocks of 32 along N
@@ -137,6 +138,8 @@ __device__ __forceinline__ void affine_chunk(const GemmParams& P, uint32_t (&v)[
 }
 
 // CTAS_ = 2: a smaller pipeline so that two CTAs share an SM (BN <= 32: half the shared memory, a quarter of TMEM each).
+// (For 32 < M <= 64 the same form with BN = 64 has room for 4 stages only and measured 45.3 us against 41.2 us for whole
+// unswapped tiles at N = 28672, K = 8192.)
 // (A third-size build, leaving room on every SM for a CTA of the next kernel of the stream, was measured and dropped:
 // its shorter ring cost 8 % at M = 16, N = 28672, more than the overlap of consecutive kernels gave back.)
 template <int BN_, bool SWAP_, bool STREAMK_, int CTAS_ = 1>
@@ -171,7 +174,7 @@ struct GemmCfg {
     static constexpr int SF_COL = OVERLAP ? 480 : 2 * BN;
     // two CTAs of an SM share its 512 columns: each takes the power of two that holds its two accumulators and 32 scale columns
     static constexpr int TMEM_COLS = CTAS_ == 2 ? (2 * BN + 32 <= 64 ? 64 : 2 * BN + 32 <= 128 ? 128 : 256) : 512;
-    static_assert(CTAS_ == 1 || (CTAS_ == 2 && BN <= 64 && !STREAMK_), "two CTAs per SM: small accumulators, whole tiles");
+    static_assert(CTAS_ == 1 || (CTAS_ == 2 && BN <= 32 && !STREAMK_), "two CTAs per SM: small accumulators, whole tiles");
     static constexpr int NUM_BARS = 2 * STAGES_MAX + 2 * RAW_SLOTS + 2 * ATOM_GROUPS + 5;
     // unswapped form: column scale and bias of the current tile for the fp32 epilogue (2 x BN floats, 16-byte aligned)
     static constexpr int AFF_BYTES = SWAP ? 0 : 2 * BN * 4 + 16;

@@ -213,9 +213,11 @@ mxfp6_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_co
                     const uint32_t dst = stage_base + s * Cfg::STAGE_BYTES;
                     const uint32_t full0 = mapa_shared(bar_full(s), 0);
                     // the even CTA announces the bytes of both CTAs' loads for this stage
+                    {
                     if (leader) mbar_arrive_expect_tx(bar_full(s), 2u * tx);
                     tma_load_2d_pair_hint(dst, &tm_p, full0, kb * Cfg::BK, my_p, pol_ld);
                     tma_load_2d_pair_hint(dst + Cfg::P_BYTES, tq, full0, kb * Cfg::BK, my_q, pol_ld);
+                    }
                 }
                 __syncwarp();
                 ++n_stage;
@@ -353,7 +355,6 @@ mxfp6_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_co
         const uint32_t ovl0 = mapa_shared(bar_ovl, 0);
         const uint64_t pol_st = l2_policy(P.l2_store);
         PairUnit u;
-        long long t_prev_full = 0;            // when the previous unit's accumulator became ready (SM clock)
         for (int it = 0; ok && pair_unit(P, it, cluster_id, n_clusters, u); ++it) {
             const int p0 = u.p0, q0 = u.q0;
             const int b = n_seg & 1;
@@ -500,7 +501,16 @@ mxfp6_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_co
                 fence_proxy_async_smem();
                 asm volatile("bar.sync 1, 128;" ::: "memory");
                 if (etid == 0) {
-                    for (int d = 0; d < P.ndst; ++d) tma_store_2d_hint(&cmaps.m[d], buf, q0 + piece * OC, my_p0, pol_st);
+                    // the local copy first, then the peers, starting with a different peer for every piece and CTA, so that
+                    // the CTAs of one GPU do not all aim at the same peer at the same moment
+                    tma_store_2d_hint(&cmaps.m[0], buf, q0 + piece * OC, my_p0, pol_st);
+                    const int peers = P.ndst - 1;
+                    const int first = (peers > 1 && P.push_rotate) ? (int)((n_out + blockIdx.x) % (uint32_t)peers) : 0;
+                    for (int i = 0; i < peers; ++i) {
+                        int d = first + i;
+                        if (d >= peers) d -= peers;
+                        tma_store_2d_hint(&cmaps.m[1 + d], buf, q0 + piece * OC, my_p0, pol_st);
+                    }
                     bulk_commit_group();
                 }
                 ++n_out;

@@ -59,6 +59,7 @@ struct Options {
     int tail_split = 1;      // MXFP6_TAIL_SPLIT: the pair kernel splits the tiles of its last partial wave along K
     int decode_rows = 1;     // MXFP6_DECODE_ROWS: skinny problems take the row-balanced kernel when they qualify
     int decode_stages = 0, decode_batch = 0;   // MXFP6_DECODE_RING = "stages,batch": ring of that kernel (0 = chosen by the library)
+    int push_rotate = 1;     // MXFP6_PUSH_ROTATE: pair kernel, rotate the order of the peer destinations from piece to piece
     int k_rot = 1;           // MXFP6_K_ROT: the even-rows skinny forms start each tile's K loop at its own K-block
 };
 static Options g_opt;
@@ -81,6 +82,7 @@ static bool set_option(const char* name, const char* v) {
     } else if (!strcmp(name, "MXFP6_TAIL_SPLIT")) g_opt.tail_split = v ? atoi(v) : d.tail_split;
     else if (!strcmp(name, "MXFP6_DECODE_ROWS")) g_opt.decode_rows = v ? atoi(v) : d.decode_rows;
     else if (!strcmp(name, "MXFP6_K_ROT")) g_opt.k_rot = v ? atoi(v) : d.k_rot;
+    else if (!strcmp(name, "MXFP6_PUSH_ROTATE")) g_opt.push_rotate = v ? atoi(v) : d.push_rotate;
     else if (!strcmp(name, "MXFP6_DECODE_RING")) {
         g_opt.decode_stages = d.decode_stages; g_opt.decode_batch = d.decode_batch;
         if (v) sscanf(v, "%d,%d", &g_opt.decode_stages, &g_opt.decode_batch);
@@ -89,7 +91,7 @@ static bool set_option(const char* name, const char* v) {
     return true;
 }
 static const char* const kOptionNames[] = {"MXFP6_FORCE_CFG", "MXFP6_NO_SF_TMA", "MXFP6_PDL", "MXFP6_GROUP_P", "MXFP6_QUANT_PATH",
-                                           "MXFP6_WAIT_MS", "MXFP6_L2", "MXFP6_TAIL_SPLIT", "MXFP6_DECODE_ROWS", "MXFP6_DECODE_RING", "MXFP6_K_ROT"};
+                                           "MXFP6_WAIT_MS", "MXFP6_L2", "MXFP6_TAIL_SPLIT", "MXFP6_DECODE_ROWS", "MXFP6_DECODE_RING", "MXFP6_K_ROT", "MXFP6_PUSH_ROTATE"};
 static const Options& options() {
     std::call_once(g_opt_once, [] {
         for (const char* n : kOptionNames)
@@ -612,6 +614,7 @@ static int gemm_impl(const void* a, const void* sfa, const void* b, const void* 
     P.c = (__nv_bfloat16*)c;
     for (int i = 1; i < dst.n; ++i) P.c_more[i - 1] = (__nv_bfloat16*)dst.c[i];
     P.ndst = dst.n;
+    P.push_rotate = o.push_rotate;
     P.c_tma = (q_fmt >= 0 || dest_by_tma(dst)) ? 1 : 0;
     P.q_out = (uint8_t*)q_out; P.q_scales = (uint8_t*)q_scales; P.q_fmt = q_fmt;
     P.q_ld = q_fmt < 0 ? 0 : (fmt_is_fp8(q_fmt) ? N : N * 3 / 4);
