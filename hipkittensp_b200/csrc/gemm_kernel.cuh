@@ -45,6 +45,8 @@ struct GemmParams {
     int stage_stride;          // bytes from one stage to the next (a multiple of 1024)
     int q_off;                 // offset of the Q box inside a stage (rows of P rounded up to 8, times 128)
     int load_batch;            // K-blocks the producer requests back to back
+    int pf_dist;               // skinny forms: the streamed operand's boxes are prefetched into L2 this many K-blocks ahead of their load (0 = off)
+    int pf_q;                  // ... and the streamed operand is Q (unswapped form) rather than P
     int k_rot;                 // whole tiles start their K loop at a tile-dependent K-block and wrap around (kblocks % 4 == 0)
     int ldc;                   // row stride of C in elements (= N)
     int c_rows, c_cols;        // M, N
@@ -58,6 +60,7 @@ struct GemmParams {
     __nv_bfloat16* c_more[7];  // the same position in further destinations (peer GPUs' copies of C)
     int ndst;                  // number of destinations, 1..8
     int push_rotate;           // pair kernel: the order in which a piece goes to the peer destinations rotates from piece to piece
+    int c_vec16;               // pair kernel, plain stores: destinations and row stride are 16-byte multiples and N % 8 == 0
     int c_tma;                 // pair kernel: C is stored by TMA (16-byte aligned destinations and row stride); else by plain stores
     uint8_t* q_out;            // re-quantised output instead of bf16 C: operand bytes [M, 3N/4 or N] ...
     uint8_t* q_scales;         // ... and E8M0 scales [M, N/32], blocks of 32 along N
@@ -436,6 +439,17 @@ mxfp6_gemm_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constan
                     }
                 }
                 if (!ok) break;
+                // Far ahead of the ring: the weight boxes of later K-blocks are asked into L2 now, so that the ring's own
+                // loads find them there and the bytes in flight from DRAM are not limited by shared memory.
+                if (P.pf_dist > 0 && elect_one_sync()) {
+                    const int first = kb == sg.k0 ? kb + nb : kb + P.pf_dist;       // the first batch of a tile prefetches the whole window
+                    const int last_pf = min(sg.k1, kb + nb + P.pf_dist);
+                    for (int k = max(first, kb + nb); k < last_pf; ++k) {
+                        if (P.pf_q) tma_prefetch_2d(&tm_q, k_at(P, sg, k) * Cfg::BK, sg.q0);
+                        else tma_prefetch_2d(&tm_p, k_at(P, sg, k) * Cfg::BK, sg.p0);
+                    }
+                }
+                __syncwarp();
                 // stages are released in order: when the last one of the batch is free, all of them are
                 uint32_t last = st_idx + nb - 1, last_phase = st_phase;
                 if (last >= (uint32_t)n_stages) { last -= n_stages; last_phase ^= 1; }
@@ -555,23 +569,37 @@ mxfp6_gemm_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constan
                         }
                         mbar_arrive(bar_raw_empty(r));
                     } else {
+                        // Scale rows that cannot be TMA boxes: the 4-byte words of the group's K-blocks are read from
+                        // global memory directly.  Four adjacent lanes read the four words of one row (16 contiguous
+                        // bytes), so an instruction touches 8 rows, not 32; each word goes straight to its place in the
+                        // atom of its K-block: row (r % 32), 4-byte column (r / 32).
                         const int kb4 = k_at(P, sg, kb & ~3);
+                        const int w = lane & 3;
+                        constexpr int NI = 16 + 4 * QG;             // 8 rows per step: 128 rows of P, then the 32-row groups of Q
+                        uint32_t v[NI];
 #pragma unroll
-                        for (int c = 0; c < 4; ++c) {
-                            const int row = sg.p0 + lane + 32 * c;
-#pragma unroll
-                            for (int jj = 0; jj < 4; ++jj)
-                                rp[c][jj] = (row < P.p_rows && kb4 + jj < P.kblocks)
-                                    ? *reinterpret_cast<const uint32_t*>(P.sfp + (size_t)row * P.sf_ld + (kb4 + jj) * 4) : 0u;
+                        for (int i = 0; i < NI; ++i) {
+                            const int ridx = 8 * i + (lane >> 2);
+                            const bool is_p = i < 16;
+                            const int row = is_p ? sg.p0 + ridx : sg.q0 + ridx - 128;
+                            const bool live = row < (is_p ? P.p_rows : P.q_rows) && kb4 + w < P.kblocks;
+                            v[i] = live ? __ldg(reinterpret_cast<const uint32_t*>((is_p ? P.sfp : P.sfq) + (size_t)row * P.sf_ld + (kb4 + w) * 4)) : 0u;
                         }
+                        const int g = n_grp % Cfg::ATOM_GROUPS;
+                        ok = wait_bar_warp(bar_atom_empty(g), ((n_grp / Cfg::ATOM_GROUPS) & 1) ^ 1, abort_flag, P, kStatusTimeoutScale);
+                        if (!ok) break;
+                        uint8_t* atom = smem_gen + (atom_base - smem_base) + g * Cfg::GROUP_BYTES + w * Cfg::ATOM_BYTES;
 #pragma unroll
-                        for (int c = 0; c < Cfg::QATOMS * 4; ++c) {
-                            const int row = sg.q0 + lane + 32 * c;
-#pragma unroll
-                            for (int jj = 0; jj < 4; ++jj)
-                                rq[c][jj] = (c < QG && row < P.q_rows && kb4 + jj < P.kblocks)
-                                    ? *reinterpret_cast<const uint32_t*>(P.sfq + (size_t)row * P.sf_ld + (kb4 + jj) * 4) : 0u;
+                        for (int i = 0; i < NI; ++i) {
+                            const int ridx = 8 * i + (lane >> 2);
+                            const int part = ridx >> 7, r = ridx & 127;     // atom 0: P, then one atom per 128 rows of Q
+                            *reinterpret_cast<uint32_t*>(atom + 512 * part + (r & 31) * 16 + (r >> 5) * 4) = v[i];
                         }
+                        fence_proxy_async_smem();
+                        mbar_arrive(bar_atom_full(g));
+                        ++n_grp;
+                        kb = kb_next;
+                        continue;
                     }
                     const int g = n_grp % Cfg::ATOM_GROUPS;
                     ok = wait_bar_warp(bar_atom_empty(g), ((n_grp / Cfg::ATOM_GROUPS) & 1) ^ 1, abort_flag, P, kStatusTimeoutScale);

@@ -307,25 +307,35 @@ mxfp6_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_co
                     }
                     mbar_arrive(bar_raw_empty(r));
                 } else {
-                    // scale rows that cannot be TMA boxes (K/32 not a multiple of 16, or unaligned arrays): the 4-byte
-                    // words of the group's K-blocks are read from global memory directly
+                    // Scale rows that cannot be TMA boxes (K/32 not a multiple of 16, or unaligned arrays): the 4-byte
+                    // words of the group's K-blocks are read from global memory directly.  Four adjacent lanes read the
+                    // four words of one row (16 contiguous bytes), so an instruction touches 8 rows, not 32; each word goes
+                    // straight to its place in the atom of its K-block: row (r % 32), 4-byte column (r / 32).
                     const int p0 = u.p0, q0 = u.q0;
+                    const int w = lane & 3;
+                    uint32_t v[48];
 #pragma unroll
-                    for (int c = 0; c < 4; ++c) {
-                        const int row = p0 + 128 * (int)rank + lane + 32 * c;
-#pragma unroll
-                        for (int jj = 0; jj < 4; ++jj)
-                            rp[c][jj] = (row < P.p_rows && kb + jj < P.kblocks)
-                                ? __ldg(reinterpret_cast<const uint32_t*>(P.sfp + (size_t)row * P.sf_ld + (kb + jj) * 4)) : 0u;
+                    for (int i = 0; i < 48; ++i) {
+                        const int ridx = 8 * i + (lane >> 2);           // 0..127: my rows of P, 128..383: the unit's rows of Q
+                        const bool is_p = i < 16;
+                        const int row = is_p ? p0 + 128 * (int)rank + ridx : q0 + ridx - 128;
+                        const bool live = row < (is_p ? P.p_rows : P.q_rows) && kb + w < P.kblocks;
+                        v[i] = live ? __ldg(reinterpret_cast<const uint32_t*>((is_p ? P.sfp : P.sfq) + (size_t)row * P.sf_ld + (kb + w) * 4)) : 0u;
                     }
+                    const int g = n_grp % Cfg::ATOM_GROUPS;
+                    ok = wait_bar_warp(bar_atom_empty(g), ((n_grp / Cfg::ATOM_GROUPS) & 1) ^ 1, abort_flag, P, kStatusTimeoutScale);
+                    if (!ok) break;
+                    uint8_t* atom = smem_gen + (atom_base - smem_base) + g * Cfg::GROUP_BYTES + w * Cfg::ATOM_BYTES;
 #pragma unroll
-                    for (int c = 0; c < 8; ++c) {
-                        const int row = q0 + lane + 32 * c;
-#pragma unroll
-                        for (int jj = 0; jj < 4; ++jj)
-                            rq[c][jj] = (row < P.q_rows && kb + jj < P.kblocks)
-                                ? __ldg(reinterpret_cast<const uint32_t*>(P.sfq + (size_t)row * P.sf_ld + (kb + jj) * 4)) : 0u;
+                    for (int i = 0; i < 48; ++i) {
+                        const int ridx = 8 * i + (lane >> 2);
+                        const int part = ridx >> 7, r = ridx & 127;     // atom 0: P, atoms 1 and 2: Q rows 0..127 and 128..255
+                        *reinterpret_cast<uint32_t*>(atom + 512 * part + (r & 31) * 16 + (r >> 5) * 4) = v[i];
                     }
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive_cluster(mapa_shared(bar_atom_full(g), 0));
+                    continue;
                 }
                 const int g = n_grp % Cfg::ATOM_GROUPS;
                 ok = wait_bar_warp(bar_atom_empty(g), ((n_grp / Cfg::ATOM_GROUPS) & 1) ^ 1, abort_flag, P, kStatusTimeoutScale);
@@ -474,10 +484,25 @@ mxfp6_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_co
                                  ::"r"(rowaddr + ((c ^ sw) << 4)), "r"(x0), "r"(x1), "r"(x2), "r"(x3) : "memory");
                 }
                 if (!P.c_tma) {
-                    // C whose rows are not 16-byte multiples cannot be a TMA destination: the staged piece is written out
-                    // with plain stores, a warp per row at a time (32 lanes x 2 columns = the row's 128 bytes)
+                    // The staged piece is written out with plain stores instead of TMA stores: always when C cannot be a TMA
+                    // destination (rows that are not 16-byte multiples), where each warp writes its 32 rows 4 bytes per lane;
+                    // with 16-byte rows (c_vec16) 16 bytes per lane, 4 rows per instruction.
                     asm volatile("bar.sync 1, 128;" ::: "memory");
                     const uint8_t* stage = smem_gen + (buf - smem_base);
+                    if (P.c_vec16) {
+                        const int chunk = lane & 7;                       // 16-byte chunk = 8 columns
+                        const int col = q0 + piece * OC + 8 * chunk;
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            const int r = quad * 32 + 4 * i + (lane >> 3);
+                            const int row = my_p0 + r;
+                            if (row < P.c_rows && col < P.c_cols) {       // N is a multiple of 8 here: a chunk is inside or outside
+                                const uint4 x = *reinterpret_cast<const uint4*>(stage + r * (OC * 2) + ((chunk ^ (r & 7)) << 4));
+                                for (int d = 0; d < P.ndst; ++d)
+                                    *reinterpret_cast<uint4*>((d == 0 ? P.c : P.c_more[d - 1]) + (size_t)row * P.ldc + col) = x;
+                            }
+                        }
+                    } else {
                     const int col = q0 + piece * OC + 2 * lane;
 #pragma unroll 4
                     for (int r = quad * 32; r < quad * 32 + 32; ++r) {
@@ -493,6 +518,7 @@ mxfp6_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_co
                                 if (col + 1 < P.c_cols) dst[1] = __ushort_as_bfloat16((unsigned short)(x >> 16));
                             }
                         }
+                    }
                     }
                     // (the next use of this buffer is two pieces away, behind the barrier that opens every piece)
                     ++n_out;

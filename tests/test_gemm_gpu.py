@@ -170,6 +170,17 @@ def test_pair_kernel_plain_store_path(shape, force):
     _case("lognormal", M, N, K, seed=N, force=force)
 
 
+@pytest.mark.parametrize("shape", [(512, 768, 512), (300, 520, 384)])
+def test_pair_kernel_plain_store_path_16_byte_rows(shape):
+    """The plain-store epilogue where C's rows are 16-byte multiples (16 bytes per lane), forced by the test switch."""
+    M, N, K = shape
+    hk.debug_option("MXFP6_C_PLAIN", "1")
+    try:
+        _case("lognormal", M, N, K, seed=N + 1, force="256,0,0,1")
+    finally:
+        hk.debug_option("MXFP6_C_PLAIN", None)
+
+
 def test_pair_kernel_plain_store_odd_window():
     """Several destinations whose column window starts at an odd element of rows with an odd stride."""
     hk.debug_option("MXFP6_FORCE_CFG", "256,0,0,1")
@@ -494,6 +505,60 @@ def test_calls_can_be_captured_in_a_cuda_graph(shape):
     hk.dispatch_micro(pa, pb, want, sa, sb, R.E2M3)
     assert hk.device_status() == 0
     assert torch.equal(C, want)
+
+
+_SCRATCH_GROWTH = r"""
+import sys, torch
+sys.path.insert(0, sys.argv[1])
+import hipkittensp_b200 as hk
+from hipkittensp_b200 import _lib
+torch.cuda.set_device(0)
+def operands(M, N, K, seed):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    pa, sa = hk.quantize(torch.randn(M, K, device="cuda", generator=g))
+    pb, sb = hk.quantize(0.02 * torch.randn(N, K, device="cuda", generator=g))
+    return pa, sa, pb, sb
+small, big = (16, 4096, 4096), (64, 38400, 1024)      # both split tiles along K; the second needs more than the first 8 MiB
+assert 0 < hk.lib.mxfp6_gemm_workspace_bytes(*small) <= (8 << 20) < hk.lib.mxfp6_gemm_workspace_bytes(*big)
+pa, sa, pb, sb = operands(*small, 1)
+qa, ta, qb, tb = operands(*big, 2)
+C = torch.empty(small[:2], dtype=torch.bfloat16, device="cuda")
+D = torch.empty(big[:2], dtype=torch.bfloat16, device="cuda")
+hk.dispatch_micro(pa, pb, C, sa, sb)                   # eager: the library allocates its first scratch buffer
+torch.cuda.synchronize()
+want = C.clone()
+g = torch.cuda.CUDAGraph()
+with torch.cuda.graph(g):
+    hk.dispatch_micro(pa, pb, C, sa, sb)               # the graph now holds that buffer's address
+    # a shape that needs a larger buffer cannot get one during capture: refused with a message, the capture survives
+    try:
+        hk.dispatch_micro(qa, qb, D, ta, tb)
+        raise SystemExit("growth during capture was not refused")
+    except _lib.Mxfp6Error as e:
+        assert e.code == _lib.ERR_BAD_ARG and "being captured" in str(e), str(e)
+hk.dispatch_micro(qa, qb, D, ta, tb)                   # outside the capture the library adds a larger buffer ...
+torch.cuda.synchronize()
+C.fill_(float("nan"))
+g.replay(); g.replay()                                 # ... and the graph still replays into the old one, which was not freed
+torch.cuda.synchronize()
+assert hk.device_status() == 0
+assert torch.equal(C.view(torch.int16), want.view(torch.int16))
+E = torch.empty_like(D)
+hk.dispatch_micro(qa, qb, E, ta, tb)
+torch.cuda.synchronize()
+assert torch.equal(D.view(torch.int16), E.view(torch.int16))
+print("SCRATCH_GROWTH_OK")
+"""
+
+
+def test_scratch_is_never_freed_under_a_captured_graph():
+    """A CUDA graph captured earlier keeps the scratch address it was given; a later, larger shape gets an additional
+    buffer (the old one stays), and asking for one while a stream is being captured is refused with a message."""
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    out = subprocess.run([sys.executable, "-c", _SCRATCH_GROWTH, root], capture_output=True, text=True, timeout=600)
+    assert "SCRATCH_GROWTH_OK" in out.stdout, out.stdout[-2000:] + out.stderr[-2000:]
 
 
 # ------------------------------------------------------------------------------- empty dimensions
