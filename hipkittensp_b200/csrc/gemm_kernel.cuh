@@ -45,8 +45,6 @@ struct GemmParams {
     int stage_stride;          // bytes from one stage to the next (a multiple of 1024)
     int q_off;                 // offset of the Q box inside a stage (rows of P rounded up to 8, times 128)
     int load_batch;            // K-blocks the producer requests back to back
-    int pf_dist;               // skinny forms: the streamed operand's boxes are prefetched into L2 this many K-blocks ahead of their load (0 = off)
-    int pf_q;                  // ... and the streamed operand is Q (unswapped form) rather than P
     int k_rot;                 // whole tiles start their K loop at a tile-dependent K-block and wrap around (kblocks % 4 == 0)
     int ldc;                   // row stride of C in elements (= N)
     int c_rows, c_cols;        // M, N
@@ -439,17 +437,6 @@ mxfp6_gemm_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constan
                     }
                 }
                 if (!ok) break;
-                // Far ahead of the ring: the weight boxes of later K-blocks are asked into L2 now, so that the ring's own
-                // loads find them there and the bytes in flight from DRAM are not limited by shared memory.
-                if (P.pf_dist > 0 && elect_one_sync()) {
-                    const int first = kb == sg.k0 ? kb + nb : kb + P.pf_dist;       // the first batch of a tile prefetches the whole window
-                    const int last_pf = min(sg.k1, kb + nb + P.pf_dist);
-                    for (int k = max(first, kb + nb); k < last_pf; ++k) {
-                        if (P.pf_q) tma_prefetch_2d(&tm_q, k_at(P, sg, k) * Cfg::BK, sg.q0);
-                        else tma_prefetch_2d(&tm_p, k_at(P, sg, k) * Cfg::BK, sg.p0);
-                    }
-                }
-                __syncwarp();
                 // stages are released in order: when the last one of the batch is free, all of them are
                 uint32_t last = st_idx + nb - 1, last_phase = st_phase;
                 if (last >= (uint32_t)n_stages) { last -= n_stages; last_phase ^= 1; }

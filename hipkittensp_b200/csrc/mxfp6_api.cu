@@ -61,7 +61,6 @@ struct Options {
     int decode_stages = 0, decode_batch = 0;   // MXFP6_DECODE_RING = "stages,batch": ring of that kernel (0 = chosen by the library)
     int push_rotate = 1;     // MXFP6_PUSH_ROTATE: pair kernel, rotate the order of the peer destinations from piece to piece
     int c_plain = 0;         // MXFP6_C_PLAIN: the pair kernel writes C with plain stores from its staging buffer even where TMA stores are possible
-    int pf_dist = 0;         // MXFP6_PF_DIST: skinny forms prefetch the streamed operand into L2 this many K-blocks ahead
     int k_rot = 1;           // MXFP6_K_ROT: the even-rows skinny forms start each tile's K loop at its own K-block
 };
 static Options g_opt;
@@ -84,7 +83,6 @@ static bool set_option(const char* name, const char* v) {
     } else if (!strcmp(name, "MXFP6_TAIL_SPLIT")) g_opt.tail_split = v ? atoi(v) : d.tail_split;
     else if (!strcmp(name, "MXFP6_DECODE_ROWS")) g_opt.decode_rows = v ? atoi(v) : d.decode_rows;
     else if (!strcmp(name, "MXFP6_K_ROT")) g_opt.k_rot = v ? atoi(v) : d.k_rot;
-    else if (!strcmp(name, "MXFP6_PF_DIST")) { g_opt.pf_dist = v ? atoi(v) : d.pf_dist; if (g_opt.pf_dist < 0 || g_opt.pf_dist > 64) g_opt.pf_dist = d.pf_dist; }
     else if (!strcmp(name, "MXFP6_C_PLAIN")) g_opt.c_plain = v ? atoi(v) : d.c_plain;
     else if (!strcmp(name, "MXFP6_PUSH_ROTATE")) g_opt.push_rotate = v ? atoi(v) : d.push_rotate;
     else if (!strcmp(name, "MXFP6_DECODE_RING")) {
@@ -95,7 +93,7 @@ static bool set_option(const char* name, const char* v) {
     return true;
 }
 static const char* const kOptionNames[] = {"MXFP6_FORCE_CFG", "MXFP6_NO_SF_TMA", "MXFP6_PDL", "MXFP6_GROUP_P", "MXFP6_QUANT_PATH",
-                                           "MXFP6_WAIT_MS", "MXFP6_L2", "MXFP6_TAIL_SPLIT", "MXFP6_DECODE_ROWS", "MXFP6_DECODE_RING", "MXFP6_K_ROT", "MXFP6_PUSH_ROTATE", "MXFP6_C_PLAIN", "MXFP6_PF_DIST"};
+                                           "MXFP6_WAIT_MS", "MXFP6_L2", "MXFP6_TAIL_SPLIT", "MXFP6_DECODE_ROWS", "MXFP6_DECODE_RING", "MXFP6_K_ROT", "MXFP6_PUSH_ROTATE", "MXFP6_C_PLAIN"};
 static const Options& options() {
     std::call_once(g_opt_once, [] {
         for (const char* n : kOptionNames)
@@ -605,8 +603,6 @@ static int gemm_impl(const void* a, const void* sfa, const void* b, const void* 
         // the even-rows forms of skinny problems (tiles narrower than a box) rotate their K loops
         const bool even_rows = pl.ctas == 2 || pl.q_tile != pl.bn;
         P.k_rot = (even_rows && o.k_rot && (K / 128) % 4 == 0) ? 1 : 0;
-        P.pf_dist = even_rows ? o.pf_dist : 0;
-        P.pf_q = pl.swap ? 0 : 1;
     }
     P.ldc = (int)dst.ldc; P.c_rows = (int)M; P.c_cols = (int)N;
     P.idesc = make_idesc_m(fmt_mma_code(fp), fmt_mma_code(fq), pl.pair ? 256u : 128u, (uint32_t)pl.bn);

@@ -98,12 +98,6 @@ __device__ __forceinline__ void tma_load_2d_hint(uint32_t dst_smem, const CUtens
         : "memory");
 }
 
-// The same box brought into L2 only (no shared memory, no barrier): issued well ahead of the load that will want it.
-__device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap* m, int x, int y) {
-    asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];"
-                 ::"l"(reinterpret_cast<uint64_t>(m)), "r"(x), "r"(y) : "memory");
-}
-
 // 2-D tiled store shared -> global (bulk async-group completion); rows/columns outside the tensor are clipped
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap* m, uint32_t src_smem, int x, int y) {
     asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%2, %3}], [%1];"
