@@ -654,17 +654,28 @@ mxfp6_gemm_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constan
             float* slot = nullptr;
             if (partial) slot = P.ws_partial + ((size_t)sg.tile * P.ws_slots + sg.segidx) * (size_t)(BN * 128);
             const int p = sg.p0 + prow;
+            // with overlapping accumulators the 32 shared columns are drained first
+            auto chunk_of = [&](int ci) { return Cfg::OVERLAP ? (b == 0 ? (ci + NCH - 1) % NCH : ci) : ci; };
+            // The chunks are read from TMEM one ahead: while chunk ci is converted and stored, the load of chunk ci + 1
+            // is already under way (the drain of a tile is a chain of TMEM round trips otherwise: 4.3 us for a 128 x 200
+            // tile, a tenth of a skinny launch).  Chunks that lie wholly past the tile's own columns are not read.
+            uint32_t v[CW], vn[CW];
+            auto load_chunk = [&](int ch, uint32_t (&dst)[CW]) {
+                if (!Cfg::SWAP && ch * CW >= P.q_tile_rows) return;
+                if constexpr (CW == 32) tmem_ld_x32(tacc + ch * CW, reinterpret_cast<uint32_t(&)[32]>(dst));
+                else tmem_ld_x16(tacc + ch * CW, reinterpret_cast<uint32_t(&)[16]>(dst));
+            };
+            load_chunk(chunk_of(0), v);
+            tmem_ld_wait();
 #pragma unroll 1
             for (int ci = 0; ci < NCH; ++ci) {
-                // with overlapping accumulators the 32 shared columns are drained first
-                const int ch = Cfg::OVERLAP ? (b == 0 ? (ci + NCH - 1) % NCH : ci) : ci;
-                uint32_t v[CW];
-                if constexpr (CW == 32) tmem_ld_x32(tacc + ch * CW, reinterpret_cast<uint32_t(&)[32]>(v));
-                else tmem_ld_x16(tacc + ch * CW, reinterpret_cast<uint32_t(&)[16]>(v));
-                tmem_ld_wait();
+                const int ch = chunk_of(ci);
+                if (ci + 1 < NCH) load_chunk(chunk_of(ci + 1), vn);
                 if (Cfg::OVERLAP && ci == 0) { tc_fence_before(); __syncwarp(); if (lane == 0) mbar_arrive(bar_ovl); }
                 if (!Cfg::OVERLAP && ci == NCH - 1) { tc_fence_before(); mbar_arrive(bar_acc_empty(b)); }
                 const int qc = sg.q0 + ch * CW;              // first D column of this chunk
+                const bool dead = !Cfg::SWAP && ch * CW >= P.q_tile_rows;      // nothing of this chunk belongs to the tile
+                if (!dead) {
                 if (!partial && affine) {
                     if constexpr (Cfg::SWAP) {
                         affine_chunk<true, CW>(P, v, p, qc);
@@ -732,6 +743,12 @@ mxfp6_gemm_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constan
                             }
                         }
                     }
+                }
+                }
+                if (ci + 1 < NCH) {
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < CW; ++i) v[i] = vn[i];
                 }
             }
             if (partial) {
