@@ -75,6 +75,7 @@ struct GemmParams {
     int stage_tx_bytes_tail;   // pair kernel: bytes one CTA's loads of a slice's stage report
     int early_p;               // swapped form: P (the weights) may be read before the preceding kernel has finished
     int l2_load, l2_store;     // L2 eviction policy of the operand loads / of the stores of C (0 normal, 1 evict_first, 2 evict_last)
+    int l2_p, l2_q;            // single-CTA kernel: policy of the loads of P / of Q (an operand that is read once leaves L2 first, one that every CTA re-reads last)
     // optional fp32 epilogue, applied to the finished sum before it is rounded (null = absent):
     // C[m,n] = (acc * scale_n[n]) * scale_m[m] + bias_n[n]
     const float* scale_m;      // [M]
@@ -386,6 +387,7 @@ mxfp6_gemm_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constan
         uint32_t st_idx = 0, st_phase = 0;        // ring position of stage number n_stage and the parity of its round (no division: the ring size may be a run-time value)
         uint32_t pre_stage = 0, pre_raw = 0;      // stages / scale slabs whose P half is already on its way
         bool ok = true;
+        const uint64_t pol_p = l2_policy(P.l2_p), pol_q = l2_policy(P.l2_q);
         if (early) {
             SegIter<Cfg> it2(P);
             Segment s2;
@@ -396,7 +398,7 @@ mxfp6_gemm_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constan
                         if (slabs && pre_raw < (uint32_t)Cfg::RAW_SLOTS) {
                             if (elect_one_sync()) {
                                 mbar_arrive_expect_tx(bar_raw_full(pre_raw), (uint32_t)P.raw_tx_bytes);
-                                tma_load_2d(raw_base + pre_raw * Cfg::RAW_BYTES, &tm_sfp, bar_raw_full(pre_raw), (k_at(P, s2, k) >> 2) * 16, s2.p0);
+                                tma_load_2d_hint(raw_base + pre_raw * Cfg::RAW_BYTES, &tm_sfp, bar_raw_full(pre_raw), (k_at(P, s2, k) >> 2) * 16, s2.p0, pol_p);
                             }
                             ++pre_raw;
                         } else {
@@ -405,7 +407,7 @@ mxfp6_gemm_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constan
                     }
                     if (elect_one_sync()) {
                         mbar_arrive_expect_tx(bar_full(pre_stage), (uint32_t)P.stage_tx_bytes);
-                        tma_load_2d(stage_base + pre_stage * stage_stride, &tm_p, bar_full(pre_stage), k_at(P, s2, k) * Cfg::BK, s2.p0);
+                        tma_load_2d_hint(stage_base + pre_stage * stage_stride, &tm_p, bar_full(pre_stage), k_at(P, s2, k) * Cfg::BK, s2.p0, pol_p);
                     }
                     __syncwarp();
                     ++pre_stage;
@@ -429,9 +431,9 @@ mxfp6_gemm_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constan
                             const uint32_t dst = raw_base + r * Cfg::RAW_BYTES;
                             if (n_raw >= pre_raw) {
                                 mbar_arrive_expect_tx(bar_raw_full(r), (uint32_t)P.raw_tx_bytes);
-                                tma_load_2d(dst, &tm_sfp, bar_raw_full(r), (k_at(P, sg, k) >> 2) * 16, sg.p0);
+                                tma_load_2d_hint(dst, &tm_sfp, bar_raw_full(r), (k_at(P, sg, k) >> 2) * 16, sg.p0, pol_p);
                             }
-                            tma_load_2d(dst + Cfg::BM * 16, &tm_sfq, bar_raw_full(r), (k_at(P, sg, k) >> 2) * 16, sg.q0);
+                            tma_load_2d_hint(dst + Cfg::BM * 16, &tm_sfq, bar_raw_full(r), (k_at(P, sg, k) >> 2) * 16, sg.q0, pol_q);
                         }
                         ++n_raw;
                     }
@@ -449,9 +451,9 @@ mxfp6_gemm_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constan
                         const uint32_t dst = stage_base + s * stage_stride;
                         if (n_stage + j >= pre_stage) {
                             mbar_arrive_expect_tx(bar_full(s), (uint32_t)P.stage_tx_bytes);
-                            tma_load_2d(dst, &tm_p, bar_full(s), k_at(P, sg, kb + j) * Cfg::BK, sg.p0);
+                            tma_load_2d_hint(dst, &tm_p, bar_full(s), k_at(P, sg, kb + j) * Cfg::BK, sg.p0, pol_p);
                         }
-                        tma_load_2d(dst + q_off, &tm_q, bar_full(s), k_at(P, sg, kb + j) * Cfg::BK, sg.q0);
+                        tma_load_2d_hint(dst + q_off, &tm_q, bar_full(s), k_at(P, sg, kb + j) * Cfg::BK, sg.q0, pol_q);
                     }
                 }
                 __syncwarp();

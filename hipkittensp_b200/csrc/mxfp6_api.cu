@@ -632,6 +632,10 @@ static int gemm_impl(const void* a, const void* sfa, const void* b, const void* 
     P.early_p = (pl.swap && (flags & MXFP6_FLAG_B_STATIC) && o.pdl) ? 1 : 0;
     P.group_p = o.group_p;   // 16 pair-tiles (4096 rows of A) share each tile of B
     P.l2_load = o.l2_load; P.l2_store = o.l2_store;
+    // single-CTA kernel: an operand whose tiles are loaded once (the weights of a skinny problem) is marked to leave L2
+    // first, one that other CTAs ask for again (always the activations of a skinny problem) to leave last
+    P.l2_p = !o.l2_load ? 0 : pl.tiles_q == 1 ? 1 : 2;
+    P.l2_q = !o.l2_load ? 0 : pl.tiles_p == 1 ? 1 : 2;
     P.scale_m = aff.scale_m; P.scale_n = aff.scale_n; P.bias_n = aff.bias_n;
 
     r.grid = pl.grid;
