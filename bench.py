@@ -54,6 +54,8 @@ def parse():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
+    ap.add_argument("--gather", default="auto", choices=["auto", "fused", "copy"],
+                    help="N > 1: the exchange that overlaps the GEMM (auto: both are probed, the faster one is timed)")
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU baseline leg (N=1)")
     ap.add_argument("--no-extras", action="store_true", help="skip extra_configs, sustained and check (profiling aid)")
     ap.add_argument("--small", action="store_true", help="1024^3 instead of 8192^3 (profiling aid, not a bench value)")
@@ -492,24 +494,50 @@ def run_sharded(args, torch, hk, device, peaks, world, rank):
     sampler.start()       # long before the timed region: the thread and NVML are in their stride when it starts
     a, sa = make_operands(torch, hk, M, K, "normal", 10, device)             # replicated: same seed on all ranks
     b, sb = make_operands(torch, hk, per, K, "normal", 100 + rank, device)   # this rank's rows of B
-    try:
-        op = ColumnParallelGemm(M, N, K, device=device)            # fused: tiles pushed to peers by the epilogue
-    except Exception as e:                                          # symmetric memory unavailable on this box
-        print(f"[bench] fused gather unavailable ({e!r}); using the NCCL all-gather", file=sys.stderr)
-        op = ColumnParallelGemm(M, N, K, device=device, gather="nccl")
-
-    def step(i):
-        return op(a, sa, b, sb)
-
     def barrier():
         dist.barrier()
         torch.cuda.synchronize()
+
+    # Two exchanges that overlap the GEMM: tiles pushed to the peers by the epilogue ("fused"), and blocks carried by the
+    # copy engines behind per-block flags the kernel raises ("copy").  Which is faster depends on the number of GPUs (the
+    # first is bound by what SM-issued stores get out of the fabric, the second waits for whole blocks), so both are
+    # warmed up and probed with a few steps, the maximum over ranks decides, and the chosen one is timed.
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ops, probe_ms = {}, {}
+    modes = ["fused", "copy"] if args.gather == "auto" else [args.gather]
+    for mode in modes:
+        try:
+            cand = ColumnParallelGemm(M, N, K, device=device, gather=mode)
+        except Exception as e:                                      # symmetric memory unavailable on this box
+            print(f"[bench] gather={mode} unavailable ({e!r})", file=sys.stderr)
+            continue
+        if cand.mode != mode:                                       # the operator fell back (shard too small for block flags)
+            continue
+        for i in range(W):
+            cand(a, sa, b, sb)
+        barrier()
+        e0.record()
+        for i in range(3):
+            cand(a, sa, b, sb)
+        e1.record()
+        barrier()
+        t = torch.tensor([e0.elapsed_time(e1) / 3], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ops[mode], probe_ms[mode] = cand, float(t)
+    if not ops:
+        print("[bench] no overlapped gather available; using the NCCL all-gather", file=sys.stderr)
+        ops["nccl"] = ColumnParallelGemm(M, N, K, device=device, gather="nccl")
+        probe_ms["nccl"] = 0.0
+    chosen = min(ops, key=lambda m: probe_ms[m])
+    op = ops[chosen]
+
+    def step(i):
+        return op(a, sa, b, sb)
 
     flops_step = 2.0 * M * N * K
     for i in range(W):
         step(i)
     assert hk.device_status() == 0
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     t0 = time.perf_counter()
     e0.record()
@@ -576,7 +604,14 @@ def run_sharded(args, torch, hk, device, peaks, world, rank):
     ranks_equal = all(int(x) == int(all_d[0]) for x in all_d)
     # (iv) the NCCL all-gather + re-layout exchange gives the same matrix
     nccl_equal = None
-    if op.mode == "fused":
+    others_equal = True
+    for mode, other in ops.items():          # the exchange that was not timed gives the same matrix
+        if other is not op:
+            c_o = other(a, sa, b, sb)
+            torch.cuda.synchronize()
+            others_equal = others_equal and int(digest(c_o)) == int(d_fused)
+            del c_o
+    if op.mode in ("fused", "copy"):
         op2 = ColumnParallelGemm(M, N, K, device=device, gather="nccl")
         c2 = op2(a, sa, b, sb)
         torch.cuda.synchronize()
@@ -590,7 +625,7 @@ def run_sharded(args, torch, hk, device, peaks, world, rank):
         nccl_ms = e0.elapsed_time(e1) / 3
         del op2, c2
         torch.cuda.empty_cache()
-    flags = torch.tensor([int(rows_equal), int(ranks_equal), int(nccl_equal is not False),
+    flags = torch.tensor([int(rows_equal), int(ranks_equal), int(nccl_equal is not False and others_equal),
                           int(rank != 0 or (oracle["row_rel"] <= 1e-2 and oracle["max_ulp"] <= 2.0))], device=device)
     dist.all_reduce(flags, op=dist.ReduceOp.MIN)
     flags = [bool(x) for x in flags.cpu()]
@@ -599,7 +634,7 @@ def run_sharded(args, torch, hk, device, peaks, world, rank):
              "rows": n_rows, "oracle_rows": n_oracle, "row_rel": float(f"{oracle['row_rel']:.3e}"), "max_ulp": round(oracle["max_ulp"], 3),
              "n_floor": oracle["n_floor"],
              "how": "every rank: 64 full rows of the gathered C bit for bit against the single-GPU kernel on regenerated shards; "
-                    "64-bit checksum of the whole C all-gathered and compared; fused and NCCL exchanges compared; rank 0: 16 rows "
+                    "64-bit checksum of the whole C all-gathered and compared; the epilogue-push, copy-engine and NCCL exchanges compared; rank 0: 16 rows "
                     "against the fp64 CPU oracle (row_rel <= 1e-2, <= 2 bf16 ulp)"}
 
     # ---- the whole problem on one GPU (rank 0's clock; the other ranks wait): the strong-scaling baseline
@@ -665,8 +700,11 @@ def run_sharded(args, torch, hk, device, peaks, world, rank):
             "config": {"workload": f"mxfp6_e2m3_gemm_{M}x{N}x{K}_colparallel_gather", "M": M, "N": N, "K": K, "format": "e2m3",
                        "scale": "e8m0 per 32 along K"},
             "notes": {"l2": "A + B shard + C exceed L2",
-                      "parallelism": (f"column-parallel x{world}, C tiles pushed to peers by the GEMM epilogue (symmetric memory, "
-                                      f"two alternating C buffers)" if op.mode == "fused" else f"column-parallel x{world}, nccl all-gather of C"),
+                      "parallelism": f"column-parallel x{world}, " + {
+                          "fused": "C tiles pushed to peers by the GEMM epilogue (symmetric memory, two alternating C buffers)",
+                          "copy": "finished blocks of C carried to the peers by the copy engines behind per-block flags the GEMM "
+                                  "raises (symmetric memory, two alternating C buffers)",
+                          "nccl": "nccl all-gather of C"}[op.mode],
                       "workload_vs_n1": "the N=1 line of this benchmark times 8192^3; single_gpu_same_workload_ms below is this "
                                         "configuration's own one-GPU time"},
             "e2e": {"value": round(e2e_val, 2), "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
@@ -684,7 +722,9 @@ def run_sharded(args, torch, hk, device, peaks, world, rank):
             "gemm_only_efficiency": round(single_ms / (world * kernel_ms), 4),
             "nvlink_ingress_gbs": round(ingress, 1),
             "nvlink_ingress_frac_of_770": round(ingress / 770.0, 4),
-            "nccl_gather_ms_per_step": round(nccl_ms, 4) if op.mode == "fused" else None,
+            "gather": {"timed": op.mode, "probe_ms_per_step": {m: round(v, 4) for m, v in probe_ms.items()},
+                       "how": "each overlapped exchange warmed up and probed with 3 steps (max over ranks); the faster one is timed"},
+            "nccl_gather_ms_per_step": round(nccl_ms, 4) if op.mode in ("fused", "copy") else None,
         }
         print(json.dumps(line), flush=True)
     dist.barrier()

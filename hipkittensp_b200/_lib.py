@@ -19,7 +19,7 @@ OK, ERR_BAD_ARG, ERR_CUDA, ERR_DEVICE_WAIT, ERR_UNSUPPORTED = 0, 1, 2, 3, 4
 
 # every symbol include/mxfp6.h declares
 SYMBOLS = ("mxfp6_version", "mxfp6_last_error", "mxfp6_gemm", "mxfp6_gemm_workspace_bytes", "mxfp6_gemm_ws",
-           "mxfp6_gemm_noalloc", "mxfp6_gemm_multi", "mxfp6_gemm_ex", "mxfp6_gemm_requant", "mxfp6_gemm_scaled",
+           "mxfp6_gemm_noalloc", "mxfp6_gemm_multi", "mxfp6_gemm_copy_gather", "mxfp6_copy_gather_scratch_bytes", "mxfp6_gemm_ex", "mxfp6_gemm_requant", "mxfp6_gemm_scaled",
            "mxfp6_quantize", "mxfp6_dequantize", "mxfp6_device_status", "mxfp6_debug_tma_dump", "mxfp6_debug_wait_timeout", "mxfp6_debug_option", "mxfp6_debug_plan")
 
 
@@ -55,6 +55,11 @@ def _load() -> ctypes.CDLL:
     lib.mxfp6_gemm_scaled.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, i64, i64, i64, ci, ci, vp]
     lib.mxfp6_gemm_multi.restype = ci
     lib.mxfp6_gemm_multi.argtypes = [vp, vp, vp, vp, ctypes.POINTER(vp), ci, i64, i64, i64, i64, ci, ci, vp]
+    lib.mxfp6_gemm_copy_gather.restype = ci
+    lib.mxfp6_gemm_copy_gather.argtypes = [vp, vp, vp, vp, ctypes.POINTER(vp), ci, i64, i64, i64, i64, ci, ci, vp, sz, ci,
+                                           ctypes.POINTER(vp), ci, vp]
+    lib.mxfp6_copy_gather_scratch_bytes.restype = sz
+    lib.mxfp6_copy_gather_scratch_bytes.argtypes = [i64, i64, ci]
     lib.mxfp6_gemm_workspace_bytes.restype = sz
     lib.mxfp6_gemm_workspace_bytes.argtypes = [i64, i64, i64]
     lib.mxfp6_gemm_ws.restype = ci

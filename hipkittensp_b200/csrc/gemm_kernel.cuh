@@ -59,6 +59,12 @@ struct GemmParams {
     int ndst;                  // number of destinations, 1..8
     int push_rotate;           // pair kernel: the order in which a piece goes to the peer destinations rotates from piece to piece
     int c_vec16;               // pair kernel, plain stores: destinations and row stride are 16-byte multiples and N % 8 == 0
+    // pair kernel, optional: C is cut into blocks (group_p * 256 rows x sig_cols * 256 columns); every CTA adds the 64-column
+    // pieces it has written to its block's counter, and the CTA that completes a block raises the block's flag, which
+    // copy streams of the host wait for (stream memory operations)
+    unsigned int* sig_counter;
+    unsigned int* sig_flag;
+    int sig_cols;
     int c_tma;                 // pair kernel: C is stored by TMA (16-byte aligned destinations and row stride); else by plain stores
     uint8_t* q_out;            // re-quantised output instead of bf16 C: operand bytes [M, 3N/4 or N] ...
     uint8_t* q_scales;         // ... and E8M0 scales [M, N/32], blocks of 32 along N

@@ -541,6 +541,25 @@ mxfp6_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_co
                 }
                 ++n_out;
             }
+            if (P.sig_flag && etid == 0) {
+                // The unit's pieces are with the TMA unit; once they are written, they count towards the block of C the
+                // unit lies in.  Release before the count, acquire after it: the CTA that completes the count has seen
+                // every other CTA's pieces land, and only then raises the flag.
+                bulk_wait_group<0>();
+                const int grp = (p0 >> 8) / P.group_p;
+                const int gsz = min(P.tiles_p - grp * P.group_p, P.group_p);
+                const int strips = (P.tiles_q + P.sig_cols - 1) / P.sig_cols;
+                const int strip = (q0 >> 8) / P.sig_cols;
+                const int ncol = min(P.sig_cols, P.tiles_q - strip * P.sig_cols);
+                const unsigned int total = (unsigned int)(gsz * ncol * 8);      // 2 CTAs x 4 pieces per tile
+                const int blk = grp * strips + strip;
+                __threadfence_system();
+                const unsigned int old = atomicAdd(P.sig_counter + blk, (unsigned int)NP);
+                if (old + (unsigned int)NP == total) {
+                    __threadfence_system();
+                    *reinterpret_cast<volatile unsigned int*>(P.sig_flag + blk) = 1u;
+                }
+            }
             ++n_seg;
         }
         if (etid == 0) bulk_wait_group<0>();      // all stores (local and peer) are done before the CTA leaves

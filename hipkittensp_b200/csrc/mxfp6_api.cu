@@ -366,6 +366,13 @@ struct Dest {
     int64_t ldc;
 };
 
+// optional completion flags per block of C (pair kernel; null = absent)
+struct Signal {
+    unsigned int* counter = nullptr;   // [blocks], cleared before every launch
+    unsigned int* flag = nullptr;      // [blocks], raised to 1 by the CTA that completes a block
+    int cols = 0;                      // 256-column tiles per block; a block is as many rows as one row group of the tile order
+};
+
 // optional fp32 epilogue vectors (null = absent)
 struct Affine {
     const float* scale_m = nullptr;   // [M]
@@ -406,6 +413,8 @@ struct CallKey {
     const float *scale_m, *scale_n, *bias_n;
     int n_dst, fmt_a, fmt_b, ws_mode, q_fmt, dev;
     unsigned flags, epoch;
+    unsigned int *sig_counter, *sig_flag;
+    int64_t sig_cols;
 };
 
 struct Recipe {
@@ -493,7 +502,7 @@ static int own_scratch(DeviceState& d, size_t bytes, cudaStream_t st, void** out
 static int gemm_impl(const void* a, const void* sfa, const void* b, const void* sfb, const Dest& dst, int64_t M, int64_t N,
                      int64_t K, int fmt_a, int fmt_b, void* ws, size_t ws_bytes, int ws_mode, void* stream,
                      unsigned flags = 0, void* q_out = nullptr, void* q_scales = nullptr, int q_fmt = -1,
-                     const Affine& aff = Affine{}) {
+                     const Affine& aff = Affine{}, const Signal& sig = Signal{}) {
     cudaStream_t st = (cudaStream_t)stream;
     // ---- the recipe of an identical earlier call
     int dev = -1;
@@ -508,6 +517,7 @@ static int gemm_impl(const void* a, const void* sfa, const void* b, const void* 
     key.scale_m = aff.scale_m; key.scale_n = aff.scale_n; key.bias_n = aff.bias_n;
     key.n_dst = dst.n; key.fmt_a = fmt_a; key.fmt_b = fmt_b; key.ws_mode = ws_mode; key.q_fmt = q_fmt; key.dev = dev;
     key.flags = flags; key.epoch = g_opt_epoch.load(std::memory_order_acquire);
+    key.sig_counter = sig.counter; key.sig_flag = sig.flag; key.sig_cols = sig.cols;
     if (!t_cache) t_cache.reset(new RecipeCache());      // a few tens of KB per calling thread
     for (int i = 0; i < kRecipeSlots && dev >= 0; ++i) {
         const Recipe& r = t_cache->slot[i];
@@ -549,6 +559,13 @@ static int gemm_impl(const void* a, const void* sfa, const void* b, const void* 
 
     Recipe r;
     r.key = key;
+    if (sig.flag) {
+        if (!pl.pair || pl.ws_bytes || q_fmt >= 0 || dst.n != 1 || !dest_by_tma(dst) || options().c_plain || sig.cols < 1 || !sig.counter)
+            return fail(MXFP6_ERR_BAD_ARG, "completion flags need the CTA-pair kernel with TMA stores of C (M > 128, N >= 256, "
+                                           "16-byte aligned C and row stride) and one destination");
+        r.counter_ptr = sig.counter;
+        r.counter_bytes = (size_t)ceil_div(pl.tiles_p, options().group_p) * ceil_div(pl.tiles_q, sig.cols) * sizeof(unsigned int);
+    }
     if (pl.ws_bytes) {
         if (ws_mode == kWsOwn) {
             if ((rc = own_scratch(d, pl.ws_bytes, st, &ws))) return rc;
@@ -632,6 +649,7 @@ static int gemm_impl(const void* a, const void* sfa, const void* b, const void* 
     P.early_p = (pl.swap && (flags & MXFP6_FLAG_B_STATIC) && o.pdl) ? 1 : 0;
     P.group_p = o.group_p;   // 16 pair-tiles (4096 rows of A) share each tile of B
     P.l2_load = o.l2_load; P.l2_store = o.l2_store;
+    P.sig_counter = sig.counter; P.sig_flag = sig.flag; P.sig_cols = sig.cols;
     // single-CTA kernel: an operand whose tiles are loaded once (the weights of a skinny problem) is marked to leave L2
     // first, one that other CTAs ask for again (always the activations of a skinny problem) to leave last
     P.l2_p = !o.l2_load ? 0 : pl.tiles_q == 1 ? 1 : 2;
@@ -890,6 +908,127 @@ extern "C" int mxfp6_gemm_multi(const void* a, const void* sfa, const void* b, c
     d.n = n_dst;
     d.ldc = ldc;
     return gemm_impl(a, sfa, b, sfb, d, M, N, K, fmt_a, fmt_b, nullptr, 0, kWsOwn, stream);
+}
+
+// ---------------------------------------------------------------------------------- GEMM with a copy-engine gather
+// The column-parallel step with the exchange carried by the copy engines instead of stores from the SMs.  The kernel
+// writes its block into the local C and raises one flag per finished block of C; for every peer, side streams wait for
+// each flag with a stream memory operation (no kernel spins) and copy the block to the peer with a 2-D copy.  Whatever
+// happens to the kernel, the launching stream sets every flag after it, so every wait ends.
+typedef CUresult (*StreamWaitValue32Fn)(CUstream, CUdeviceptr, cuuint32_t, unsigned int);
+static std::atomic<StreamWaitValue32Fn> g_wait_value{nullptr};
+static int get_wait_value_fn(StreamWaitValue32Fn* out) {
+    StreamWaitValue32Fn f = g_wait_value.load(std::memory_order_acquire);
+    if (!f) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        CUDA_TRY(cudaGetDriverEntryPoint("cuStreamWaitValue32", &fn, cudaEnableDefault, &qres));
+        if (!fn || qres != cudaDriverEntryPointSuccess) return fail(MXFP6_ERR_CUDA, "cuStreamWaitValue32 not available from the driver");
+        f = (StreamWaitValue32Fn)fn;
+        g_wait_value.store(f, std::memory_order_release);
+    }
+    *out = f;
+    return MXFP6_OK;
+}
+
+struct GatherBlocks {
+    int rows_per_block, cols_per_block, n_row_blocks, n_col_blocks;
+    int total() const { return n_row_blocks * n_col_blocks; }
+};
+static GatherBlocks gather_blocks(int64_t M, int64_t N, int strip_tiles) {
+    GatherBlocks g;
+    const int gp = options().group_p;
+    g.rows_per_block = gp * 256;
+    g.cols_per_block = strip_tiles * 256;
+    g.n_row_blocks = ceil_div(ceil_div(M, 256), gp);
+    g.n_col_blocks = ceil_div(ceil_div(N, 256), strip_tiles);
+    return g;
+}
+
+// events of the calling thread, one set per device (created once, never destroyed)
+static thread_local std::map<int, std::vector<cudaEvent_t>> t_events;
+static int thread_events(int dev, int n, cudaEvent_t** out) {
+    std::vector<cudaEvent_t>& v = t_events[dev];
+    while ((int)v.size() < n) {
+        cudaEvent_t e;
+        CUDA_TRY(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+        v.push_back(e);
+    }
+    *out = v.data();
+    return MXFP6_OK;
+}
+
+extern "C" size_t mxfp6_copy_gather_scratch_bytes(int64_t M, int64_t N, int strip_tiles) {
+    if (M <= 0 || N <= 0 || strip_tiles < 1) return 0;
+    return (size_t)gather_blocks(M, N, strip_tiles).total() * 2 * sizeof(unsigned int);
+}
+
+extern "C" int mxfp6_gemm_copy_gather(const void* a, const void* sfa, const void* b, const void* sfb, void* const* c_dst,
+                                      int n_dst, int64_t ldc, int64_t M, int64_t N, int64_t K, int fmt_a, int fmt_b,
+                                      void* scratch, size_t scratch_bytes, int strip_tiles, void* const* copy_streams,
+                                      int n_copy_streams, void* stream) {
+    if (!c_dst) return fail(MXFP6_ERR_BAD_ARG, "null destination list");
+    if (n_dst < 1 || n_dst > 8) return fail(MXFP6_ERR_BAD_ARG, "1 to 8 destinations, got %d", n_dst);
+    if (M <= 0 || N <= 0 || K <= 0) return fail(MXFP6_ERR_BAD_ARG, "empty problem (M=%lld N=%lld K=%lld)", (long long)M, (long long)N, (long long)K);
+    if (strip_tiles < 1) return fail(MXFP6_ERR_BAD_ARG, "strip_tiles must be at least 1");
+    const int peers = n_dst - 1;
+    if (peers > 0 && (!copy_streams || n_copy_streams < peers || n_copy_streams % peers))
+        return fail(MXFP6_ERR_BAD_ARG, "need a multiple of %d copy streams (one or more per peer), got %d", peers, n_copy_streams);
+    for (int i = 0; i < n_dst; ++i)
+        if (!c_dst[i]) return fail(MXFP6_ERR_BAD_ARG, "null C (destination %d)", i);
+    const GatherBlocks g = gather_blocks(M, N, strip_tiles);
+    const int nb = g.total();
+    if (!scratch || scratch_bytes < (size_t)nb * 2 * sizeof(unsigned int) || ((uintptr_t)scratch & 3))
+        return fail(MXFP6_ERR_BAD_ARG, "scratch too small: need %zu bytes (mxfp6_copy_gather_scratch_bytes), got %zu",
+                    (size_t)nb * 2 * sizeof(unsigned int), scratch_bytes);
+    cudaStream_t st = (cudaStream_t)stream;
+    unsigned int* flags = (unsigned int*)scratch;
+    unsigned int* counters = flags + nb;
+    StreamWaitValue32Fn wait_value = nullptr;
+    int rc = get_wait_value_fn(&wait_value);
+    if (rc) return rc;
+    int dev = 0;
+    CUDA_TRY(cudaGetDevice(&dev));
+    cudaEvent_t* ev = nullptr;
+    const int spp = peers ? n_copy_streams / peers : 0;      // streams per peer
+    if ((rc = thread_events(dev, 1 + n_copy_streams, &ev))) return rc;
+
+    CUDA_TRY(cudaMemsetAsync(flags, 0, (size_t)nb * sizeof(unsigned int), st));
+    CUDA_TRY(cudaEventRecord(ev[0], st));
+    Signal sig;
+    sig.counter = counters; sig.flag = flags; sig.cols = strip_tiles;
+    Dest d{};
+    d.c[0] = c_dst[0]; d.n = 1; d.ldc = ldc;
+    rc = gemm_impl(a, sfa, b, sfb, d, M, N, K, fmt_a, fmt_b, nullptr, 0, kWsOwn, stream, 0, nullptr, nullptr, -1, Affine{}, sig);
+    if (rc) return rc;                                        // nothing waits yet
+    // every flag is set behind the kernel: a kernel that gave up (bounded waits) leaves no stream waiting
+    CUDA_TRY(cudaMemsetAsync(flags, 0x01, (size_t)nb * sizeof(unsigned int), st));
+    if (!peers) return MXFP6_OK;
+    for (int i = 0; i < n_copy_streams; ++i) CUDA_TRY(cudaStreamWaitEvent((cudaStream_t)copy_streams[i], ev[0], 0));
+    // blocks in the order the kernel finishes them: row groups one after the other, column strips within a group
+    for (int rb = 0; rb < g.n_row_blocks; ++rb) {
+        for (int cb = 0; cb < g.n_col_blocks; ++cb) {
+            const int blk = rb * g.n_col_blocks + cb;
+            const int64_t row0 = (int64_t)rb * g.rows_per_block, col0 = (int64_t)cb * g.cols_per_block;
+            const size_t rows = (size_t)(M - row0 < g.rows_per_block ? M - row0 : g.rows_per_block);
+            const size_t width = (size_t)(N - col0 < g.cols_per_block ? N - col0 : g.cols_per_block) * 2;
+            const size_t off = ((size_t)row0 * (size_t)ldc + (size_t)col0) * 2;
+            for (int p = 0; p < peers; ++p) {
+                // peers take turns being first, so that the first copies of a block do not all leave for the same GPU
+                const int peer = (p + blk) % peers;
+                cudaStream_t cs = (cudaStream_t)copy_streams[peer * spp + blk % spp];
+                const CUresult cr = wait_value((CUstream)cs, (CUdeviceptr)(uintptr_t)(flags + blk), 1u, CU_STREAM_WAIT_VALUE_GEQ);
+                if (cr != CUDA_SUCCESS) return fail(MXFP6_ERR_CUDA, "cuStreamWaitValue32 failed with %d", (int)cr);
+                CUDA_TRY(cudaMemcpy2DAsync((uint8_t*)c_dst[1 + peer] + off, (size_t)ldc * 2, (const uint8_t*)c_dst[0] + off,
+                                           (size_t)ldc * 2, width, rows, cudaMemcpyDeviceToDevice, cs));
+            }
+        }
+    }
+    for (int i = 0; i < n_copy_streams; ++i) {
+        CUDA_TRY(cudaEventRecord(ev[1 + i], (cudaStream_t)copy_streams[i]));
+        CUDA_TRY(cudaStreamWaitEvent(st, ev[1 + i], 0));
+    }
+    return MXFP6_OK;
 }
 
 // ---------------------------------------------------------------------------------- GEMM without allocation

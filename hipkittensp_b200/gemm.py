@@ -124,6 +124,42 @@ def dispatch_multi(A, B, dests, col_offset: int, scale_A, scale_B, fmt: int = E2
                                    ldc, M, N, K, fmt, fmt, _stream_ptr()))
 
 
+def copy_gather_scratch_bytes(M: int, N: int, strip_tiles: int) -> int:
+    """Bytes of device scratch `dispatch_copy_gather` needs for an [M, N] block."""
+    return int(lib.mxfp6_copy_gather_scratch_bytes(M, N, strip_tiles))
+
+
+def dispatch_copy_gather(A, B, dests, col_offset: int, scale_A, scale_B, scratch, copy_streams, strip_tiles: int = 8,
+                         fmt: int = E2M3) -> None:
+    """`dispatch_multi` with the peers served by the copy engines: the kernel writes dests[0] only and raises a flag per
+    finished block of C; `copy_streams` (torch streams, a multiple of len(dests) - 1) wait for the flags and copy the
+    blocks to the peers.  Work queued on the current stream after the call sees all copies done."""
+    import ctypes
+
+    _accept(A, "A", torch.uint8)
+    _accept(B, "B", torch.uint8)
+    _accept(scale_A, "scale_A", torch.uint8)
+    _accept(scale_B, "scale_B", torch.uint8)
+    M, N = A.shape[0], B.shape[0]
+    K = _k_of(A, fmt, "A")
+    if not 1 <= len(dests) <= 8:
+        raise RuntimeError("1 to 8 destinations")
+    ldc = dests[0].stride(0)
+    for d in dests:
+        if d.dtype != torch.bfloat16 or d.dim() != 2 or d.stride(1) != 1 or d.stride(0) != ldc or d.shape[0] != M:
+            raise RuntimeError("destinations must be bf16 [M, ldc] matrices with one common row stride")
+        if col_offset < 0 or col_offset + N > d.shape[1]:
+            raise RuntimeError("column window outside the destination")
+    if scratch.device != A.device or not scratch.is_contiguous():
+        raise RuntimeError("scratch must be a contiguous tensor on the operands' device")
+    ptrs = (ctypes.c_void_p * len(dests))(*[d.data_ptr() + 2 * col_offset for d in dests])
+    streams = (ctypes.c_void_p * max(len(copy_streams), 1))(*[s.cuda_stream for s in copy_streams])
+    with _on_device_of(A):
+        check(lib.mxfp6_gemm_copy_gather(A.data_ptr(), scale_A.data_ptr(), B.data_ptr(), scale_B.data_ptr(), ptrs, len(dests),
+                                         ldc, M, N, K, fmt, fmt, scratch.data_ptr(), scratch.numel() * scratch.element_size(),
+                                         strip_tiles, streams, len(copy_streams), _stream_ptr()))
+
+
 def gemm_requant(A, scale_A, B, scale_B, fmt: int = E2M3, fmt_b: int | None = None, out_fmt: int = E2M3):
     """C = A @ B^T delivered as an MX operand for the next layer: (operand bytes [M, 3N/4 | N], scales [M, N/32]),
     quantised in the GEMM epilogue from the fp32 accumulators (blocks of 32 along N)."""

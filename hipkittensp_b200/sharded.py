@@ -18,6 +18,11 @@ Two exchanges:
   on each rank's stream lies behind its own readers of this C.  With `depth=1` there is one C, and every call
   opens with a second cross-GPU barrier on the stream (all ranks' queued readers of the previous C are done)
   before any tile is pushed.  Either way the reader's work must be queued on the same stream before the next call.
+* `gather="copy"`: the same symmetric C buffers, but the kernel writes only the local C and raises a flag per finished
+  block of it; side streams wait for the flags (stream memory operations) and the GPU's copy engines carry the blocks
+  to the peers (`mxfp6_gemm_copy_gather`).  Copy engines move this all-to-all faster than stores issued by the SMs, and
+  the GEMM is not slowed by pushing; the price is that nothing leaves before a whole block is finished.  The same
+  ordering rules as "fused".
 * `gather="nccl"`: one NCCL (or gloo, on CPU) all-gather of the contiguous [M, N/g] shards into a [g, M, N/g]
   buffer followed by a strided copy into row-major C.  The baseline, and the path the CPU tests use.
 """
@@ -56,7 +61,7 @@ class ColumnParallelGemm:
     """Holds the communicator and the reusable buffers of one sharded GEMM shape."""
 
     def __init__(self, M: int, N: int, K: int, group=None, device=None, fmt: int = E2M3, gather: str | None = None,
-                 depth: int = 2):
+                 depth: int = 2, strip_tiles: int = 8, streams_per_peer: int = 2):
         if depth not in (1, 2):
             raise ValueError("depth must be 1 or 2")
         self.depth, self.calls = depth, 0
@@ -69,11 +74,26 @@ class ColumnParallelGemm:
         on_gpu = device is not None and torch.device(device).type == "cuda"
         if gather is None:
             gather = "fused" if (on_gpu and self.world > 1) else "nccl"
-        if gather not in ("fused", "nccl"):
+        if gather not in ("fused", "copy", "nccl"):
             raise ValueError(gather)
+        if gather == "copy" and self.world > 1:
+            from ._lib import debug_plan
+
+            # per-block flags exist in the CTA-pair kernel only: smaller shards keep the pushes from the epilogue
+            sms = torch.cuda.get_device_properties(device).multi_processor_count
+            if not debug_plan(M, self.hi - self.lo, K, sm_count=sms)["pair"] or (self.hi - self.lo) % 8 or N % 8:
+                gather = "fused"
         self.mode = gather
         self.symm = None
-        if self.mode == "fused" and self.world > 1:
+        self.copy_streams, self.copy_scratch, self.strip_tiles = [], None, strip_tiles
+        if self.mode == "copy" and self.world > 1:
+            from .gemm import copy_gather_scratch_bytes
+
+            with torch.cuda.device(device):
+                self.copy_streams = [torch.cuda.Stream(device=device) for _ in range(streams_per_peer * (self.world - 1))]
+            nbytes = copy_gather_scratch_bytes(M, self.hi - self.lo, strip_tiles)
+            self.copy_scratch = torch.zeros(max(nbytes // 4, 1), dtype=torch.int32, device=device)
+        if self.mode in ("fused", "copy") and self.world > 1:
             import torch.distributed._symmetric_memory as symm
 
             # destination 0 is local, the rest are the peers' copies of C, rotated so that ranks do not all
@@ -95,7 +115,7 @@ class ColumnParallelGemm:
 
     def local_gemm(self, A, scale_A, B_shard, scale_B_shard) -> torch.Tensor:
         """This rank's [M, N/g] block of C (no exchange)."""
-        if self.mode == "fused" and self.world > 1:
+        if self.mode in ("fused", "copy") and self.world > 1:
             from .gemm import dispatch_multi
 
             # (into the buffer of the latest call: no peer is written, so no ordering is needed)
@@ -111,15 +131,19 @@ class ColumnParallelGemm:
         return assemble_columns(self.gathered, self.c_full)
 
     def __call__(self, A, scale_A, B_shard, scale_B_shard) -> torch.Tensor:
-        if self.mode == "fused" and self.world > 1:
-            from .gemm import dispatch_multi
+        if self.mode in ("fused", "copy") and self.world > 1:
+            from .gemm import dispatch_copy_gather, dispatch_multi
 
             self.c_full, self.symm, self.dests = self.bufs[self.calls % self.depth]
             self.c_shard = self.c_full[:, self.lo:self.hi]
             if self.depth == 1 and self.calls > 0:
                 self.symm.barrier()      # every rank's readers of the previous C are done before anyone overwrites it
             self.calls += 1
-            dispatch_multi(A, B_shard, self.dests, self.lo, scale_A, scale_B_shard, self.fmt)
+            if self.mode == "copy":
+                dispatch_copy_gather(A, B_shard, self.dests, self.lo, scale_A, scale_B_shard, self.copy_scratch,
+                                     self.copy_streams, self.strip_tiles, self.fmt)
+            else:
+                dispatch_multi(A, B_shard, self.dests, self.lo, scale_A, scale_B_shard, self.fmt)
             self.symm.barrier()          # every rank's pushes have landed before anyone reads C
             return self.c_full
         self.local_gemm(A, scale_A, B_shard, scale_B_shard)

@@ -137,6 +137,28 @@ int mxfp6_gemm_multi(const void* a, const void* sfa, const void* b, const void* 
                      void* stream);
 
 /*
+ * The same multi-destination GEMM with the exchange carried by the GPU's copy engines instead of stores from the
+ * SMs (on this fabric copy engines move an all-to-all of C windows at about 750 GB/s per GPU, stores issued by SMs at
+ * about 600).  The kernel writes its [M,N] block to c_dst[0] only and raises one flag per finished block of C
+ * (16 x 256 rows by strip_tiles x 256 columns; blocks finish in row-major order of this grid).  For every peer
+ * destination c_dst[1..] the call queues, on the caller's copy streams, one stream memory operation per block that
+ * waits for the block's flag, followed by a 2-D copy of the block from c_dst[0] to the peer; no kernel waits for
+ * another.  `stream` itself sets every flag behind the kernel, so the copy streams drain even when the kernel gave up,
+ * and finally waits for all copy streams: work queued on `stream` after the call sees all copies done.
+ * copy_streams: a multiple of (n_dst - 1) streams of the same device, consecutive groups belonging to consecutive
+ * peers; two per peer hide the start-up of one copy behind the previous one.  scratch: device memory of at least
+ * mxfp6_copy_gather_scratch_bytes(M, N, strip_tiles) bytes, 4-byte aligned, owned by this call until `stream` has
+ * passed it.  Needs the CTA-pair kernel with TMA stores of C (M > 128, N >= 256, 16-byte aligned destinations and
+ * row stride); other problems are refused with MXFP6_ERR_BAD_ARG.  Not capturable into a CUDA graph.  Stands where
+ * mxfp6_gemm_multi stands (distributed-kernels/bf16_gemm/kernel.cpp:253-265); the reference has no copy-engine path.
+ */
+size_t mxfp6_copy_gather_scratch_bytes(int64_t M, int64_t N, int strip_tiles);
+int mxfp6_gemm_copy_gather(const void* a, const void* sfa, const void* b, const void* sfb, void* const* c_dst,
+                           int n_dst, int64_t ldc, int64_t M, int64_t N, int64_t K, int fmt_a, int fmt_b,
+                           void* scratch, size_t scratch_bytes, int strip_tiles, void* const* copy_streams,
+                           int n_copy_streams, void* stream);
+
+/*
  * The same GEMM for hosts that must not allocate device memory while they run: servers that hand all of the
  * GPU's memory to their own pool at start-up, control loops with a latency bound (cudaMalloc may synchronise
  * the device, and may fail when memory is tight), or plug-ins whose host forbids allocation in the call path.

@@ -181,6 +181,47 @@ def test_pair_kernel_plain_store_path_16_byte_rows(shape):
         hk.debug_option("MXFP6_C_PLAIN", None)
 
 
+@pytest.mark.parametrize("shape,strip,spp", [((4352, 2304, 512), 4, 2),      # 2 row groups, strips of 4, 4 and 1 tiles, sliced last wave
+                                             ((2000, 2568, 256), 2, 1),      # ragged edges, one copy stream per peer
+                                             ((2304, 2560, 256), 16, 2)])    # one block per row group
+def test_copy_gather_on_one_gpu(shape, strip, spp):
+    """`mxfp6_gemm_copy_gather` with the "peers" on the same GPU: the kernel writes destination 0 and raises a flag per
+    finished block; copy streams wait for the flags and copy the blocks into the other destinations' column windows.
+    Every destination ends with the plain GEMM's result bit for bit and nothing outside its window is touched.  Two
+    calls in a row: the second starts from flags the first left set."""
+    M, N, K = shape
+    pa, sa, pb, sb = quantized_inputs("lognormal", M, N, K, seed=N)
+    t = [torch.from_numpy(x).cuda() for x in (pa, sa, pb, sb)]
+    want = torch.empty((M, N), dtype=torch.bfloat16, device="cuda")
+    hk.dispatch_micro(t[0], t[2], want, t[1], t[3], R.E2M3)
+    ldc, off, n_dst = N + 264, 136, 3
+    streams = [torch.cuda.Stream() for _ in range(spp * (n_dst - 1))]
+    scratch = torch.zeros(hk.copy_gather_scratch_bytes(M, N, strip) // 4, dtype=torch.int32, device="cuda")
+    for _ in range(2):
+        dests = [torch.full((M, ldc), float("nan"), dtype=torch.bfloat16, device="cuda") for _ in range(n_dst)]
+        hk.dispatch_copy_gather(t[0], t[2], dests, off, t[1], t[3], scratch, streams, strip, R.E2M3)
+        reader = [d[:, off:off + N].clone() for d in dests]      # queued on the launching stream, no host synchronisation
+        torch.cuda.synchronize()
+        assert hk.device_status() == 0
+        for d, r in zip(dests, reader):
+            assert torch.equal(r.view(torch.int16), want.view(torch.int16))
+            assert torch.isnan(d[:, :off]).all() and torch.isnan(d[:, off + N:]).all(), "write outside the window"
+    ref, absdot = oracle_f64(pa, sa, pb, sb, R.E2M3)
+    check(want.float().cpu().numpy(), ref, absdot)
+
+
+def test_copy_gather_refuses_what_it_cannot_signal():
+    """Problems that do not run on the CTA-pair kernel have no per-block flags: the call says so and queues nothing."""
+    M, N, K = 64, 1024, 256
+    pa, sa, pb, sb = quantized_inputs("normal", M, N, K, seed=3)
+    t = [torch.from_numpy(x).cuda() for x in (pa, sa, pb, sb)]
+    dests = [torch.zeros((M, N), dtype=torch.bfloat16, device="cuda") for _ in range(2)]
+    scratch = torch.zeros(64, dtype=torch.int32, device="cuda")
+    with pytest.raises(RuntimeError, match="CTA-pair kernel"):
+        hk.dispatch_copy_gather(t[0], t[2], dests, 0, t[1], t[3], scratch, [torch.cuda.Stream()], 8, R.E2M3)
+    torch.cuda.synchronize()
+
+
 def test_pair_kernel_plain_store_odd_window():
     """Several destinations whose column window starts at an odd element of rows with an odd stride."""
     hk.debug_option("MXFP6_FORCE_CFG", "256,0,0,1")

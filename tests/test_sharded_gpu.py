@@ -21,33 +21,42 @@ from hipkittensp_b200.sharded import ColumnParallelGemm, RowParallelGemm, shard_
 rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
 torch.cuda.set_device(rank); dev = torch.device("cuda", rank)
 dist.init_process_group("nccl", device_id=dev)
-M, N, K = 512, 2048, 1024
-g = torch.Generator(device=dev).manual_seed(5)
-B = torch.randn(N, K, device=dev, generator=g)
-pb, sb = hk.quantize(B)
-# a different A for every step, and the single-GPU result of each whole problem
 STEPS = 6
-ops, want = [], []
-for i in range(STEPS):
-    pa, sa = hk.quantize(torch.randn(M, K, device=dev, generator=g))
-    ops.append((pa, sa)); want.append(hk.gemm(pa, sa, pb, sb))
+ok = True
 def digest(C):
     # a reader of C queued on the stream right behind the step (no host synchronisation in between)
     return (C.view(torch.int16).to(torch.int64) * torch.arange(1, C.numel() + 1, device=dev).view_as(C)).sum()
-want_digest = [digest(w) for w in want]
-ok = True
-pbs, sbs = shard_rows(pb, world, rank), shard_rows(sb, world, rank)
-for mode, depth in (("nccl", 2), ("fused", 2), ("fused", 1)):
-    op = ColumnParallelGemm(M, N, K, device=dev, gather=mode, depth=depth)
-    got = []
+def column_parallel_case(M, N, K, modes):
+    global ok
+    g = torch.Generator(device=dev).manual_seed(5)
+    B = torch.randn(N, K, device=dev, generator=g)
+    pb, sb = hk.quantize(B)
+    # a different A for every step, and the single-GPU result of each whole problem
+    ops, want = [], []
     for i in range(STEPS):
-        C = op(ops[i][0], ops[i][1], pbs, sbs)
-        got.append(digest(C))                 # the next step follows without waiting for this reader on the host
-        if rank == i % world:
-            torch.cuda._sleep(2000000)        # one rank falls behind: its peers run ahead into the next step
-    torch.cuda.synchronize()
-    ok = ok and all(int(a) == int(b) for a, b in zip(got, want_digest))
-    ok = ok and bool(torch.equal(C.view(torch.int16), want[-1].view(torch.int16)))
+        pa, sa = hk.quantize(torch.randn(M, K, device=dev, generator=g))
+        ops.append((pa, sa)); want.append(hk.gemm(pa, sa, pb, sb))
+    want_digest = [digest(w) for w in want]
+    pbs, sbs = shard_rows(pb, world, rank), shard_rows(sb, world, rank)
+    for mode, depth, kw in modes:
+        op = ColumnParallelGemm(M, N, K, device=dev, gather=mode, depth=depth, **kw)
+        ok = ok and op.mode == mode
+        got = []
+        for i in range(STEPS):
+            C = op(ops[i][0], ops[i][1], pbs, sbs)
+            got.append(digest(C))                 # the next step follows without waiting for this reader on the host
+            if rank == i % world:
+                torch.cuda._sleep(2000000)        # one rank falls behind: its peers run ahead into the next step
+        torch.cuda.synchronize()
+        ok = ok and all(int(a) == int(b) for a, b in zip(got, want_digest))
+        ok = ok and bool(torch.equal(C.view(torch.int16), want[-1].view(torch.int16)))
+    return ops, want, pb, sb
+M, N, K = 512, 2048, 1024
+ops, want, pb, sb = column_parallel_case(M, N, K, (("nccl", 2, {}), ("fused", 2, {}), ("fused", 1, {})))
+# a shard large enough for the CTA-pair kernel (2 row groups, ragged column strips, sliced last wave): the exchange by
+# copy engines behind per-block flags, with one and with two copy streams per peer
+column_parallel_case(4352, 2 * 2304, 512, (("copy", 2, dict(strip_tiles=4)), ("copy", 1, dict(strip_tiles=2, streams_per_peer=1)),
+                                           ("fused", 2, {})))
 for gth, depth in ((False, 2), (True, 2), (True, 1)):
     rp = RowParallelGemm(M, N, K, device=dev, gather=gth, depth=depth)
     got = []
