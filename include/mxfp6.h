@@ -138,15 +138,18 @@ int mxfp6_gemm_multi(const void* a, const void* sfa, const void* b, const void* 
 
 /*
  * The same multi-destination GEMM with the exchange carried by the GPU's copy engines instead of stores from the
- * SMs (on this fabric copy engines move an all-to-all of C windows at about 750 GB/s per GPU, stores issued by SMs at
- * about 600).  The kernel writes its [M,N] block to c_dst[0] only and raises one flag per finished block of C
+ * SMs (on this fabric copy engines move an all-to-all of C windows at about 750 GB/s per GPU when each window is one
+ * copy, stores issued by SMs at about 600; cut into blocks that can follow the GEMM the copies lose that advantage, so
+ * this form is an alternative to mxfp6_gemm_multi for callers that want the SMs free of the exchange, not a faster one).  The kernel writes its [M,N] block to c_dst[0] only and raises one flag per finished block of C
  * (16 x 256 rows by strip_tiles x 256 columns; blocks finish in row-major order of this grid).  For every peer
  * destination c_dst[1..] the call queues, on the caller's copy streams, one stream memory operation per block that
  * waits for the block's flag, followed by a 2-D copy of the block from c_dst[0] to the peer; no kernel waits for
  * another.  `stream` itself sets every flag behind the kernel, so the copy streams drain even when the kernel gave up,
  * and finally waits for all copy streams: work queued on `stream` after the call sees all copies done.
  * copy_streams: a multiple of (n_dst - 1) streams of the same device, consecutive groups belonging to consecutive
- * peers; two per peer hide the start-up of one copy behind the previous one.  scratch: device memory of at least
+ * peers.  Measured on 4 GPUs: the copy engines are at their best with few large copies (one copy of the whole window per
+ * peer 737 GB/s, 4 row blocks 708, 16 row blocks 605, 4 x 7 blocks 579), and several copies in flight to the same peer
+ * make it worse (16 blocks on two streams per peer 449), so: one stream per peer and strip_tiles large.  scratch: device memory of at least
  * mxfp6_copy_gather_scratch_bytes(M, N, strip_tiles) bytes, 4-byte aligned, owned by this call until `stream` has
  * passed it.  Needs the CTA-pair kernel with TMA stores of C (M > 128, N >= 256, 16-byte aligned destinations and
  * row stride); other problems are refused with MXFP6_ERR_BAD_ARG.  Not capturable into a CUDA graph.  Stands where
