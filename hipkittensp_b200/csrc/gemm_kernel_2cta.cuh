@@ -166,16 +166,27 @@ mxfp6_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_co
         tma_prefetch_desc(&tm_p); tma_prefetch_desc(&tm_q); tma_prefetch_desc(&tm_sfp); tma_prefetch_desc(&tm_sfq);
         if (P.tail_split > 1) tma_prefetch_desc(&tm_q_tail);
     }
+    // Every thread arrives at the cluster's meeting point as soon as it can (thread 0 after it has initialised the
+    // barriers): once the wait returns, the barriers of both CTAs are initialised, which is all the producer warp needs
+    // before it signals the peer.  It does not wait for the TMEM allocation: it announces itself at the CTA's own meeting
+    // point and goes on to request the first stages, everybody else meets there and picks up the TMEM address.
+    __syncwarp();                // (warp 0 comes out of the one-thread blocks above)
+    cluster_arrive();
     if (warp == 1) {
         tmem_alloc_pair(smem_u32(tmem_slot), Cfg::TMEM_COLS);
         tmem_relinquish_pair();
     }
     tc_fence_before();
-    __syncthreads();
-    cluster_arrive();            // barriers of both CTAs are initialised before anyone signals the peer
+    if (warp == 0) {
+        __syncwarp();
+        __threadfence_block();
+        asm volatile("bar.arrive 2, 256;" ::: "memory");
+    } else {
+        asm volatile("bar.sync 2, 256;" ::: "memory");
+    }
     cluster_wait();
     tc_fence_after();
-    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t tmem_base = warp == 0 ? 0u : *tmem_slot;
     pdl_wait();                  // nothing above touches global memory; everything below may
 
     auto signal_abort_to_peer = [&]() { st_shared_cluster_u32(mapa_shared(abort_addr, rank ^ 1), 1u); };
@@ -562,7 +573,9 @@ mxfp6_gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_co
             }
             ++n_seg;
         }
-        if (etid == 0) bulk_wait_group<0>();      // all stores (local and peer) are done before the CTA leaves
+        // the staging buffers have been read before the CTA leaves; the writes themselves are complete when the grid is
+        // (with completion flags every unit has already waited for its writes above)
+        if (etid == 0) bulk_wait_group_read<0>();
         if (!ok && lane == 0) signal_abort_to_peer();
     }
 
