@@ -65,6 +65,7 @@ struct GemmParams {
     unsigned int* sig_counter;
     unsigned int* sig_flag;
     int sig_cols;
+    int c_tma_last;            // single-CTA kernel, unswapped: the last tile of every CTA leaves through the idle ring and TMA stores (tm_c is a map of C)
     int c_tma;                 // pair kernel: C is stored by TMA (16-byte aligned destinations and row stride); else by plain stores
     uint8_t* q_out;            // re-quantised output instead of bf16 C: operand bytes [M, 3N/4 or N] ...
     uint8_t* q_scales;         // ... and E8M0 scales [M, N/32], blocks of 32 along N
@@ -239,6 +240,8 @@ struct SegIter {
         p0 = (first_p + in % gsz) * P.p_tile_rows;
         q0 = (in / gsz) * P.q_tile_rows;
     }
+    // after next() returned a segment: is it the last one of this CTA?
+    __device__ bool last() const { return Cfg::STREAMK ? i >= nsegs : tile >= num_tiles; }
     __device__ bool next(Segment& s) {
         if (Cfg::STREAMK) {
             if (i >= nsegs) return false;
@@ -312,7 +315,7 @@ template <class Cfg>
 __global__ void __launch_bounds__(Cfg::THREADS, Cfg::CTAS)
 mxfp6_gemm_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constant__ CUtensorMap tm_q,
                   const __grid_constant__ CUtensorMap tm_sfp, const __grid_constant__ CUtensorMap tm_sfq,
-                  const GemmParams P) {
+                  const __grid_constant__ CUtensorMap tm_c, const GemmParams P) {
     constexpr int BN = Cfg::BN;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -664,26 +667,22 @@ mxfp6_gemm_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constan
             const int p = sg.p0 + prow;
             // with overlapping accumulators the 32 shared columns are drained first
             auto chunk_of = [&](int ci) { return Cfg::OVERLAP ? (b == 0 ? (ci + NCH - 1) % NCH : ci) : ci; };
-            // The chunks are read from TMEM one ahead: while chunk ci is converted and stored, the load of chunk ci + 1
-            // is already under way (the drain of a tile is a chain of TMEM round trips otherwise: 4.3 us for a 128 x 200
-            // tile, a tenth of a skinny launch).  Chunks that lie wholly past the tile's own columns are not read.
-            uint32_t v[CW], vn[CW];
-            auto load_chunk = [&](int ch, uint32_t (&dst)[CW]) {
-                if (!Cfg::SWAP && ch * CW >= P.q_tile_rows) return;
-                if constexpr (CW == 32) tmem_ld_x32(tacc + ch * CW, reinterpret_cast<uint32_t(&)[32]>(dst));
-                else tmem_ld_x16(tacc + ch * CW, reinterpret_cast<uint32_t(&)[16]>(dst));
-            };
-            load_chunk(chunk_of(0), v);
-            tmem_ld_wait();
-#pragma unroll 1
-            for (int ci = 0; ci < NCH; ++ci) {
-                const int ch = chunk_of(ci);
-                if (ci + 1 < NCH) load_chunk(chunk_of(ci + 1), vn);
-                if (Cfg::OVERLAP && ci == 0) { tc_fence_before(); __syncwarp(); if (lane == 0) mbar_arrive(bar_ovl); }
-                if (!Cfg::OVERLAP && ci == NCH - 1) { tc_fence_before(); mbar_arrive(bar_acc_empty(b)); }
+            // The tile is read from TMEM in groups of up to four chunks per wait.  A load and its wait are a round trip of
+            // about half a microsecond whatever the width: drained chunk by chunk, a 256-column tile took 4.3 us (a tenth
+            // of a skinny launch), whether or not the next chunk's load was already under way and whether the stores went
+            // to rows of C or to shared memory.  Chunks that lie wholly past the tile's own columns are not read.
+            constexpr int G = NCH < 4 ? NCH : 4;
+            // The last tile of a CTA overlaps nothing, and in the unswapped form every lane stores to a row of its own: a
+            // store instruction touches 32 lines and costs the load/store unit about 300 cycles, 2.2 to 2.8 us for a
+            // 128 x 200 tile whatever the number of live rows.  By then the ring is idle (every load has landed and every MMA
+            // has read it: that is what acc_full says), so the whole 64-column pieces of that tile are staged there as
+            // swizzled 128-byte rows and leave by TMA stores; columns past the last whole piece keep the plain stores.
+            const bool staged = !Cfg::SWAP && CW == 32 && P.c_tma_last && !partial && P.q_fmt < 0 && it.last();
+            const int tile_cols = min(P.c_cols - sg.q0, P.q_tile_rows);
+            const int n_pieces = staged ? tile_cols / 64 : 0;
+            auto process = [&](int ch, uint32_t (&v)[CW]) {
                 const int qc = sg.q0 + ch * CW;              // first D column of this chunk
-                const bool dead = !Cfg::SWAP && ch * CW >= P.q_tile_rows;      // nothing of this chunk belongs to the tile
-                if (!dead) {
+                if (!Cfg::SWAP && ch * CW >= P.q_tile_rows) return;          // nothing of this chunk belongs to the tile
                 if (!partial && affine) {
                     if constexpr (Cfg::SWAP) {
                         affine_chunk<true, CW>(P, v, p, qc);
@@ -727,6 +726,20 @@ mxfp6_gemm_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constan
                         if (p < P.c_rows && qc < P.c_cols)
                             quant_store32(v, P.q_fmt, P.q_out, (size_t)P.q_ld, P.q_scales, P.c_cols, p, qc);
                     }
+                } else if (!Cfg::SWAP && CW == 32 && (ch >> 1) < n_pieces) {
+                    // row prow of piece ch / 2 is 128 bytes in 16-byte units; unit u sits at u ^ (row % 8): the 128-byte
+                    // swizzle the TMA store expects
+                    const uint32_t rowaddr = stage_base + (uint32_t)(ch >> 1) * (128u * 128u) + (uint32_t)prow * 128u;
+                    const uint32_t sw = (uint32_t)(prow & 7);
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        const uint32_t x0 = pack_bf16x2(__uint_as_float(v[8 * c + 0]), __uint_as_float(v[8 * c + 1]));
+                        const uint32_t x1 = pack_bf16x2(__uint_as_float(v[8 * c + 2]), __uint_as_float(v[8 * c + 3]));
+                        const uint32_t x2 = pack_bf16x2(__uint_as_float(v[8 * c + 4]), __uint_as_float(v[8 * c + 5]));
+                        const uint32_t x3 = pack_bf16x2(__uint_as_float(v[8 * c + 6]), __uint_as_float(v[8 * c + 7]));
+                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};"
+                                     ::"r"(rowaddr + ((((uint32_t)(ch & 1) * 4u + (uint32_t)c) ^ sw) << 4)), "r"(x0), "r"(x1), "r"(x2), "r"(x3) : "memory");
+                    }
                 } else {
                     // columns past the tile's own columns belong to the next tile
                     const int q_lim = min(P.c_cols, sg.q0 + P.q_tile_rows);
@@ -735,6 +748,20 @@ mxfp6_gemm_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constan
                         __nv_bfloat16* cbase = d == 0 ? P.c : P.c_more[d - 1];
                         __nv_bfloat16* dst = cbase + (size_t)p * P.ldc + qc;
                         const bool vec = ((P.ldc & 7) == 0) && ((reinterpret_cast<uintptr_t>(cbase) & 15) == 0) && ((P.q_tile_rows & 7) == 0);
+                        // whole 32-byte sectors where the chunk starts on one: a 16-byte store is a partial write of its sector
+                        if (CW == 32 && vec && ((P.ldc & 15) == 0) && ((reinterpret_cast<uintptr_t>(dst) & 31) == 0) && qc + CW <= q_lim) {
+#pragma unroll
+                            for (int i = 0; i < CW; i += 16)
+                                st_global_v8(dst + i, pack_bf16x2(__uint_as_float(v[i + 0]), __uint_as_float(v[i + 1])),
+                                             pack_bf16x2(__uint_as_float(v[i + 2]), __uint_as_float(v[i + 3])),
+                                             pack_bf16x2(__uint_as_float(v[i + 4]), __uint_as_float(v[i + 5])),
+                                             pack_bf16x2(__uint_as_float(v[i + 6]), __uint_as_float(v[i + 7])),
+                                             pack_bf16x2(__uint_as_float(v[i + 8]), __uint_as_float(v[i + 9])),
+                                             pack_bf16x2(__uint_as_float(v[i + 10]), __uint_as_float(v[i + 11])),
+                                             pack_bf16x2(__uint_as_float(v[i + 12]), __uint_as_float(v[i + 13])),
+                                             pack_bf16x2(__uint_as_float(v[i + 14]), __uint_as_float(v[i + 15])));
+                            continue;
+                        }
 #pragma unroll
                         for (int i = 0; i < CW; i += 8) {
                             if (vec && qc + i + 8 <= q_lim) {
@@ -752,11 +779,33 @@ mxfp6_gemm_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constan
                         }
                     }
                 }
-                }
-                if (ci + 1 < NCH) {
-                    tmem_ld_wait();
+            };
+#pragma unroll 1
+            for (int cg = 0; cg < NCH; cg += G) {
+                uint32_t v[G][CW];
 #pragma unroll
-                    for (int i = 0; i < CW; ++i) v[i] = vn[i];
+                for (int g = 0; g < G; ++g) {
+                    const int ch = chunk_of(cg + g);
+                    if (Cfg::SWAP || ch * CW < P.q_tile_rows) {
+                        if constexpr (CW == 32) tmem_ld_x32(tacc + ch * CW, reinterpret_cast<uint32_t(&)[32]>(v[g]));
+                        else tmem_ld_x16(tacc + ch * CW, reinterpret_cast<uint32_t(&)[16]>(v[g]));
+                    }
+                }
+                tmem_ld_wait();
+                // (the first group holds the columns the two accumulators share; after the last group nothing of this
+                // accumulator is left in TMEM)
+                if (Cfg::OVERLAP && cg == 0) { tc_fence_before(); __syncwarp(); if (lane == 0) mbar_arrive(bar_ovl); }
+                if (!Cfg::OVERLAP && cg + G >= NCH) { tc_fence_before(); mbar_arrive(bar_acc_empty(b)); }
+#pragma unroll
+                for (int g = 0; g < G; ++g) process(chunk_of(cg + g), v[g]);
+            }
+            if (n_pieces > 0) {
+                fence_proxy_async_smem();
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (etid == 0) {
+                    for (int pc = 0; pc < n_pieces; ++pc) tma_store_2d(&tm_c, stage_base + (uint32_t)pc * (128u * 128u), sg.q0 + 64 * pc, sg.p0);
+                    bulk_commit_group();
+                    bulk_wait_group_read<0>();       // the ring is read before the CTA leaves (this was its last tile)
                 }
             }
             if (partial) {

@@ -60,6 +60,7 @@ struct Options {
     int decode_rows = 1;     // MXFP6_DECODE_ROWS: skinny problems take the row-balanced kernel when they qualify
     int decode_stages = 0, decode_batch = 0;   // MXFP6_DECODE_RING = "stages,batch": ring of that kernel (0 = chosen by the library)
     int push_rotate = 1;     // MXFP6_PUSH_ROTATE: pair kernel, rotate the order of the peer destinations from piece to piece
+    int c_tma_last = 1;      // MXFP6_C_TMA_LAST: the unswapped single-CTA kernel drains the last tile of every CTA through its idle ring and TMA stores
     int c_plain = 0;         // MXFP6_C_PLAIN: the pair kernel writes C with plain stores from its staging buffer even where TMA stores are possible
     int k_rot = 1;           // MXFP6_K_ROT: the even-rows skinny forms start each tile's K loop at its own K-block
 };
@@ -84,6 +85,7 @@ static bool set_option(const char* name, const char* v) {
     else if (!strcmp(name, "MXFP6_DECODE_ROWS")) g_opt.decode_rows = v ? atoi(v) : d.decode_rows;
     else if (!strcmp(name, "MXFP6_K_ROT")) g_opt.k_rot = v ? atoi(v) : d.k_rot;
     else if (!strcmp(name, "MXFP6_C_PLAIN")) g_opt.c_plain = v ? atoi(v) : d.c_plain;
+    else if (!strcmp(name, "MXFP6_C_TMA_LAST")) g_opt.c_tma_last = v ? atoi(v) : d.c_tma_last;
     else if (!strcmp(name, "MXFP6_PUSH_ROTATE")) g_opt.push_rotate = v ? atoi(v) : d.push_rotate;
     else if (!strcmp(name, "MXFP6_DECODE_RING")) {
         g_opt.decode_stages = d.decode_stages; g_opt.decode_batch = d.decode_batch;
@@ -93,7 +95,7 @@ static bool set_option(const char* name, const char* v) {
     return true;
 }
 static const char* const kOptionNames[] = {"MXFP6_FORCE_CFG", "MXFP6_NO_SF_TMA", "MXFP6_PDL", "MXFP6_GROUP_P", "MXFP6_QUANT_PATH",
-                                           "MXFP6_WAIT_MS", "MXFP6_L2", "MXFP6_TAIL_SPLIT", "MXFP6_DECODE_ROWS", "MXFP6_DECODE_RING", "MXFP6_K_ROT", "MXFP6_PUSH_ROTATE", "MXFP6_C_PLAIN"};
+                                           "MXFP6_WAIT_MS", "MXFP6_L2", "MXFP6_TAIL_SPLIT", "MXFP6_DECODE_ROWS", "MXFP6_DECODE_RING", "MXFP6_K_ROT", "MXFP6_PUSH_ROTATE", "MXFP6_C_PLAIN", "MXFP6_C_TMA_LAST"};
 static const Options& options() {
     std::call_once(g_opt_once, [] {
         for (const char* n : kOptionNames)
@@ -425,7 +427,7 @@ struct Recipe {
     bool pair = false, pdl = true;
     size_t counter_bytes = 0;    // built-in scratch: counters to clear before every launch
     void* counter_ptr = nullptr;
-    CUtensorMap tp, tq, tq_tail, tsp, tsq;
+    CUtensorMap tp, tq, tq_tail, tsp, tsq, tc;
     CMaps cm;
     GemmParams P;
 };
@@ -457,7 +459,7 @@ static int launch_recipe(const Recipe& r, cudaStream_t st) {
         void* args[] = {(void*)&r.tp, (void*)&r.tq, (void*)&r.tq_tail, (void*)&r.tsp, (void*)&r.tsq, (void*)&r.cm, (void*)&r.P};
         CUDA_TRY(cudaLaunchKernelExC(&lc, r.func, args));
     } else {
-        void* args[] = {(void*)&r.tp, (void*)&r.tq, (void*)&r.tsp, (void*)&r.tsq, (void*)&r.P};
+        void* args[] = {(void*)&r.tp, (void*)&r.tq, (void*)&r.tsp, (void*)&r.tsq, (void*)&r.tc, (void*)&r.P};
         CUDA_TRY(cudaLaunchKernelExC(&lc, r.func, args));
     }
     return MXFP6_OK;
@@ -636,6 +638,10 @@ static int gemm_impl(const void* a, const void* sfa, const void* b, const void* 
     P.push_rotate = o.push_rotate;
     P.c_tma = (q_fmt >= 0 || (dest_by_tma(dst) && !o.c_plain)) ? 1 : 0;
     P.c_vec16 = (dest_by_tma(dst) && N % 8 == 0) ? 1 : 0;
+    // (a TMA store writes 128 rows: tiles of fewer rows only where there is a single row of tiles, so that what lies
+    // below the tile lies below C and is clipped)
+    P.c_tma_last = (!pl.pair && !pl.swap && o.c_tma_last && q_fmt < 0 && dst.n == 1 && dest_by_tma(dst) &&
+                    (pl.p_tile == 128 || pl.tiles_p == 1)) ? 1 : 0;
     P.q_out = (uint8_t*)q_out; P.q_scales = (uint8_t*)q_scales; P.q_fmt = q_fmt;
     P.q_ld = q_fmt < 0 ? 0 : (fmt_is_fp8(q_fmt) ? N : N * 3 / 4);
     P.ws_counter = (unsigned int*)ws;
@@ -672,6 +678,8 @@ static int gemm_impl(const void* a, const void* sfa, const void* b, const void* 
             } else if ((rc = make_map(dst.c[i], M, N, 128, 2, &r.cm.m[i], dst.ldc * 2))) return rc;
         }
     } else {
+        r.tc = r.tp;            // (the slot only has to hold a valid map when the kernel does not use it)
+        if (P.c_tma_last && (rc = make_map(dst.c[0], M, N, 128, 2, &r.tc, dst.ldc * 2))) return rc;
         rc = -1;
 #define MXFP6_CASE(BN_, SWAP_, SK_)                                                              \
         if (pl.ctas == 1 && pl.bn == BN_ && pl.swap == SWAP_ && pl.streamk == SK_) rc = bind_cfg<GemmCfg<BN_, SWAP_, SK_>>(d, r);

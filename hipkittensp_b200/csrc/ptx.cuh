@@ -91,6 +91,12 @@ __device__ __forceinline__ uint64_t l2_policy_evict_normal() {
 __device__ __forceinline__ uint64_t l2_policy(int kind) {
     return kind == 1 ? l2_policy_evict_first() : kind == 2 ? l2_policy_evict_last() : l2_policy_evict_normal();
 }
+// 32-byte global store (one whole sector per lane)
+__device__ __forceinline__ void st_global_v8(void* ptr, uint32_t x0, uint32_t x1, uint32_t x2, uint32_t x3,
+                                             uint32_t x4, uint32_t x5, uint32_t x6, uint32_t x7) {
+    asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+                 ::"l"(ptr), "r"(x0), "r"(x1), "r"(x2), "r"(x3), "r"(x4), "r"(x5), "r"(x6), "r"(x7) : "memory");
+}
 __device__ __forceinline__ void tma_load_2d_hint(uint32_t dst_smem, const CUtensorMap* m, uint32_t bar, int x, int y, uint64_t policy) {
     asm volatile(
         "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%3, %4}], [%2], %5;"

@@ -212,7 +212,7 @@ int mxfp6_debug_wait_timeout(int budget_us, void* stream);
 /*
  * Test hook: sets one of the library's switches (the names of the environment variables that give their first
  * values: "MXFP6_FORCE_CFG" = "bn,swap,streamk[,pair]" forces a kernel variant, "MXFP6_NO_SF_TMA", "MXFP6_PDL",
- * "MXFP6_GROUP_P", "MXFP6_QUANT_PATH", "MXFP6_L2", "MXFP6_TAIL_SPLIT", "MXFP6_DECODE_ROWS", "MXFP6_DECODE_RING", "MXFP6_K_ROT", "MXFP6_PUSH_ROTATE", "MXFP6_C_PLAIN"); value NULL restores the
+ * "MXFP6_GROUP_P", "MXFP6_QUANT_PATH", "MXFP6_L2", "MXFP6_TAIL_SPLIT", "MXFP6_DECODE_ROWS", "MXFP6_DECODE_RING", "MXFP6_K_ROT", "MXFP6_PUSH_ROTATE", "MXFP6_C_PLAIN", "MXFP6_C_TMA_LAST"); value NULL restores the
  * default.  Takes effect for calls made after it returns.  (No counterpart in the reference.)
  */
 int mxfp6_debug_option(const char* name, const char* value);

@@ -181,6 +181,32 @@ def test_pair_kernel_plain_store_path_16_byte_rows(shape):
         hk.debug_option("MXFP6_C_PLAIN", None)
 
 
+@pytest.mark.parametrize("shape,force", [((64, 29600, 256), None),           # unswapped skinny form: 148 tiles of 200 columns, 3 whole pieces each
+                                         ((128, 29600, 256), None),          # every row of the tile live
+                                         ((96, 23680, 256), None),           # 160-column tiles: 2 whole pieces and a 32-column rest
+                                         ((100, 1024, 384), "256,0,0"),      # rows past M clipped by the store
+                                         ((300, 520, 384), "256,0,0"),       # ragged edges, tiles of the last row block clipped
+                                         ((1536, 1792, 256), "128,0,0"),     # BN = 128, several tiles per CTA: only the last is staged
+                                         ((2304, 2560, 256), "256,0,1")])    # K-split form: the last visited piece is a whole tile
+def test_single_cta_last_tile_leaves_by_tma(shape, force):
+    """The unswapped single-CTA kernel drains the last tile of every CTA through its idle ring and TMA stores; the
+    values are those of the plain stores, bit for bit, and nothing outside C is written."""
+    M, N, K = shape
+    if force:
+        hk.debug_option("MXFP6_FORCE_CFG", force)
+    try:
+        pa, sa, pb, sb = quantized_inputs("lognormal", M, N, K, seed=M + N)
+        c = run_gpu(pa, sa, pb, sb, R.E2M3)
+        ref, absdot = oracle_f64(pa, sa, pb, sb, R.E2M3)
+        check(c, ref, absdot)
+        hk.debug_option("MXFP6_C_TMA_LAST", "0")
+        c_plain = run_gpu(pa, sa, pb, sb, R.E2M3)
+    finally:
+        hk.debug_option("MXFP6_C_TMA_LAST", None)
+        hk.debug_option("MXFP6_FORCE_CFG", None)
+    np.testing.assert_array_equal(c, c_plain)
+
+
 @pytest.mark.parametrize("shape,strip,spp", [((4352, 2304, 512), 4, 2),      # 2 row groups, strips of 4, 4 and 1 tiles, sliced last wave
                                              ((2000, 2568, 256), 2, 1),      # ragged edges, one copy stream per peer
                                              ((2304, 2560, 256), 16, 2)])    # one block per row group
