@@ -21,9 +21,9 @@ Two exchanges:
 * `gather="copy"`: the same symmetric C buffers, but the kernel writes only the local C and raises a flag per finished
   block of it; side streams wait for the flags (stream memory operations) and the GPU's copy engines carry the blocks
   to the peers (`mxfp6_gemm_copy_gather`).  The GEMM is not slowed by pushing, but nothing leaves before a whole block
-  is finished and the copy engines want few large copies: measured on 4 GPUs this exchange is no faster than "fused"
-  (2.3 to 3.3 ms per step of 16384 x 57344 x 8192 depending on the block shape, against 2.3).  The same ordering rules
-  as "fused".
+  is finished, the copy engines want few large copies, and copies and GEMM compete for HBM: measured on 4 GPUs this
+  exchange is slower than "fused" (3.3 ms per step of 16384 x 57344 x 8192 against 2.3).  The same ordering rules as
+  "fused".
 * `gather="nccl"`: one NCCL (or gloo, on CPU) all-gather of the contiguous [M, N/g] shards into a [g, M, N/g]
   buffer followed by a strided copy into row-major C.  The baseline, and the path the CPU tests use.
 """
