@@ -139,8 +139,10 @@ int mxfp6_gemm_multi(const void* a, const void* sfa, const void* b, const void* 
 /*
  * The same multi-destination GEMM with the exchange carried by the GPU's copy engines instead of stores from the
  * SMs (on this fabric copy engines move an all-to-all of C windows at about 750 GB/s per GPU when each window is one
- * copy, stores issued by SMs at about 600; cut into blocks that can follow the GEMM the copies lose that advantage, so
- * this form is an alternative to mxfp6_gemm_multi for callers that want the SMs free of the exchange, not a faster one).  The kernel writes its [M,N] block to c_dst[0] only and raises one flag per finished block of C
+ * copy, stores issued by SMs at about 600; cut into blocks that can follow the GEMM the copies lose that advantage,
+ * and they compete with the GEMM for HBM: a step of 16384 x 57344 x 8192 on 4 GPUs takes 3.3 ms this way against 2.3 ms
+ * with mxfp6_gemm_multi, so this form is an alternative for callers that want the SMs free of the exchange, not a
+ * faster one).  The kernel writes its [M,N] block to c_dst[0] only and raises one flag per finished block of C
  * (16 x 256 rows by strip_tiles x 256 columns; blocks finish in row-major order of this grid).  For every peer
  * destination c_dst[1..] the call queues, on the caller's copy streams, one stream memory operation per block that
  * waits for the block's flag, followed by a 2-D copy of the block from c_dst[0] to the peer; no kernel waits for
