@@ -80,7 +80,7 @@ struct GemmParams {
     int tail_first;            // pair kernel: first tile of the last partial wave that is cut into column slices (= tile count if none)
     int tail_split;            // pair kernel: slices per such tile (1, 2 or 4)
     int stage_tx_bytes_tail;   // pair kernel: bytes one CTA's loads of a slice's stage report
-    int early_p;               // swapped form: P (the weights) may be read before the preceding kernel has finished
+    int early_p;               // single-CTA kernel: the weights (B: P when swapped, Q otherwise) may be read before the preceding kernel has finished
     int l2_load, l2_store;     // L2 eviction policy of the operand loads / of the stores of C (0 normal, 1 evict_first, 2 evict_last)
     int l2_p, l2_q;            // single-CTA kernel: policy of the loads of P / of Q (an operand that is read once leaves L2 first, one that every CTA re-reads last)
     // optional fp32 epilogue, applied to the finished sum before it is rounded (null = absent):
@@ -383,8 +383,8 @@ mxfp6_gemm_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constan
     tc_fence_after();
     const uint32_t tmem_base = warp == 0 ? 0u : *tmem_slot;
     // Nothing above touches global memory; everything below may.  With early_p the producer warp alone goes
-    // ahead and requests the first stages of P (weights that the preceding kernel does not write) before it waits.
-    const bool early = Cfg::SWAP && P.early_p != 0;
+    // ahead and requests the first stages of the weights (which the preceding kernel does not write) before it waits.
+    const bool early = P.early_p != 0;
     if (!(early && warp == 0)) pdl_wait();
 
     // =========================================================== warp 0: TMA producer
@@ -394,9 +394,28 @@ mxfp6_gemm_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constan
         Segment sg;
         uint32_t n_stage = 0, n_raw = 0;
         uint32_t st_idx = 0, st_phase = 0;        // ring position of stage number n_stage and the parity of its round (no division: the ring size may be a run-time value)
-        uint32_t pre_stage = 0, pre_raw = 0;      // stages / scale slabs whose P half is already on its way
+        uint32_t pre_stage = 0, pre_raw = 0;      // stages / scale slabs whose weights half is already on its way
         bool ok = true;
         const uint64_t pol_p = l2_policy(P.l2_p), pol_q = l2_policy(P.l2_q);
+        // The weights are P in the swapped form and Q otherwise; "the other operand" is the activations.  Stage halves
+        // and scale-slab parts of the two, as the early requests below and the loop after them issue them.
+        constexpr bool WQ = !Cfg::SWAP;
+        auto load_weights = [&](uint32_t stage_dst, uint32_t bar, int kblk, const Segment& s) {
+            if (WQ) tma_load_2d_hint(stage_dst + q_off, &tm_q, bar, kblk * Cfg::BK, s.q0, pol_q);
+            else tma_load_2d_hint(stage_dst, &tm_p, bar, kblk * Cfg::BK, s.p0, pol_p);
+        };
+        auto load_other = [&](uint32_t stage_dst, uint32_t bar, int kblk, const Segment& s) {
+            if (WQ) tma_load_2d_hint(stage_dst, &tm_p, bar, kblk * Cfg::BK, s.p0, pol_p);
+            else tma_load_2d_hint(stage_dst + q_off, &tm_q, bar, kblk * Cfg::BK, s.q0, pol_q);
+        };
+        auto slab_weights = [&](uint32_t slab_dst, uint32_t bar, int kblk, const Segment& s) {
+            if (WQ) tma_load_2d_hint(slab_dst + Cfg::BM * 16, &tm_sfq, bar, (kblk >> 2) * 16, s.q0, pol_q);
+            else tma_load_2d_hint(slab_dst, &tm_sfp, bar, (kblk >> 2) * 16, s.p0, pol_p);
+        };
+        auto slab_other = [&](uint32_t slab_dst, uint32_t bar, int kblk, const Segment& s) {
+            if (WQ) tma_load_2d_hint(slab_dst, &tm_sfp, bar, (kblk >> 2) * 16, s.p0, pol_p);
+            else tma_load_2d_hint(slab_dst + Cfg::BM * 16, &tm_sfq, bar, (kblk >> 2) * 16, s.q0, pol_q);
+        };
         if (early) {
             SegIter<Cfg> it2(P);
             Segment s2;
@@ -407,7 +426,7 @@ mxfp6_gemm_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constan
                         if (slabs && pre_raw < (uint32_t)Cfg::RAW_SLOTS) {
                             if (elect_one_sync()) {
                                 mbar_arrive_expect_tx(bar_raw_full(pre_raw), (uint32_t)P.raw_tx_bytes);
-                                tma_load_2d_hint(raw_base + pre_raw * Cfg::RAW_BYTES, &tm_sfp, bar_raw_full(pre_raw), (k_at(P, s2, k) >> 2) * 16, s2.p0, pol_p);
+                                slab_weights(raw_base + pre_raw * Cfg::RAW_BYTES, bar_raw_full(pre_raw), k_at(P, s2, k), s2);
                             }
                             ++pre_raw;
                         } else {
@@ -416,13 +435,13 @@ mxfp6_gemm_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constan
                     }
                     if (elect_one_sync()) {
                         mbar_arrive_expect_tx(bar_full(pre_stage), (uint32_t)P.stage_tx_bytes);
-                        tma_load_2d_hint(stage_base + pre_stage * stage_stride, &tm_p, bar_full(pre_stage), k_at(P, s2, k) * Cfg::BK, s2.p0, pol_p);
+                        load_weights(stage_base + pre_stage * stage_stride, bar_full(pre_stage), k_at(P, s2, k), s2);
                     }
                     __syncwarp();
                     ++pre_stage;
                 }
             }
-            pdl_wait();          // the Q halves (activations) and all stores come after the preceding kernel
+            pdl_wait();          // the activations' halves and all stores come after the preceding kernel
         }
         while (ok && it.next(sg)) {
             for (int kb = sg.k0; kb < sg.k1 && ok;) {
@@ -440,9 +459,9 @@ mxfp6_gemm_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constan
                             const uint32_t dst = raw_base + r * Cfg::RAW_BYTES;
                             if (n_raw >= pre_raw) {
                                 mbar_arrive_expect_tx(bar_raw_full(r), (uint32_t)P.raw_tx_bytes);
-                                tma_load_2d_hint(dst, &tm_sfp, bar_raw_full(r), (k_at(P, sg, k) >> 2) * 16, sg.p0, pol_p);
+                                slab_weights(dst, bar_raw_full(r), k_at(P, sg, k), sg);
                             }
-                            tma_load_2d_hint(dst + Cfg::BM * 16, &tm_sfq, bar_raw_full(r), (k_at(P, sg, k) >> 2) * 16, sg.q0, pol_q);
+                            slab_other(dst, bar_raw_full(r), k_at(P, sg, k), sg);
                         }
                         ++n_raw;
                     }
@@ -460,9 +479,9 @@ mxfp6_gemm_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constan
                         const uint32_t dst = stage_base + s * stage_stride;
                         if (n_stage + j >= pre_stage) {
                             mbar_arrive_expect_tx(bar_full(s), (uint32_t)P.stage_tx_bytes);
-                            tma_load_2d_hint(dst, &tm_p, bar_full(s), k_at(P, sg, kb + j) * Cfg::BK, sg.p0, pol_p);
+                            load_weights(dst, bar_full(s), k_at(P, sg, kb + j), sg);
                         }
-                        tma_load_2d_hint(dst + q_off, &tm_q, bar_full(s), k_at(P, sg, kb + j) * Cfg::BK, sg.q0, pol_q);
+                        load_other(dst, bar_full(s), k_at(P, sg, kb + j), sg);
                     }
                 }
                 __syncwarp();

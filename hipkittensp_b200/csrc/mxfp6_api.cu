@@ -650,9 +650,9 @@ static int gemm_impl(const void* a, const void* sfa, const void* b, const void* 
     P.status = d.status;
     P.wait_cycles = d.wait_cycles;
     r.pdl = o.pdl != 0;
-    // B is the P operand of the swapped (skinny-M) form; with programmatic dependent launch its first stages may be
-    // requested while the preceding kernel is still draining
-    P.early_p = (pl.swap && (flags & MXFP6_FLAG_B_STATIC) && o.pdl) ? 1 : 0;
+    // B is the P operand of the swapped (skinny-M) form and the Q operand otherwise; with programmatic dependent launch
+    // the single-CTA kernel may request its first stages while the preceding kernel is still draining
+    P.early_p = (!pl.pair && (flags & MXFP6_FLAG_B_STATIC) && o.pdl) ? 1 : 0;
     P.group_p = o.group_p;   // 16 pair-tiles (4096 rows of A) share each tile of B
     P.l2_load = o.l2_load; P.l2_store = o.l2_store;
     P.sig_counter = sig.counter; P.sig_flag = sig.flag; P.sig_cols = sig.cols;

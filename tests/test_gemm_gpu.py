@@ -397,9 +397,12 @@ def test_b_static_flag_back_to_back(M):
     check(want.float().cpu().numpy(), ref, absdot)
 
 
-@pytest.mark.parametrize("M,N,K", [(16, 296 * 82, 1024), (32, 296 * 97, 512)])
+@pytest.mark.parametrize("M,N,K", [(16, 296 * 82, 1024), (32, 296 * 97, 512),
+                                   (64, 148 * 200, 1024), (128, 148 * 160, 512),     # unswapped skinny forms: the weights are the Q operand
+                                   (384, 1280, 1024)])                                # single-CTA tiles of a small unswapped problem
 def test_b_static_flag_even_rows_form(M, N, K):
-    """The same promise in the even-rows skinny form (two CTAs per SM, rotated K loops)."""
+    """The same promise in the even-rows skinny forms (two CTAs per SM with rotated K loops; unswapped with the weights
+    as the second operand) and in a small unswapped problem."""
     pa, sa, pb, sb = quantized_inputs("decode", M, N, K, seed=M)
     t = [torch.from_numpy(x).cuda() for x in (pa, sa, pb, sb)]
     want = hk.gemm(t[0], t[1], t[2], t[3])
