@@ -54,8 +54,8 @@ def parse():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
-    ap.add_argument("--gather", default="auto", choices=["auto", "fused", "copy"],
-                    help="N > 1: the exchange that overlaps the GEMM (auto: both are probed, the faster one is timed)")
+    ap.add_argument("--gather", default="fused", choices=["fused", "copy"],
+                    help="N > 1: the exchange that overlaps the GEMM and is timed (epilogue pushes, or copy engines behind block flags)")
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU baseline leg (N=1)")
     ap.add_argument("--no-extras", action="store_true", help="skip extra_configs, sustained and check (profiling aid)")
     ap.add_argument("--small", action="store_true", help="1024^3 instead of 8192^3 (profiling aid, not a bench value)")
@@ -498,38 +498,21 @@ def run_sharded(args, torch, hk, device, peaks, world, rank):
         dist.barrier()
         torch.cuda.synchronize()
 
-    # Two exchanges that overlap the GEMM: tiles pushed to the peers by the epilogue ("fused"), and blocks carried by the
-    # copy engines behind per-block flags the kernel raises ("copy").  Which is faster depends on the number of GPUs (the
-    # first is bound by what SM-issued stores get out of the fabric, the second waits for whole blocks), so both are
-    # warmed up and probed with a few steps, the maximum over ranks decides, and the chosen one is timed.
+    # Two exchanges overlap the GEMM: tiles pushed to the peers by the epilogue ("fused", the default: the faster one on
+    # every box measured so far) and blocks carried by the copy engines behind per-block flags the kernel raises ("copy").
+    # The one named by --gather is timed; the other runs a few steps after the timed region, for the record and for the
+    # check that both give the same matrix.  (Nothing runs before the timed region but its own warm-up: a second exchange
+    # probed first would heat the part and cost the GEMM-bound configurations a few per cent.)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     ops, probe_ms = {}, {}
-    modes = ["fused", "copy"] if args.gather == "auto" else [args.gather]
-    for mode in modes:
-        try:
-            cand = ColumnParallelGemm(M, N, K, device=device, gather=mode)
-        except Exception as e:                                      # symmetric memory unavailable on this box
-            print(f"[bench] gather={mode} unavailable ({e!r})", file=sys.stderr)
-            continue
-        if cand.mode != mode:                                       # the operator fell back (shard too small for block flags)
-            continue
-        for i in range(W):
-            cand(a, sa, b, sb)
-        barrier()
-        e0.record()
-        for i in range(3):
-            cand(a, sa, b, sb)
-        e1.record()
-        barrier()
-        t = torch.tensor([e0.elapsed_time(e1) / 3], device=device)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ops[mode], probe_ms[mode] = cand, float(t)
-    if not ops:
-        print("[bench] no overlapped gather available; using the NCCL all-gather", file=sys.stderr)
-        ops["nccl"] = ColumnParallelGemm(M, N, K, device=device, gather="nccl")
-        probe_ms["nccl"] = 0.0
-    chosen = min(ops, key=lambda m: probe_ms[m])
-    op = ops[chosen]
+    try:
+        op = ColumnParallelGemm(M, N, K, device=device, gather=args.gather)
+        if op.mode != args.gather:          # the operator fell back (shard too small for block flags)
+            print(f"[bench] gather={args.gather} not available for this shard; timing gather={op.mode}", file=sys.stderr)
+    except Exception as e:                                          # symmetric memory unavailable on this box
+        print(f"[bench] gather={args.gather} unavailable ({e!r}); using the NCCL all-gather", file=sys.stderr)
+        op = ColumnParallelGemm(M, N, K, device=device, gather="nccl")
+    ops[op.mode] = op
 
     def step(i):
         return op(a, sa, b, sb)
@@ -605,12 +588,31 @@ def run_sharded(args, torch, hk, device, peaks, world, rank):
     # (iv) the NCCL all-gather + re-layout exchange gives the same matrix
     nccl_equal = None
     others_equal = True
-    for mode, other in ops.items():          # the exchange that was not timed gives the same matrix
-        if other is not op:
+    if op.mode in ("fused", "copy"):         # the overlapped exchange that was not timed: same matrix, and its time for the record
+        other_mode = "copy" if op.mode == "fused" else "fused"
+        try:
+            other = ColumnParallelGemm(M, N, K, device=device, gather=other_mode)
+        except Exception as e:
+            other = None
+            print(f"[bench] gather={other_mode} unavailable ({e!r})", file=sys.stderr)
+        if other is not None and other.mode == other_mode:
             c_o = other(a, sa, b, sb)
             torch.cuda.synchronize()
-            others_equal = others_equal and int(digest(c_o)) == int(d_fused)
+            others_equal = int(digest(c_o)) == int(d_fused)
             del c_o
+            for _ in range(2):
+                other(a, sa, b, sb)
+            barrier()
+            e0.record()
+            for _ in range(3):
+                other(a, sa, b, sb)
+            e1.record()
+            barrier()
+            t = torch.tensor([e0.elapsed_time(e1) / 3], device=device)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            probe_ms[other_mode] = float(t)
+        del other
+        torch.cuda.empty_cache()
     if op.mode in ("fused", "copy"):
         op2 = ColumnParallelGemm(M, N, K, device=device, gather="nccl")
         c2 = op2(a, sa, b, sb)
@@ -722,8 +724,9 @@ def run_sharded(args, torch, hk, device, peaks, world, rank):
             "gemm_only_efficiency": round(single_ms / (world * kernel_ms), 4),
             "nvlink_ingress_gbs": round(ingress, 1),
             "nvlink_ingress_frac_of_770": round(ingress / 770.0, 4),
-            "gather": {"timed": op.mode, "probe_ms_per_step": {m: round(v, 4) for m, v in probe_ms.items()},
-                       "how": "each overlapped exchange warmed up and probed with 3 steps (max over ranks); the faster one is timed"},
+            "gather": {"timed": op.mode, "other_ms_per_step": {m: round(v, 4) for m, v in probe_ms.items()},
+                       "how": "the exchange named by --gather is timed; the other overlapped exchange runs 3 steps after the timed "
+                              "region (max over ranks), for the record"},
             "nccl_gather_ms_per_step": round(nccl_ms, 4) if op.mode in ("fused", "copy") else None,
         }
         print(json.dumps(line), flush=True)
