@@ -588,14 +588,19 @@ def run_sharded(args, torch, hk, device, peaks, world, rank):
     # (iv) the NCCL all-gather + re-layout exchange gives the same matrix
     nccl_equal = None
     others_equal = True
-    if op.mode in ("fused", "copy"):         # the overlapped exchange that was not timed: same matrix, and its time for the record
+    # the overlapped exchange that was not timed: same matrix, and its time for the record (on up to 4 GPUs, where it has
+    # been run before: this leg must not put the line of a larger run at risk)
+    if op.mode in ("fused", "copy") and world <= 4:
         other_mode = "copy" if op.mode == "fused" else "fused"
         try:
             other = ColumnParallelGemm(M, N, K, device=device, gather=other_mode)
+            built = 1
         except Exception as e:
-            other = None
+            other, built = None, 0
             print(f"[bench] gather={other_mode} unavailable ({e!r})", file=sys.stderr)
-        if other is not None and other.mode == other_mode:
+        t_built = torch.tensor([built], device=device)
+        dist.all_reduce(t_built, op=dist.ReduceOp.MIN)      # every rank or none
+        if int(t_built) == 1 and other.mode == other_mode:
             c_o = other(a, sa, b, sb)
             torch.cuda.synchronize()
             others_equal = int(digest(c_o)) == int(d_fused)
