@@ -80,6 +80,7 @@ struct GemmParams {
     int tail_first;            // pair kernel: first tile of the last partial wave that is cut into column slices (= tile count if none)
     int tail_split;            // pair kernel: slices per such tile (1, 2 or 4)
     int stage_tx_bytes_tail;   // pair kernel: bytes one CTA's loads of a slice's stage report
+    int l2_ahead;              // single-CTA kernel: while it waits for the preceding kernel the producer asks the weights of its first stages into L2
     int early_p;               // single-CTA kernel: the weights (B: P when swapped, Q otherwise) may be read before the preceding kernel has finished
     int l2_load, l2_store;     // L2 eviction policy of the operand loads / of the stores of C (0 normal, 1 evict_first, 2 evict_last)
     int l2_p, l2_q;            // single-CTA kernel: policy of the loads of P / of Q (an operand that is read once leaves L2 first, one that every CTA re-reads last)
@@ -385,7 +386,8 @@ mxfp6_gemm_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constan
     // Nothing above touches global memory; everything below may.  With early_p the producer warp alone goes
     // ahead and requests the first stages of the weights (which the preceding kernel does not write) before it waits.
     const bool early = P.early_p != 0;
-    if (!(early && warp == 0)) pdl_wait();
+    const bool ahead = early || P.l2_ahead != 0;      // the producer warp has something to do before the wait
+    if (!(ahead && warp == 0)) pdl_wait();
 
     // =========================================================== warp 0: TMA producer
     if (warp == 0) {
@@ -420,8 +422,18 @@ mxfp6_gemm_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constan
             SegIter<Cfg> it2(P);
             Segment s2;
             bool slabs = P.sf_tma != 0;
-            while (pre_stage < (uint32_t)n_stages && it2.next(s2)) {
-                for (int k = s2.k0; k < s2.k1 && pre_stage < (uint32_t)n_stages; ++k) {
+            // the ring's first fill is requested for real; the K-blocks behind it are asked into L2 (see below)
+            uint32_t n_seen = 0;
+            const uint32_t n_total = (uint32_t)(n_stages * (1 + P.l2_ahead));
+            while (n_seen < n_total && it2.next(s2)) {
+                for (int k = s2.k0; k < s2.k1 && n_seen < n_total; ++k, ++n_seen) {
+                    if (n_seen >= (uint32_t)n_stages) {
+                        if (elect_one_sync()) {
+                            if (WQ) tma_prefetch_l2_2d(&tm_q, k_at(P, s2, k) * Cfg::BK, s2.q0);
+                            else tma_prefetch_l2_2d(&tm_p, k_at(P, s2, k) * Cfg::BK, s2.p0);
+                        }
+                        continue;
+                    }
                     if (P.sf_tma && (k == s2.k0 || (k & 3) == 0)) {
                         if (slabs && pre_raw < (uint32_t)Cfg::RAW_SLOTS) {
                             if (elect_one_sync()) {
@@ -441,7 +453,26 @@ mxfp6_gemm_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constan
                     ++pre_stage;
                 }
             }
+            __syncwarp();
             pdl_wait();          // the activations' halves and all stores come after the preceding kernel
+        } else if (ahead) {
+            // Without the caller's promise nothing may be read into shared memory yet, but the weights of the first
+            // stages can be asked into L2: a cache fill consumes nothing, and whatever the preceding kernel (or a peer, or
+            // the host) still writes to those lines goes through the same L2.  The loads after the wait then hit.
+            SegIter<Cfg> it2(P);
+            Segment s2;
+            uint32_t n_pre = 0;
+            const uint32_t want = (uint32_t)(n_stages * P.l2_ahead);      // l2_ahead ring fills
+            while (n_pre < want && it2.next(s2)) {
+                for (int k = s2.k0; k < s2.k1 && n_pre < want; ++k, ++n_pre) {
+                    if (elect_one_sync()) {
+                        if (WQ) tma_prefetch_l2_2d(&tm_q, k_at(P, s2, k) * Cfg::BK, s2.q0);
+                        else tma_prefetch_l2_2d(&tm_p, k_at(P, s2, k) * Cfg::BK, s2.p0);
+                    }
+                }
+            }
+            __syncwarp();
+            pdl_wait();
         }
         while (ok && it.next(sg)) {
             for (int kb = sg.k0; kb < sg.k1 && ok;) {

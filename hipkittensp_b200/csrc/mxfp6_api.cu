@@ -60,6 +60,7 @@ struct Options {
     int decode_rows = 1;     // MXFP6_DECODE_ROWS: skinny problems take the row-balanced kernel when they qualify
     int decode_stages = 0, decode_batch = 0;   // MXFP6_DECODE_RING = "stages,batch": ring of that kernel (0 = chosen by the library)
     int push_rotate = 1;     // MXFP6_PUSH_ROTATE: pair kernel, rotate the order of the peer destinations from piece to piece
+    int l2_ahead = 1;        // MXFP6_L2_AHEAD: the single-CTA kernel asks the weights of its first stages into L2 while it waits for the preceding kernel
     int c_tma_last = 1;      // MXFP6_C_TMA_LAST: the unswapped single-CTA kernel drains the last tile of every CTA through its idle ring and TMA stores
     int c_plain = 0;         // MXFP6_C_PLAIN: the pair kernel writes C with plain stores from its staging buffer even where TMA stores are possible
     int k_rot = 1;           // MXFP6_K_ROT: the even-rows skinny forms start each tile's K loop at its own K-block
@@ -86,6 +87,7 @@ static bool set_option(const char* name, const char* v) {
     else if (!strcmp(name, "MXFP6_K_ROT")) g_opt.k_rot = v ? atoi(v) : d.k_rot;
     else if (!strcmp(name, "MXFP6_C_PLAIN")) g_opt.c_plain = v ? atoi(v) : d.c_plain;
     else if (!strcmp(name, "MXFP6_C_TMA_LAST")) g_opt.c_tma_last = v ? atoi(v) : d.c_tma_last;
+    else if (!strcmp(name, "MXFP6_L2_AHEAD")) g_opt.l2_ahead = v ? atoi(v) : d.l2_ahead;
     else if (!strcmp(name, "MXFP6_PUSH_ROTATE")) g_opt.push_rotate = v ? atoi(v) : d.push_rotate;
     else if (!strcmp(name, "MXFP6_DECODE_RING")) {
         g_opt.decode_stages = d.decode_stages; g_opt.decode_batch = d.decode_batch;
@@ -95,7 +97,7 @@ static bool set_option(const char* name, const char* v) {
     return true;
 }
 static const char* const kOptionNames[] = {"MXFP6_FORCE_CFG", "MXFP6_NO_SF_TMA", "MXFP6_PDL", "MXFP6_GROUP_P", "MXFP6_QUANT_PATH",
-                                           "MXFP6_WAIT_MS", "MXFP6_L2", "MXFP6_TAIL_SPLIT", "MXFP6_DECODE_ROWS", "MXFP6_DECODE_RING", "MXFP6_K_ROT", "MXFP6_PUSH_ROTATE", "MXFP6_C_PLAIN", "MXFP6_C_TMA_LAST"};
+                                           "MXFP6_WAIT_MS", "MXFP6_L2", "MXFP6_TAIL_SPLIT", "MXFP6_DECODE_ROWS", "MXFP6_DECODE_RING", "MXFP6_K_ROT", "MXFP6_PUSH_ROTATE", "MXFP6_C_PLAIN", "MXFP6_C_TMA_LAST", "MXFP6_L2_AHEAD"};
 static const Options& options() {
     std::call_once(g_opt_once, [] {
         for (const char* n : kOptionNames)
@@ -650,9 +652,10 @@ static int gemm_impl(const void* a, const void* sfa, const void* b, const void* 
     P.status = d.status;
     P.wait_cycles = d.wait_cycles;
     r.pdl = o.pdl != 0;
-    // B is the P operand of the swapped (skinny-M) form and the Q operand otherwise; with programmatic dependent launch
-    // the single-CTA kernel may request its first stages while the preceding kernel is still draining
-    P.early_p = (!pl.pair && (flags & MXFP6_FLAG_B_STATIC) && o.pdl) ? 1 : 0;
+    // Asking the first weights into L2 before the wait needs no promise and measured 1 % faster than requesting them for
+    // real under the promise (and 3 % faster than the promise alone), so the promise is only used when the former is off.
+    P.l2_ahead = (!pl.pair && o.pdl && o.l2_ahead > 0) ? o.l2_ahead : 0;
+    P.early_p = (!pl.pair && (flags & MXFP6_FLAG_B_STATIC) && o.pdl && !P.l2_ahead) ? 1 : 0;
     P.group_p = o.group_p;   // 16 pair-tiles (4096 rows of A) share each tile of B
     P.l2_load = o.l2_load; P.l2_store = o.l2_store;
     P.sig_counter = sig.counter; P.sig_flag = sig.flag; P.sig_cols = sig.cols;

@@ -91,6 +91,11 @@ __device__ __forceinline__ uint64_t l2_policy_evict_normal() {
 __device__ __forceinline__ uint64_t l2_policy(int kind) {
     return kind == 1 ? l2_policy_evict_first() : kind == 2 ? l2_policy_evict_last() : l2_policy_evict_normal();
 }
+// Ask for a box of a tensor map to be brought into L2 (no shared-memory destination, no completion to wait for)
+__device__ __forceinline__ void tma_prefetch_l2_2d(const CUtensorMap* m, int x, int y) {
+    asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];"
+                 ::"l"(reinterpret_cast<uint64_t>(m)), "r"(x), "r"(y) : "memory");
+}
 // 32-byte global store (one whole sector per lane)
 __device__ __forceinline__ void st_global_v8(void* ptr, uint32_t x0, uint32_t x1, uint32_t x2, uint32_t x3,
                                              uint32_t x4, uint32_t x5, uint32_t x6, uint32_t x7) {

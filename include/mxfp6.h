@@ -77,10 +77,13 @@ int mxfp6_gemm(const void* a, const void* sfa, const void* b, const void* sfb, v
 
 /*
  * mxfp6_gemm with option flags.  MXFP6_FLAG_B_STATIC promises that B and its scales are not written by the work
- * queued on the stream directly before this call (weights of a layer): for skinny M, where B is the operand that
- * is streamed from HBM, the kernel then starts requesting B while the preceding kernel is still finishing
- * (programmatic dependent launch) and only the reads of A and all writes wait for it.  Without the flag nothing
- * is read before the preceding kernel has completed.  (No counterpart in the reference.)
+ * queued on the stream directly before this call (weights of a layer): the single-CTA kernels may then request B
+ * while the preceding kernel is still finishing (programmatic dependent launch), and only the reads of A and all
+ * writes wait for it.  Without the flag nothing is read into the kernel before the preceding kernel has completed;
+ * what every call does while it waits is to ask the first weight tiles into L2, which consumes nothing and sees
+ * later writes through the same cache.  That measured faster than the early requests, so in the default
+ * configuration the flag changes nothing; it takes effect when MXFP6_L2_AHEAD is switched off.  (No counterpart in
+ * the reference.)
  */
 #define MXFP6_FLAG_B_STATIC 1u
 int mxfp6_gemm_ex(const void* a, const void* sfa, const void* b, const void* sfb, void* c,
@@ -214,7 +217,7 @@ int mxfp6_debug_wait_timeout(int budget_us, void* stream);
 /*
  * Test hook: sets one of the library's switches (the names of the environment variables that give their first
  * values: "MXFP6_FORCE_CFG" = "bn,swap,streamk[,pair]" forces a kernel variant, "MXFP6_NO_SF_TMA", "MXFP6_PDL",
- * "MXFP6_GROUP_P", "MXFP6_QUANT_PATH", "MXFP6_L2", "MXFP6_TAIL_SPLIT", "MXFP6_DECODE_ROWS", "MXFP6_DECODE_RING", "MXFP6_K_ROT", "MXFP6_PUSH_ROTATE", "MXFP6_C_PLAIN", "MXFP6_C_TMA_LAST"); value NULL restores the
+ * "MXFP6_GROUP_P", "MXFP6_QUANT_PATH", "MXFP6_L2", "MXFP6_TAIL_SPLIT", "MXFP6_DECODE_ROWS", "MXFP6_DECODE_RING", "MXFP6_K_ROT", "MXFP6_PUSH_ROTATE", "MXFP6_C_PLAIN", "MXFP6_C_TMA_LAST", "MXFP6_L2_AHEAD"); value NULL restores the
  * default.  Takes effect for calls made after it returns.  (No counterpart in the reference.)
  */
 int mxfp6_debug_option(const char* name, const char* value);

@@ -387,12 +387,19 @@ def test_b_static_flag_back_to_back(M):
     pa, sa, pb, sb = quantized_inputs("decode", M, N, K, seed=M)
     t = [torch.from_numpy(x).cuda() for x in (pa, sa, pb, sb)]
     want = hk.gemm(t[0], t[1], t[2], t[3])
-    outs = [torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda") for _ in range(6)]
-    for o in outs:                                   # six launches queued without a host sync in between
-        hk.dispatch_micro(t[0], t[2], o, t[1], t[3], R.E2M3, b_static=True)
-    assert hk.device_status() == 0
-    for o in outs:
-        assert torch.equal(o.view(torch.int16), want.view(torch.int16))
+    # with the L2 requests that every call makes while it waits (the promise then changes nothing), and without them
+    # (the weights of the first stages are then loaded for real before the wait)
+    for ahead in (None, "0"):
+        hk.debug_option("MXFP6_L2_AHEAD", ahead)
+        try:
+            outs = [torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda") for _ in range(6)]
+            for o in outs:                               # six launches queued without a host sync in between
+                hk.dispatch_micro(t[0], t[2], o, t[1], t[3], R.E2M3, b_static=True)
+            assert hk.device_status() == 0
+        finally:
+            hk.debug_option("MXFP6_L2_AHEAD", None)
+        for o in outs:
+            assert torch.equal(o.view(torch.int16), want.view(torch.int16))
     ref, absdot = oracle_f64(pa, sa, pb, sb, R.E2M3)
     check(want.float().cpu().numpy(), ref, absdot)
 
@@ -406,12 +413,17 @@ def test_b_static_flag_even_rows_form(M, N, K):
     pa, sa, pb, sb = quantized_inputs("decode", M, N, K, seed=M)
     t = [torch.from_numpy(x).cuda() for x in (pa, sa, pb, sb)]
     want = hk.gemm(t[0], t[1], t[2], t[3])
-    outs = [torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda") for _ in range(6)]
-    for o in outs:
-        hk.dispatch_micro(t[0], t[2], o, t[1], t[3], R.E2M3, b_static=True)
-    assert hk.device_status() == 0
-    for o in outs:
-        assert torch.equal(o.view(torch.int16), want.view(torch.int16))
+    for ahead in (None, "0"):
+        hk.debug_option("MXFP6_L2_AHEAD", ahead)
+        try:
+            outs = [torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda") for _ in range(6)]
+            for o in outs:
+                hk.dispatch_micro(t[0], t[2], o, t[1], t[3], R.E2M3, b_static=True)
+            assert hk.device_status() == 0
+        finally:
+            hk.debug_option("MXFP6_L2_AHEAD", None)
+        for o in outs:
+            assert torch.equal(o.view(torch.int16), want.view(torch.int16))
     ref, absdot = oracle_f64(pa, sa, pb, sb, R.E2M3)
     check(want.float().cpu().numpy(), ref, absdot)
 
