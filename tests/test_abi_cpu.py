@@ -53,6 +53,30 @@ def test_bad_arguments_rejected_without_gpu():
     assert L.mxfp6_debug_option(b"MXFP6_GROUP_P", None) == _lib.OK
 
 
+def test_copy_gather_arguments_and_block_count():
+    """The copy-engine gather refuses bad arguments before it touches a device, and its scratch is two 32-bit words
+    (flag, counter) per block of C: row groups of 16 tile rows by strips of `strip_tiles` 256-column tiles."""
+    L = hk.lib
+    vp = ctypes.c_void_p
+    one = (vp * 1)(0x1000)
+    two = (vp * 2)(0x1000, 0x2000)
+    args = lambda dst, n, M, N, K, scratch, nbytes, strip, streams, ns: (None, None, None, None, dst, n, N, M, N, K, 0, 0, scratch, nbytes, strip, streams, ns, None)
+    assert L.mxfp6_gemm_copy_gather(*args(None, 1, 512, 512, 128, None, 0, 1, None, 0)) == _lib.ERR_BAD_ARG
+    assert b"destination" in L.mxfp6_last_error()
+    assert L.mxfp6_gemm_copy_gather(*args(one, 9, 512, 512, 128, None, 0, 1, None, 0)) == _lib.ERR_BAD_ARG
+    assert L.mxfp6_gemm_copy_gather(*args(one, 1, 0, 512, 128, None, 0, 1, None, 0)) == _lib.ERR_BAD_ARG
+    assert L.mxfp6_gemm_copy_gather(*args(one, 1, 512, 512, 128, None, 0, 0, None, 0)) == _lib.ERR_BAD_ARG
+    assert b"strip_tiles" in L.mxfp6_last_error()
+    assert L.mxfp6_gemm_copy_gather(*args(two, 2, 512, 512, 128, None, 0, 1, None, 0)) == _lib.ERR_BAD_ARG
+    assert b"copy streams" in L.mxfp6_last_error()
+    assert L.mxfp6_gemm_copy_gather(*args(one, 1, 512, 512, 128, None, 0, 1, None, 0)) == _lib.ERR_BAD_ARG
+    assert b"scratch too small" in L.mxfp6_last_error()
+    assert L.mxfp6_copy_gather_scratch_bytes(16384, 14336, 8) == 4 * 7 * 8
+    assert L.mxfp6_copy_gather_scratch_bytes(4352, 2304, 4) == 2 * 3 * 8
+    assert L.mxfp6_copy_gather_scratch_bytes(4352, 2304, 1000) == 2 * 1 * 8
+    assert L.mxfp6_copy_gather_scratch_bytes(0, 2304, 4) == 0
+
+
 def test_python_wrapper_rejects_cpu_and_bad_tensors():
     import torch
     A = torch.zeros(16, 96, dtype=torch.uint8)
