@@ -619,7 +619,9 @@ static int gemm_impl(const void* a, const void* sfa, const void* b, const void* 
         if (ns > 8) ns = 8;
         if (o.decode_stages >= 2 && o.decode_stages <= ns) ns = o.decode_stages;
         P.n_stages = ns;
-        P.load_batch = !pl.swap ? 1 : ns >= 8 ? 4 : ns >= 6 ? 3 : 2;
+        // K-blocks requested back to back (a row's adjacent 96-byte pieces then reach DRAM together).  Unswapped skinny
+        // tiles: two with a ring of 5 stages (M = 64 / 96 at N = 28672: +3 / +5 %), one with 4 (M = 128: two cost 6 %)
+        P.load_batch = !pl.swap ? (ns >= 5 ? 2 : 1) : ns >= 8 ? 4 : ns >= 6 ? 3 : 2;
         if (o.decode_batch >= 1 && o.decode_batch <= ns / 2) P.load_batch = o.decode_batch;
         // the even-rows forms of skinny problems (tiles narrower than a box) rotate their K loops
         const bool even_rows = pl.ctas == 2 || pl.q_tile != pl.bn;
