@@ -466,6 +466,11 @@ mxfp6_gemm_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constan
             while (n_pre < want && it2.next(s2)) {
                 for (int k = s2.k0; k < s2.k1 && n_pre < want; ++k, ++n_pre) {
                     if (elect_one_sync()) {
+                        // (the scale slab of the group first: the first MMA waits for the re-tiled scales as well)
+                        if (P.sf_tma && (k == s2.k0 || (k & 3) == 0)) {
+                            if (WQ) tma_prefetch_l2_2d(&tm_sfq, (k_at(P, s2, k) >> 2) * 16, s2.q0);
+                            else tma_prefetch_l2_2d(&tm_sfp, (k_at(P, s2, k) >> 2) * 16, s2.p0);
+                        }
                         if (WQ) tma_prefetch_l2_2d(&tm_q, k_at(P, s2, k) * Cfg::BK, s2.q0);
                         else tma_prefetch_l2_2d(&tm_p, k_at(P, s2, k) * Cfg::BK, s2.p0);
                     }

@@ -628,7 +628,12 @@ static int gemm_impl(const void* a, const void* sfa, const void* b, const void* 
         P.k_rot = (even_rows && o.k_rot && (K / 128) % 4 == 0) ? 1 : 0;
     }
     P.ldc = (int)dst.ldc; P.c_rows = (int)M; P.c_cols = (int)N;
-    P.idesc = make_idesc_m(fmt_mma_code(fp), fmt_mma_code(fq), pl.pair ? 256u : 128u, (uint32_t)pl.bn);
+    // The instruction's N: the accumulator's width, or, where an unswapped tile is narrower than its accumulator (the
+    // skinny forms: 200 of 256 columns at N = 28672), the tile's columns rounded up to 16, so that the tensor cores do
+    // not multiply the stale rows behind the tile (a fifth of the MMA work and of its power there).
+    uint32_t mma_n = (uint32_t)pl.bn;
+    if (!pl.pair && !pl.swap && pl.q_tile < pl.bn) mma_n = (uint32_t)((pl.q_tile + 15) / 16 * 16);
+    P.idesc = make_idesc_m(fmt_mma_code(fp), fmt_mma_code(fq), pl.pair ? 256u : 128u, mma_n);
     P.sf_tma = sf_tma ? 1 : 0;
     P.sf_ld = (int)(K / 32);
     // bytes a stage's two loads credit to its mbarrier: the global bytes of the boxes (fp6: 96 per 128 elements)
