@@ -727,6 +727,9 @@ mxfp6_gemm_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constan
             // of a skinny launch), whether or not the next chunk's load was already under way and whether the stores went
             // to rows of C or to shared memory.  Chunks that lie wholly past the tile's own columns are not read.
             constexpr int G = NCH < 4 ? NCH : 4;
+            // unswapped form: a warp whose 32 rows all lie below C (M <= 96) neither reads nor stores: the TMEM read-out
+            // shares 64 bytes per clock among the warps
+            const bool warp_live = Cfg::SWAP || sg.p0 + quad * 32 < (partial ? P.p_rows : P.c_rows);
             // The last tile of a CTA overlaps nothing, and in the unswapped form every lane stores to a row of its own: a
             // store instruction touches 32 lines and costs the load/store unit about 300 cycles, 2.2 to 2.8 us for a
             // 128 x 200 tile whatever the number of live rows.  By then the ring is idle (every load has landed and every MMA
@@ -841,7 +844,7 @@ mxfp6_gemm_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constan
 #pragma unroll
                 for (int g = 0; g < G; ++g) {
                     const int ch = chunk_of(cg + g);
-                    if (Cfg::SWAP || ch * CW < P.q_tile_rows) {
+                    if (warp_live && (Cfg::SWAP || ch * CW < P.q_tile_rows)) {
                         if constexpr (CW == 32) tmem_ld_x32(tacc + ch * CW, reinterpret_cast<uint32_t(&)[32]>(v[g]));
                         else tmem_ld_x16(tacc + ch * CW, reinterpret_cast<uint32_t(&)[16]>(v[g]));
                     }
@@ -851,8 +854,10 @@ mxfp6_gemm_kernel(const __grid_constant__ CUtensorMap tm_p, const __grid_constan
                 // accumulator is left in TMEM)
                 if (Cfg::OVERLAP && cg == 0) { tc_fence_before(); __syncwarp(); if (lane == 0) mbar_arrive(bar_ovl); }
                 if (!Cfg::OVERLAP && cg + G >= NCH) { tc_fence_before(); mbar_arrive(bar_acc_empty(b)); }
+                if (warp_live) {
 #pragma unroll
-                for (int g = 0; g < G; ++g) process(chunk_of(cg + g), v[g]);
+                    for (int g = 0; g < G; ++g) process(chunk_of(cg + g), v[g]);
+                }
             }
             if (n_pieces > 0) {
                 fence_proxy_async_smem();
