@@ -1114,7 +1114,7 @@ extern "C" int mxfp6_quantize(const void* src, int src_dtype, int64_t rows, int6
         CUtensorMap tm;
         if ((rc = make_map(src, nblk, 32, 128, src_dtype == 0 ? 4 : 5, &tm))) return rc;
         const int64_t n_tiles = (nblk + 127) / 128;
-        const int64_t max_grid = (int64_t)d->sm_count * (src_dtype == 0 ? 4 : 6);      // QuantCfg::CTAS_PER_SM resident CTAs per SM
+        const int64_t max_grid = (int64_t)d->sm_count * (src_dtype == 0 ? 4 : 7);      // QuantCfg::CTAS_PER_SM resident CTAs per SM
         const unsigned grid = (unsigned)(n_tiles < max_grid ? n_tiles : max_grid);
 #define QT(T, F)                                                                                                     \
         do {                                                                                                         \
